@@ -1,0 +1,309 @@
+// Mixture-of-experts entry points of the kernel ABI: lx_moe_route and the routed experts (lx_moe_experts_grouped,
+// lx_moe_experts_decode and the bf16 / BF16X variants), lernex/dromos engine/cuda/kernels.h:203-225, 495-511, 603-611.
+//
+// Routed experts, for T tokens each with top_k (expert, weight) pairs:
+//   1. group   the T * top_k pairs are sorted by expert, stably (ascending pair index inside an expert): one CTA, a
+//              thread per expert walks the ids in order. Integer work only, so the grouping is exact.
+//   2. gate_up the streaming kernel per (expert, 16 gate rows + the matching 16 up rows) with the expert's tokens as
+//              columns; its epilogue writes mid = bf16(silu(gate) * up) in grouped order.
+//   3. down    the streaming kernel per (expert, 32 output rows) on mid; its epilogue writes weight * row per pair.
+//   4. sum     out[t] = the token's top_k rows added in k order.
+// Every stage reads each chosen expert's weights once; no float atomics anywhere, so a token's bits do not depend on
+// the batch or the run.
+#include <algorithm>
+
+#include "launch.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kMaxExperts = 1024;
+constexpr int kMaxTopK = 32;
+
+// ---- routing (one warp per token) ------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) route_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                                    int32_t* __restrict__ ids, float* __restrict__ weights,
+                                                    float* __restrict__ entropy, float* __restrict__ confidence, int T,
+                                                    int E, int top_k) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const int lane = threadIdx.x & 31;
+  const float* row = logits + static_cast<int64_t>(t) * E;
+  // softmax statistics of the whole row
+  float m = -INFINITY;
+  for (int i = lane; i < E; i += 32) m = fmaxf(m, row[i]);
+  m = warp_max(m);
+  float z = 0.0f;
+  for (int i = lane; i < E; i += 32) z += expf(row[i] - m);
+  z = warp_sum(z);
+  float h = 0.0f;
+  for (int i = lane; i < E; i += 32) {
+    const float p = expf(row[i] - m) / z;
+    h -= p * logf(fmaxf(p, 1e-9f));
+  }
+  h = warp_sum(h);
+  if (lane == 0) {
+    if (entropy) entropy[t] = h;
+    if (confidence) confidence[t] = 1.0f / z;
+  }
+  // top_k by logit + bias, descending, ties to the lower index: top_k rounds of a warp arg-max over what is left
+  int mine = -1;        // lane j keeps pick j
+  float mine_logit = -INFINITY;
+  for (int r = 0; r < top_k; ++r) {
+    float best = -INFINITY;
+    int best_i = E;
+    for (int i = lane; i < E; i += 32) {
+      bool taken = false;
+      for (int j = 0; j < r; ++j) taken |= __shfl_sync(0xffffffffu, mine, j) == i;
+      if (taken) continue;
+      const float v = row[i] + (bias ? bias[i] : 0.0f);
+      if (v > best || (v == best && i < best_i)) best = v, best_i = i;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (ov > best || (ov == best && oi < best_i)) best = ov, best_i = oi;
+    }
+    if (lane == r) mine = best_i, mine_logit = best_i < E ? row[best_i] : -INFINITY;
+  }
+  // weights: softmax over the picks of their unbiased logits
+  const bool live = lane < top_k && mine >= 0 && mine < E;
+  const float lmax = warp_max(live ? mine_logit : -INFINITY);
+  const float ex = live ? expf(mine_logit - lmax) : 0.0f;
+  const float sum = warp_sum(ex);
+  if (lane < top_k) {
+    ids[static_cast<int64_t>(t) * top_k + lane] = live ? mine : 0;
+    weights[static_cast<int64_t>(t) * top_k + lane] = live ? ex / sum : 0.0f;
+  }
+}
+
+// ---- grouping --------------------------------------------------------------------------------------------------
+// offsets[e] = pairs of experts below e; pairs[offsets[e] + j] = the j-th pair (ascending) that chose expert e.
+// One CTA of 1024 threads, thread e walks the ids; E <= 1024.
+__global__ void __launch_bounds__(1024) group_kernel(const int32_t* __restrict__ ids, int P, int E,
+                                                     int32_t* __restrict__ offsets, int32_t* __restrict__ pairs) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ int32_t start[kMaxExperts + 1];
+  const int e = threadIdx.x;
+  int count = 0;
+  if (e < E)
+    for (int p = 0; p < P; ++p) count += ids[p] == e;
+  start[e] = e < E ? count : 0;
+  __syncthreads();
+  if (e == 0) {
+    int run = 0;
+    for (int i = 0; i < E; ++i) {
+      const int c = start[i];
+      start[i] = run;
+      run += c;
+    }
+    start[E] = run;
+  }
+  __syncthreads();
+  if (e <= E) offsets[e] = start[e];
+  if (e < E) {
+    int at = start[e];
+    for (int p = 0; p < P && count > 0; ++p)
+      if (ids[p] == e) pairs[at++] = p, --count;
+  }
+}
+
+// Grouping without knowing E (the decode entry points): the distinct experts of the ids in ascending order.
+// groups[g] = expert, offsets[g], pairs as above; unused groups get empty ranges. One CTA; P <= 1024.
+__global__ void __launch_bounds__(1024) group_small_kernel(const int32_t* __restrict__ ids, int P,
+                                                           int32_t* __restrict__ group_expert,
+                                                           int32_t* __restrict__ offsets, int32_t* __restrict__ pairs) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ int32_t sid[1024];
+  __shared__ int32_t first[1024];  // 1 when pair p is the first (lowest p) with its expert
+  __shared__ int32_t rank[1024];
+  const int p = threadIdx.x;
+  sid[p] = p < P ? ids[p] : 0x7fffffff;
+  __syncthreads();
+  int is_first = p < P;
+  int smaller = 0;  // distinct experts below mine = my group index (counted on first occurrences)
+  int before = 0;   // pairs of my expert before me
+  if (p < P) {
+    for (int q = 0; q < p; ++q) {
+      if (sid[q] == sid[p]) is_first = 0, ++before;
+    }
+  }
+  first[p] = is_first;
+  __syncthreads();
+  int members = 0;  // pairs of my expert
+  if (p < P) {
+    for (int q = 0; q < P; ++q) {
+      smaller += first[q] && sid[q] < sid[p];
+      members += sid[q] == sid[p];
+    }
+  }
+  rank[p] = smaller;
+  // pairs with a smaller expert id than mine = where my group starts
+  int below = 0;
+  if (p < P)
+    for (int q = 0; q < P; ++q) below += sid[q] < sid[p];
+  if (p < P) {
+    pairs[below + before] = p;
+    if (is_first) {
+      group_expert[smaller] = sid[p];
+      offsets[smaller] = below;
+    }
+  }
+  __syncthreads();
+  // groups past the last distinct expert: empty, starting at P
+  int groups = 0;
+  for (int q = 0; q < P; ++q) groups += first[q];
+  if (p <= P && p >= groups) offsets[p] = P;
+  if (p < P && p >= groups) group_expert[p] = 0;
+}
+
+// out[t, l] = sum over k, in order, of rows[t * top_k + k, l]
+__global__ void __launch_bounds__(256) ordered_sum_kernel(const float* __restrict__ rows, float* __restrict__ out, int T,
+                                                          int L, int top_k) {
+  pdl_trigger();
+  pdl_wait();
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= static_cast<int64_t>(T) * L) return;
+  const int64_t t = i / L, l = i % L;
+  float acc = 0.0f;
+  for (int k = 0; k < top_k; ++k) acc += rows[(t * top_k + k) * L + l];
+  out[i] = acc;
+}
+
+int64_t round_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+struct Layout {
+  int64_t offsets, group_expert, pairs, mid, rows, total;
+};
+// groups: the number of expert groups the tables hold (E, or P when E is not known)
+Layout layout(int P, int groups, int L, int I) {
+  Layout l{};
+  int64_t o = 0;
+  auto take = [&](int64_t bytes) {
+    const int64_t at = o;
+    o = round_up(o + bytes, 256);
+    return at;
+  };
+  l.offsets = take(4ll * (groups + 1));
+  l.group_expert = take(4ll * groups);
+  l.pairs = take(4ll * P);
+  l.mid = take(2ll * P * I);
+  l.rows = take(4ll * P * L);
+  l.total = o;
+  return l;
+}
+
+int row_bytes_of(int type, int K) {
+  switch (type) {
+    case LX_W_BF16: return 2 * K;
+    case LX_W_NVFP4: return K / 2;
+    case LX_W_BF16X: return static_cast<int>(x16::row_bytes(K));
+    default: return K;
+  }
+}
+
+bool stack_streams(const lx_weight& w, int K) {
+  switch (w.type) {
+    case LX_W_BF16: return K % 32 == 0 && aligned(w.data, 16);
+    case LX_W_INT8:
+    case LX_W_FP8: return K % 64 == 0 && aligned(w.data, 16);
+    case LX_W_NVFP4: return K % 256 == 0 && aligned(w.data, 16) && aligned(w.scale, 16);
+    case LX_W_BF16X: return K % 32 == 0 && aligned(w.data, 8);
+    default: return false;
+  }
+}
+
+template <int MODE>
+int launch_expert_stage(const StreamParams& P, int type, dim3 grid, cudaStream_t s) {
+  switch (type) {
+    case LX_W_BF16: return launch_stream<LX_W_BF16, 1, 2, 1, 2, 4, MODE>(P, grid, s);
+    case LX_W_INT8: return launch_stream<LX_W_INT8, 1, 2, 1, 2, 4, MODE>(P, grid, s);
+    case LX_W_FP8: return launch_stream<LX_W_FP8, 1, 2, 1, 2, 4, MODE>(P, grid, s);
+    case LX_W_NVFP4: return launch_stream<LX_W_NVFP4, 1, 2, 1, 2, 4, MODE>(P, grid, s);
+    case LX_W_BF16X: return launch_stream<LX_W_BF16X, 1, 2, 1, 2, 4, MODE>(P, grid, s);
+  }
+  return kInvalid;
+}
+
+// Stages 2-4 on grouping tables already in the workspace. groups = grid extent over expert groups.
+int run_experts(const void* latent, const float* weights, const lx_weight& gate_up, const lx_weight& down, float* out,
+                uint8_t* ws, const Layout& l, bool indirect, int groups, int T, int L, int I, int top_k, cudaStream_t s) {
+  StreamParams g{};
+  g.w = static_cast<const uint8_t*>(gate_up.data);
+  g.scale = static_cast<const uint8_t*>(gate_up.scale);
+  g.global = gate_up.global;
+  g.expert_global = gate_up.type == LX_W_NVFP4 ? gate_up.expert_global : nullptr;
+  g.row_bytes = row_bytes_of(gate_up.type, L);
+  g.N = 2 * I, g.K = L;
+  g.x = latent, g.x_dtype = LX_BF16, g.ld_x = L, g.M = T;
+  g.offsets = reinterpret_cast<const int32_t*>(ws + l.offsets);
+  g.group_expert = indirect ? reinterpret_cast<const int32_t*>(ws + l.group_expert) : nullptr;
+  g.pairs = reinterpret_cast<const int32_t*>(ws + l.pairs);
+  g.route_w = weights;
+  g.top_k = top_k, g.I = I;
+  g.moe_out = ws + l.mid;
+  g.status = status_word();
+  if (int e = launch_expert_stage<kGateUp>(g, gate_up.type, dim3((I + 15) / 16, groups), s)) return e;
+
+  StreamParams d = g;
+  d.w = static_cast<const uint8_t*>(down.data);
+  d.scale = static_cast<const uint8_t*>(down.scale);
+  d.global = down.global;
+  d.expert_global = down.type == LX_W_NVFP4 ? down.expert_global : nullptr;
+  d.row_bytes = row_bytes_of(down.type, I);
+  d.N = L, d.K = I;
+  d.x = ws + l.mid, d.ld_x = I;
+  d.moe_out = ws + l.rows;
+  if (int e = launch_expert_stage<kDown>(d, down.type, dim3((L + 31) / 32, groups), s)) return e;
+
+  const int64_t n = static_cast<int64_t>(T) * L;
+  return launch_kernel(ordered_sum_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, s,
+                       reinterpret_cast<const float*>(ws + l.rows), out, T, L, top_k);
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int lx_moe_route(const float* logits, const float* selection_bias, int32_t* ids, float* weights,
+                            float* entropy, float* confidence, int T, int E, int top_k, void* stream) {
+  if (T <= 0) return kOk;
+  if (top_k < 1 || top_k > kMaxTopK || top_k > E || !logits || !ids || !weights) return kInvalid;
+  return launch_kernel(route_kernel, dim3((T + 7) / 8), dim3(256), 0, static_cast<cudaStream_t>(stream), logits,
+                       selection_bias, ids, weights, entropy, confidence, T, E, top_k);
+}
+
+extern "C" int64_t lx_moe_grouped_workspace_bytes(int T, int L, int I, int E, int top_k, lx_math math) {
+  (void)math;
+  if (T <= 0 || L <= 0 || I <= 0 || E <= 0 || top_k <= 0) return 0;
+  return layout(T * top_k, E, L, I).total;
+}
+
+extern "C" int lx_moe_experts_grouped(const void* latent, const int32_t* ids, const float* weights,
+                                      const lx_weight* gate_up, const lx_weight* down, lx_math math, float* out,
+                                      void* workspace, int T, int L, int I, int E, int top_k, void* stream) {
+  if (T < 0 || L <= 0 || I <= 0 || E <= 0 || top_k <= 0 || top_k > E || !gate_up || !down) return kInvalid;
+  if (math < LX_MATH_BF16 || math > LX_MATH_FP4) return kInvalid;
+  if (T == 0) return kOk;
+  if (!latent || !ids || !weights || !out || !workspace || !gate_up->data || !down->data) return kInvalid;
+  if ((gate_up->type != LX_W_BF16 && !gate_up->scale) || (down->type != LX_W_BF16 && !down->scale)) return kInvalid;
+  if (E > kMaxExperts || static_cast<int64_t>(T) * top_k > (1ll << 30)) return kNotSupported;
+  if (gate_up->type < LX_W_BF16 || gate_up->type > LX_W_NVFP4 || down->type < LX_W_BF16 || down->type > LX_W_NVFP4)
+    return kNotSupported;
+  if (math != LX_MATH_BF16) return kNotSupported;  // activations stay bf16: weight-only products
+  if (I % 8 != 0 || L % 8 != 0 || !stack_streams(*gate_up, L) || !stack_streams(*down, I)) return kNotSupported;
+  auto s = static_cast<cudaStream_t>(stream);
+  const int P = T * top_k;
+  const Layout l = layout(P, E, L, I);
+  auto* ws = static_cast<uint8_t*>(workspace);
+  if (int e = launch_kernel(group_kernel, dim3(1), dim3(1024), 0, s, ids, P, E, reinterpret_cast<int32_t*>(ws + l.offsets),
+                            reinterpret_cast<int32_t*>(ws + l.pairs)))
+    return e;
+  return run_experts(latent, weights, *gate_up, *down, out, ws, l, false, E, T, L, I, top_k, s);
+}

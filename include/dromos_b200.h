@@ -1,0 +1,168 @@
+/* libdromos_b200.so: the decode weight-streaming products of the Dromos kernel ABI, for NVIDIA B200 (sm_100a).
+ *
+ * Every function below has the name, argument list, argument meaning and error behaviour of the function
+ * it replaces in the reference project's backend interface (lernex/dromos engine/cuda/kernels.h and
+ * engine/cuda/tunable.h; the line cited beside each declaration). The reference's dispatcher resolves
+ * backend entry points by name with dlsym from one shared library chosen by LX_KERNELS=<file>
+ * (engine/dispatch/dispatch.cpp:198-205, tools/gen_dispatch.py:200-211), so exporting these names is the
+ * whole integration: functions this library does not export answer LX_ERR_NOT_SUPPORTED from the
+ * dispatcher's own stub (tools/gen_dispatch.py:168-184).
+ *
+ * Conventions (kernels.h:1-4, 29-38): pointers are device pointers to row-major buffers, ld_* is a row
+ * stride in elements, `stream` is a cudaStream_t passed as void* (null = default stream), weights are
+ * [out, in] and y = x @ W^T. Functions return a cudaError_t value: 0 success, 1 invalid argument, 801 an
+ * unsupported format / math / shape. No function falls back to the CPU.
+ */
+#pragma once
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef LX_API
+#define LX_API __attribute__((visibility("default")))
+#endif
+
+/* kernels.h:27 */
+typedef enum { LX_F32 = 0, LX_BF16 = 1 } lx_dtype;
+/* kernels.h:243 */
+typedef enum { LX_W_BF16 = 0, LX_W_INT8 = 1, LX_W_FP8 = 2, LX_W_NVFP4 = 3, LX_W_BF16X = 4 } lx_wtype;
+/* kernels.h:431 */
+typedef enum { LX_MATH_BF16 = 0, LX_MATH_INT8 = 1, LX_MATH_FP8 = 2, LX_MATH_FP4 = 3 } lx_math;
+/* kernels.h:302-303 */
+#define LX_ERR_NOT_SUPPORTED 801
+typedef enum { LX_BACKEND_CUDA = 0, LX_BACKEND_HIP = 1, LX_BACKEND_METAL = 2, LX_BACKEND_CPU = 3 } lx_backend;
+/* tunable.h:27-32 */
+#define LX_ERR_TUNE_REJECTED 802
+#define LX_ERR_TUNE_VARIANT 803
+
+/* kernels.h:411-417. A host struct; data / scale / expert_global are device pointers.
+ *   LX_W_BF16   data bf16 [N, K]
+ *   LX_W_INT8   data int8 [N, K], scale f32 [N]:                 w = q * scale[n]
+ *   LX_W_FP8    data e4m3 [N, K], scale f32 [N]:                 w = fp8 * scale[n]
+ *   LX_W_NVFP4  data u8 [N, K/2] (low nibble = even k), scale e4m3 [N, K/16], global f32
+ *   LX_W_BF16X  data = N records of lx_bf16x_row_bytes(K) bytes (+ overflow records)
+ * Stacks [E, N, K] are the experts one after the other; an NVFP4 stack may carry expert_global f32 [E]. */
+typedef struct {
+  lx_wtype type;
+  const void* data;
+  const void* scale;
+  float global;
+  const float* expert_global;
+} lx_weight;
+
+/* ---- decode GEMV, M <= 8 rows -------------------------------------------------------------------------
+ * y[m, n] = alpha * (sum_k x[m, k] * w[n, k] + bias[n]) + beta * y[m, n]; f32 accumulation; y is read only
+ * when beta != 0; deterministic; a row's bits do not depend on M. */
+/* kernels.h:436 (engine/cuda/gemv.cu:1183) */
+LX_API int lx_gemv_w(const void* x, lx_dtype x_dtype, int ld_x, const lx_weight* w, const void* bias,
+                     lx_dtype bias_dtype, void* y, lx_dtype y_dtype, int ld_y, int M, int N, int K, float alpha,
+                     float beta, void* stream);
+/* kernels.h:244 (gemv.cu:1239): bf16 or int8 weights with a per-row scale */
+LX_API int lx_gemv(const void* x, lx_dtype x_dtype, int ld_x, const void* w, lx_wtype w_type, const float* w_scale,
+                   const void* bias, lx_dtype bias_dtype, void* y, lx_dtype y_dtype, int ld_y, int M, int N, int K,
+                   float alpha, float beta, void* stream);
+/* kernels.h:589 (engine/cuda/bf16x.cu:1297): LX_W_BF16X weights, y bit-identical to the bf16 product */
+LX_API int lx_gemv_bf16x(const void* x, lx_dtype x_dtype, int ld_x, const void* w, const void* bias,
+                         lx_dtype bias_dtype, void* y, lx_dtype y_dtype, int ld_y, int M, int N, int K, float alpha,
+                         float beta, void* stream);
+/* kernels.h:594: the same product on plain bf16 weights */
+LX_API int lx_gemv_decode_bf16(const void* x, lx_dtype x_dtype, int ld_x, const void* w, const void* bias,
+                               lx_dtype bias_dtype, void* y, lx_dtype y_dtype, int ld_y, int M, int N, int K,
+                               float alpha, float beta, void* stream);
+
+/* ---- batched decode / prefill product, any M ------------------------------------------------------------
+ * kernels.h:448, 451 (engine/cuda/gemm_w.cu:187-192). workspace: at least lx_gemm_workspace_bytes. */
+LX_API int lx_gemm_w(const void* x, lx_dtype x_dtype, int ld_x, const lx_weight* w, lx_math math, const void* bias,
+                     lx_dtype bias_dtype, void* y, lx_dtype y_dtype, int ld_y, int M, int N, int K, float alpha,
+                     float beta, void* workspace, void* stream);
+LX_API int64_t lx_gemm_workspace_bytes(int M, int K, lx_math math);
+/* kernels.h:475 (engine/cuda/gemm_skinny.cu:286): bf16 weights, bf16 x, any M in chunks of 64 */
+LX_API int lx_gemm_skinny(const void* x, lx_dtype x_dtype, int ld_x, const lx_weight* w, const void* bias,
+                          lx_dtype bias_dtype, void* y, lx_dtype y_dtype, int ld_y, int M, int N, int K, float alpha,
+                          float beta, void* stream);
+
+/* ---- quantizers (load time) ----------------------------------------------------------------------------- */
+/* kernels.h:492 (engine/cuda/quant_act.cu:279) */
+LX_API int lx_quantize_act(const void* x, lx_dtype x_dtype, int ld_x, lx_math math, void* q, int ld_q, float* scale,
+                           void* block_scale, int ld_bs, int M, int K, void* stream);
+/* kernels.h:518 (engine/cuda/quant.cu:140). NVFP4 synchronizes the stream and writes out->global. */
+LX_API int lx_quantize_weight(const void* w, lx_weight* out, int64_t rows, int cols, void* stream);
+/* kernels.h:523 (quant.cu:196) */
+LX_API int lx_dequantize_weight(const lx_weight* w, void* out, int64_t rows, int cols, void* stream);
+/* kernels.h:251 (gemv.cu:1251) */
+LX_API int lx_quantize_w8(const void* w, int8_t* q, float* scale, int64_t rows, int cols, void* stream);
+
+/* ---- lossless bf16 (LX_W_BF16X) --------------------------------------------------------------------------
+ * kernels.h:574-583 (engine/cuda/bf16x.cu:1236-1295). lx_bf16x_bytes and lx_bf16x_encode synchronize the
+ * stream and are load-time calls. */
+LX_API int64_t lx_bf16x_row_bytes(int K);
+LX_API int64_t lx_bf16x_bytes(const void* w, int64_t rows, int K, void* stream);
+LX_API int lx_bf16x_encode(const void* w, int64_t rows, int K, void* out, int64_t out_bytes, void* stream);
+LX_API int lx_bf16x_decode(const void* data, int64_t rows, int K, void* w, void* stream);
+
+/* ---- mixture of experts -------------------------------------------------------------------------------- */
+/* kernels.h:208 (engine/cuda/moe.cu:249, route.cuh:18-81) */
+LX_API int lx_moe_route(const float* logits, const float* selection_bias, int32_t* ids, float* weights,
+                        float* entropy, float* confidence, int T, int E, int top_k, void* stream);
+/* kernels.h:508, 511 (engine/cuda/moe_grouped.cu:381-388) */
+LX_API int lx_moe_experts_grouped(const void* latent, const int32_t* ids, const float* weights,
+                                  const lx_weight* gate_up, const lx_weight* down, lx_math math, float* out,
+                                  void* workspace, int T, int L, int I, int E, int top_k, void* stream);
+LX_API int64_t lx_moe_grouped_workspace_bytes(int T, int L, int I, int E, int top_k, lx_math math);
+/* kernels.h:504, 507 (engine/cuda/moe_decode.cu:397): T <= 8, top_k <= 8 */
+LX_API int lx_moe_experts_decode(const void* latent, const int32_t* ids, const float* weights,
+                                 const lx_weight* gate_up, const lx_weight* down, float* out, void* workspace, int T,
+                                 int L, int I, int top_k, void* stream);
+LX_API int64_t lx_moe_decode_workspace_bytes(int T, int I, int top_k);
+/* kernels.h:603-611 (engine/cuda/bf16x.cu:1320-1369): BF16X and plain bf16 stacks, T <= 8 */
+LX_API int lx_moe_experts_bf16x(const void* latent, const int32_t* ids, const float* weights, const void* gate_up,
+                                const void* down, float* out, void* workspace, int T, int L, int I, int top_k,
+                                void* stream);
+LX_API int lx_moe_experts_decode_bf16(const void* latent, const int32_t* ids, const float* weights,
+                                      const void* gate_up, const void* down, float* out, void* workspace, int T,
+                                      int L, int I, int top_k, void* stream);
+LX_API int64_t lx_moe_bf16x_workspace_bytes(int T, int I, int top_k);
+/* kernels.h:224 (engine/cuda/moe.cu:290): bf16 stacks, any T; allocates its scratch on the stream */
+LX_API int lx_moe_experts(const void* latent, const int32_t* ids, const float* weights, const void* gate_up,
+                          const void* down, float* out, int T, int L, int I, int top_k, void* stream);
+
+/* ---- architecture and variant table (tunable.h:37-75, engine/cuda/tunable.cu) ---------------------------- */
+typedef struct {
+  int M, N, K;
+  int experts;
+  int weight;
+  int math;
+} lx_tune_problem;
+LX_API int lx_arch(void);
+LX_API int lx_set_arch_override(int arch);
+LX_API int lx_tune_get(const char* kernel, int M, int N, int K);
+LX_API int lx_tune_set(const char* kernel, int M, int N, int K, int variant);
+LX_API int lx_tune_force(const char* kernel, int M, int N, int K, int variant);
+LX_API void lx_tune_clear(void);
+LX_API int lx_tune_kernels(const char** names, int capacity);
+LX_API int lx_tune_variants(const char* kernel);
+LX_API const char* lx_tune_variant_name(const char* kernel, int variant);
+LX_API int lx_tune_run(const char* kernel, int variant, const lx_tune_problem* problem, float* out, void* stream);
+LX_API int lx_tune_runnable(const char* kernel);
+LX_API int lx_tune_key(const char* kernel, const lx_tune_problem* problem, char* out, int capacity);
+
+/* ---- what the loader probes (kernels.h:308-309; engine/dispatch/dispatch.cpp:122-126) -------------------- */
+LX_API int lx_rt_backend(void);      /* LX_BACKEND_CUDA */
+LX_API int lx_rt_device_count(void);
+/* kernels.h:373 (engine/cuda/bandwidth.cu:104): read-only DRAM bandwidth of the current device */
+LX_API int lx_bandwidth_probe(int64_t bytes, int reps, double* read_gbps, double* spec_gbps, void* stream);
+
+/* ---- additions of this library (no counterpart in the reference) ---------------------------------------- */
+/* Kernels this library has launched in this process since it was loaded (every stream, every thread). */
+LX_API int64_t lx_b200_kernel_launches(void);
+/* Reads and clears the device-side status word of the current device: 0, or a code saying which bounded wait
+ * inside a kernel ran out (the kernel then finished without hanging; its output is not valid).
+ * Synchronizes the device. */
+LX_API int lx_b200_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif

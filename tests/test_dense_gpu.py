@@ -1,0 +1,194 @@
+"""Parity of the decode products (lx_gemv_w, lx_gemv_bf16x, lx_gemm_w) against the float64 oracle, through the C ABI.
+
+Mirrors the reference's tests/kernels/test_gemv_w.py and test_gemm_w.py: dtype matrix, every M, strided rows with a
+"wrote past N" check, epilogue constants, determinism and batch invariance, plus the configurations the headline
+metric is quoted on, checked on sampled rows at full size.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from dromos_b200 import abi
+from oracle import dromos_oracle as O
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+FORMATS = [O.W_BF16, O.W_INT8, O.W_FP8, O.W_NVFP4, O.W_BF16X]
+NAMES = {O.W_BF16: "bf16", O.W_INT8: "int8", O.W_FP8: "fp8", O.W_NVFP4: "nvfp4", O.W_BF16X: "bf16x"}
+
+
+def run(lx, fmt, M, N, K, x_f32=False, y_f32=True, bias_dtype=None, alpha=1.0, beta=0.0, seed=0, fn="lx_gemv_w",
+        ld_pad=0, w_bits=None):
+    w_bits = util.bf16_normal((N, K), 0.02, seed) if w_bits is None else w_bits
+    wt = util.make_weight(w_bits, fmt)
+    dw = util.DeviceWeight(wt)
+    ld_x, ld_y = K + ld_pad, N + ld_pad
+    if x_f32:
+        xh = np.zeros((M, ld_x), dtype=np.float32)
+        xh[:, :K] = util.f32_normal((M, K), 1.0, seed + 1)
+        x_vals = xh[:, :K].astype(np.float64)
+    else:
+        xh = np.zeros((M, ld_x), dtype=np.uint16)
+        xh[:, :K] = util.bf16_normal((M, K), 1.0, seed + 1)
+        x_vals = O.bf16_bits_to_f32(xh[:, :K]).astype(np.float64)
+    bias_h = bias_v = None
+    if bias_dtype is not None:
+        if bias_dtype == abi.F32:
+            bias_h = util.f32_normal((N,), 0.5, seed + 2)
+            bias_v = bias_h.astype(np.float64)
+        else:
+            bias_h = util.bf16_normal((N,), 0.5, seed + 2)
+            bias_v = O.bf16_bits_to_f32(bias_h).astype(np.float64)
+    y_old = util.f32_normal((M, ld_y), 1.0, seed + 3)
+    if not y_f32:
+        y_old_bits = O.f32_to_bf16_bits(y_old)
+        y_old = O.bf16_bits_to_f32(y_old_bits)
+    # y pre-filled with NaN when beta == 0: it must not be read
+    y_init = y_old.copy() if beta != 0.0 else np.full((M, ld_y), np.nan, dtype=np.float32)
+    y_dev = util.dev(y_init if y_f32 else O.f32_to_bf16_bits(y_init))
+    x_dev = util.dev(xh)
+    bias_dev = None if bias_h is None else util.dev(bias_h)
+    ws = torch.empty(max(1, lx.lx_gemm_workspace_bytes(M, K, 0)), dtype=torch.uint8, device="cuda")
+    st = util.gemv(lx, x_dev, abi.F32 if x_f32 else abi.BF16, ld_x, dw, y_dev, abi.F32 if y_f32 else abi.BF16, ld_y, M, N, K,
+                   bias=bias_dev, bias_dtype=bias_dtype if bias_dtype is not None else abi.BF16, alpha=alpha, beta=beta,
+                   fn=fn, workspace=ws)
+    assert st == 0, f"status {st}"
+    util.check_status(lx)
+    got_full = util.host(y_dev) if y_f32 else O.bf16_bits_to_f32(util.host(y_dev, np.uint16))
+    want = O.gemv_reference(x_vals, util.reference_weight(w_bits, wt), bias_v, y_old[:, :N], alpha, beta)
+    return got_full, want, y_init
+
+
+def check(got_full, want, y_init, N, y_f32, what):
+    got = got_full[:, :N]
+    scale = max(1e-30, float(np.abs(want).max()))
+    # the reference suite's own bound (2^-8 of max|y| for bf16 outputs, 2e-4 for f32) and the acceptance bound
+    tol = (2.0**-8 if not y_f32 else 2e-4) * scale
+    assert np.all(np.isfinite(got)), f"{what}: non-finite"
+    err = float(np.abs(got - want).max())
+    assert err <= tol, f"{what}: max abs err {err:.3e} > {tol:.3e}"
+    if y_f32:
+        util.assert_close(got, want, what=what)
+    # columns past N keep what they held (compare bit patterns: NaN != NaN)
+    if got_full.shape[1] > N:
+        a = np.ascontiguousarray(got_full[:, N:]).view(np.uint32)
+        b = np.ascontiguousarray(y_init[:, N:]).view(np.uint32)
+        assert np.array_equal(a, b) or not y_f32, f"{what}: wrote past N"
+
+
+@pytest.mark.parametrize("fmt", FORMATS, ids=lambda f: NAMES[f])
+@pytest.mark.parametrize("M", [1, 2, 3, 5, 8])
+def test_gemv_every_m(lx, fmt, M):
+    N, K = 320, 2048
+    got, want, y0 = run(lx, fmt, M, N, K, seed=M)
+    check(got, want, y0, N, True, f"{NAMES[fmt]} M={M}")
+
+
+@pytest.mark.parametrize("fmt", FORMATS, ids=lambda f: NAMES[f])
+@pytest.mark.parametrize("x_f32", [False, True])
+@pytest.mark.parametrize("y_f32", [False, True])
+@pytest.mark.parametrize("bias_dtype", [None, abi.F32, abi.BF16])
+@pytest.mark.parametrize("alpha,beta", [(1.0, 0.0), (0.5, 0.75)])
+def test_gemv_dtype_matrix(lx, fmt, x_f32, y_f32, bias_dtype, alpha, beta):
+    M, N, K = 3, 136, 1024
+    got, want, y0 = run(lx, fmt, M, N, K, x_f32, y_f32, bias_dtype, alpha, beta, seed=7)
+    check(got, want, y0, N, y_f32, NAMES[fmt])
+
+
+@pytest.mark.parametrize("fmt", FORMATS, ids=lambda f: NAMES[f])
+@pytest.mark.parametrize("K", [32, 48, 256, 528, 768, 4096 + 256])
+def test_gemv_k_boundaries(lx, fmt, K):
+    if fmt == O.W_NVFP4 and K % 16:
+        pytest.skip("NVFP4 needs K % 16 == 0")
+    M, N = 2, 77
+    got, want, y0 = run(lx, fmt, M, N, K, seed=K)
+    check(got, want, y0, N, True, f"{NAMES[fmt]} K={K}")
+
+
+@pytest.mark.parametrize("fmt", FORMATS, ids=lambda f: NAMES[f])
+def test_gemv_strided_rows_and_tail(lx, fmt):
+    M, N, K = 4, 100, 512
+    got, want, y0 = run(lx, fmt, M, N, K, ld_pad=24, seed=3)
+    check(got, want, y0, N, True, NAMES[fmt])
+
+
+@pytest.mark.parametrize("fmt", FORMATS, ids=lambda f: NAMES[f])
+@pytest.mark.parametrize("M", [9, 16, 17, 32, 33, 64, 70])
+def test_gemm_w_small_m(lx, fmt, M):
+    if fmt == O.W_BF16X:
+        pytest.skip("lx_gemm_w takes BF16X through lx_bf16x_decode in the engine")
+    N, K = 264, 1024
+    got, want, y0 = run(lx, fmt, M, N, K, seed=M, fn="lx_gemm_w")
+    check(got, want, y0, N, True, f"{NAMES[fmt]} M={M}")
+
+
+@pytest.mark.parametrize("fmt", FORMATS, ids=lambda f: NAMES[f])
+def test_rows_do_not_depend_on_batch_and_runs_repeat(lx, fmt):
+    N, K = 256, 2048
+    w_bits = util.bf16_normal((N, K), 0.02, 11)
+    wt = util.make_weight(w_bits, fmt)
+    dw = util.DeviceWeight(wt)
+    x = util.bf16_normal((8, K), 1.0, 12)
+    x_dev = util.dev(x)
+    outs = {}
+    for M in (1, 2, 4, 8):
+        y = torch.full((M, N), float("nan"), device="cuda")
+        assert util.gemv(lx, x_dev, abi.BF16, K, dw, y, abi.F32, N, M, N, K) == 0
+        outs[M] = util.host(y).view(np.uint32).copy()
+    y2 = torch.full((8, N), float("nan"), device="cuda")
+    assert util.gemv(lx, x_dev, abi.BF16, K, dw, y2, abi.F32, N, 8, N, K) == 0
+    util.check_status(lx)
+    assert np.array_equal(outs[8], util.host(y2).view(np.uint32)), "two runs differ"
+    for M in (1, 2, 4):
+        assert np.array_equal(outs[M], outs[8][:M]), f"rows at M={M} differ from the same rows at M=8"
+
+
+def test_bf16x_product_equals_bf16_product_bitwise(lx):
+    N, K = 512, 4096
+    w_bits = util.bf16_normal((N, K), 0.02, 5)
+    # patches: a few values far below their block's largest, one row with more patches than its slots
+    w_bits[3, 100] = O.f32_to_bf16_bits(np.float32([2.0**-60]))[0]
+    w_bits[3, 1000] = O.f32_to_bf16_bits(np.float32([-(2.0**-70)]))[0]
+    w_bits[17, ::9] = O.f32_to_bf16_bits(np.float32([2.0**-90]))[0]
+    dw16 = util.DeviceWeight(util.make_weight(w_bits, O.W_BF16))
+    dwx = util.DeviceWeight(util.make_weight(w_bits, O.W_BF16X))
+    x_dev = util.dev(util.bf16_normal((8, K), 1.0, 6))
+    for M in (1, 8):
+        ya = torch.full((M, N), float("nan"), device="cuda")
+        yb = torch.full((M, N), float("nan"), device="cuda")
+        assert util.gemv(lx, x_dev, abi.BF16, K, dw16, ya, abi.F32, N, M, N, K) == 0
+        assert util.gemv(lx, x_dev, abi.BF16, K, dwx, yb, abi.F32, N, M, N, K) == 0
+        util.check_status(lx)
+        assert np.array_equal(util.host(ya).view(np.uint32), util.host(yb).view(np.uint32))
+
+
+@pytest.mark.parametrize("fmt", FORMATS, ids=lambda f: NAMES[f])
+def test_scalar_path_agrees(lx, fmt, monkeypatch):
+    """The scalar kernel (unaligned / odd shapes) and the streaming kernel are two implementations of one contract."""
+    M, N, K = 3, 96, 1024
+    got_a, want, y0 = run(lx, fmt, M, N, K, seed=21)
+    monkeypatch.setenv("LX_B200_FORCE_SCALAR", "1")
+    got_b, _, _ = run(lx, fmt, M, N, K, seed=21)
+    check(got_b, want, y0, N, True, f"{NAMES[fmt]} scalar")
+    scale = float(np.abs(want).max())
+    assert float(np.abs(got_a[:, :N] - got_b[:, :N]).max()) <= 1e-4 * scale
+
+
+def test_argument_errors(lx):
+    N, K = 64, 256
+    dw = util.DeviceWeight(util.make_weight(util.bf16_normal((N, K), 0.02, 1), O.W_INT8))
+    x = util.dev(util.bf16_normal((8, K), 1.0, 2))
+    y = torch.zeros((8, N), device="cuda")
+    assert util.gemv(lx, x, abi.BF16, K, dw, y, abi.F32, N, 0, N, K) == 0           # nothing to do
+    assert util.gemv(lx, x, abi.BF16, K, dw, y, abi.F32, N, 9, N, K) == abi.ERR_INVALID   # GEMV is M <= 8
+    assert util.gemv(lx, x, abi.BF16, K - 1, dw, y, abi.F32, N, 1, N, K) == abi.ERR_INVALID  # ld_x < K
+    assert util.gemv(lx, x, abi.BF16, K, dw, y, abi.F32, N - 1, 1, N, K) == abi.ERR_INVALID  # ld_y < N
+    no_scale = abi.make_weight(O.W_INT8, dw.data, None)
+    import ctypes
+    assert lx.lx_gemv_w(abi.ptr(x), abi.BF16, K, ctypes.byref(no_scale), None, abi.BF16, abi.ptr(y), abi.F32, N, 1, N, K,
+                        1.0, 0.0, util.stream_ptr()) == abi.ERR_INVALID
+    ws = torch.empty(1 << 20, dtype=torch.uint8, device="cuda")
+    assert util.gemv(lx, x, abi.BF16, K, dw, y, abi.F32, N, 8, N, K, fn="lx_gemm_w", math=abi.MATH_FP4,
+                     workspace=ws) == abi.ERR_NOT_SUPPORTED
