@@ -113,19 +113,23 @@ bool stream_ok(const lx_weight& w, int K) {
 template <int F>
 int launch_dense_format(const StreamParams& P, cudaStream_t stream) {
   const int cols = columns_needed(std::min(P.M, 64), P.x_dtype);
-  constexpr int U8 = F == LX_W_NVFP4 ? 1 : 2;
+  constexpr int UW = F == LX_W_NVFP4 ? 1 : 2;  // NVFP4 holds four times the values per byte: shorter stages
   if (cols <= 8) {
     // decode GEMV: the variant the table holds for this shape (keyed on M's power-of-two bucket), else variant 0
     switch (lx_tune_get(gemv_kernel_name(F), P.M, P.N, P.K)) {
-      case 1: return launch_stream<F, 1, 1, 1, 1, 4, kDense>(P, dim3((P.N + 15) / 16), stream);
-      case 2: return launch_stream<F, 1, 2, 1, 4, 3, kDense>(P, dim3((P.N + 31) / 32), stream);
-      case 3: return launch_stream<F, 1, 4, 1, 4, 3, kDense>(P, dim3((P.N + 63) / 64), stream);
-      default: return launch_stream<F, 1, 2, 1, 2, 4, kDense>(P, dim3((P.N + 31) / 32), stream);
+      case 1: return launch_stream<F, 1, 1, 1, 1, 4, kDense>(P, dim3((P.N + 15) / 16), stream, P.N);
+      case 2: return launch_stream<F, 1, 2, 1, 4, 3, kDense>(P, dim3((P.N + 31) / 32), stream, P.N);
+      case 3: return launch_stream<F, 1, 4, 1, 4, 3, kDense>(P, dim3((P.N + 63) / 64), stream, P.N);
+      case 4: return launch_stream<F, 1, 2, 1, 2, 6, kDense>(P, dim3((P.N + 31) / 32), stream, P.N);
+      case 5: return launch_stream<F, 1, 1, 1, 1, 8, kDense>(P, dim3((P.N + 15) / 16), stream, P.N);
+      case 6: return launch_stream<F, 1, 4, 1, 2, 4, kDense>(P, dim3((P.N + 63) / 64), stream, P.N);
+      case 7: return launch_stream<F, 1, 1, 1, 2, 6, kDense>(P, dim3((P.N + 15) / 16), stream, P.N);
+      default: return launch_stream<F, 1, 2, 1, 2, 4, kDense>(P, dim3((P.N + 31) / 32), stream, P.N);
     }
   }
-  if (cols <= 16) return launch_stream<F, 1, 2, 2, 2, 4, kDense>(P, dim3((P.N + 31) / 32), stream);
-  if (cols <= 32) return launch_stream<F, 2, 2, 4, 2, 3, kDense>(P, dim3((P.N + 63) / 64), stream);
-  return launch_stream<F, 2, 4, 8, U8, 3, kDense>(P, dim3((P.N + 127) / 128), stream);
+  if (cols <= 16) return launch_stream<F, 1, 2, 2, 2, 4, kDense>(P, dim3((P.N + 31) / 32), stream, P.N);
+  if (cols <= 32) return launch_stream<F, 2, 2, 4, UW, 3, kDense>(P, dim3((P.N + 63) / 64), stream, P.N);
+  return launch_stream<F, 2, 4, 8, UW, 2, kDense>(P, dim3((P.N + 127) / 128), stream, P.N);
 }
 
 int row_bytes_of(int type, int K) {
@@ -148,6 +152,7 @@ int dense_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, cons
   P.row_bytes = row_bytes_of(w.type, K);
   P.N = N, P.K = K;
   P.x = x, P.x_dtype = x_dtype, P.ld_x = ld_x, P.M = M;
+  P.x_vec = x_dtype == LX_BF16 && aligned(x, 16) && (M == 1 || ld_x % 8 == 0);
   P.bias = bias, P.bias_dtype = bias_dtype;
   P.y = y, P.y_dtype = y_dtype, P.ld_y = ld_y;
   P.alpha = alpha, P.beta = beta;

@@ -4,6 +4,7 @@
 #pragma once
 
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "stream.cuh"
@@ -46,11 +47,37 @@ int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, 
   return kOk;
 }
 
+// cuTensorMapEncodeTiled, fetched from the driver through the runtime (the library does not link libcuda).
+using TensorMapEncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                       const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                       CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+TensorMapEncodeFn tensor_map_encoder();
+
+// A 2-D map over `rows` rows of `row_bytes` bytes each (row pitch = row_bytes, a multiple of 16; base 16-byte aligned),
+// copied in boxes of box_rows x box_bytes. elem_bytes (1 or 4) is the unit the kernel gives x coordinates in.
+inline int make_tile_map(CUtensorMap* map, const void* base, int64_t row_bytes, int64_t rows, int box_bytes, int box_rows,
+                         int elem_bytes) {
+  TensorMapEncodeFn encode = tensor_map_encoder();
+  if (!encode) return kNotSupported;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_bytes / elem_bytes), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_bytes)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_bytes / elem_bytes), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = encode(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                            const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? kOk : kInvalid;
+}
+
+// stack_rows: rows of the whole weight the kernel may address (N, or E * N for a stack of experts).
 template <int F, int RT, int WR, int NT, int U, int S, int MODE>
-int launch_stream(const StreamParams& P, dim3 grid, cudaStream_t stream) {
+int launch_stream(StreamParams P, dim3 grid, cudaStream_t stream, int64_t stack_rows) {
+  using C = StreamCfg<F, RT, WR, NT, U, S>;
   auto kernel = stream_kernel<F, RT, WR, NT, U, S, MODE>;
   const size_t smem = stream_smem_bytes<F, RT, WR, NT, U, S>(P.K);
-  // The opt-in to more than 48 KB of dynamic shared memory is per device and per kernel; set it once per device.
+  if (smem > 226 * 1024) return kNotSupported;
+  // The opt-in to more than 48 KB of dynamic shared memory is per device and per kernel; set it once per device,
+  // with the whole of the SM's L1 given to shared memory so that as many CTAs fit as their sizes allow.
   static std::mutex mu;
   static unsigned long long done_mask = 0;  // bit per device ordinal (< 64)
   int dev = 0;
@@ -58,7 +85,9 @@ int launch_stream(const StreamParams& P, dim3 grid, cudaStream_t stream) {
   {
     std::lock_guard<std::mutex> lock(mu);
     if (!(done_mask >> (dev & 63) & 1ull)) {
-      const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
       if (e != cudaSuccess) {
         cudaGetLastError();
         return static_cast<int>(e);
@@ -66,8 +95,19 @@ int launch_stream(const StreamParams& P, dim3 grid, cudaStream_t stream) {
       done_mask |= 1ull << (dev & 63);
     }
   }
-  if (smem > 220 * 1024) return kNotSupported;
-  return launch_kernel(kernel, grid, dim3(kThreads), smem, stream, P);
+  alignas(64) CUtensorMap wmap, smap;
+  memset(&wmap, 0, sizeof(wmap));
+  memset(&smap, 0, sizeof(smap));
+  // BF16X records come as tiles when they and their data start on 16-byte boundaries; every other format always does
+  // (the callers check stream_ok).
+  P.tiled = !C::kX16 || (aligned(P.w, 16) && P.row_bytes % 16 == 0 && x16::header_bytes(P.K) % 16 == 0);
+  if (P.tiled) {
+    const int box_rows = MODE == kGateUp ? C::R / 2 : C::R;
+    if (int e = make_tile_map(&wmap, P.w, P.row_bytes, stack_rows, C::SEG, box_rows, 4)) return e;
+    if constexpr (F == LX_W_NVFP4)
+      if (int e = make_tile_map(&smap, P.scale, P.K / 16, stack_rows, C::SCALE_SEG, box_rows, 1)) return e;
+  }
+  return launch_kernel(kernel, grid, dim3(kThreads), smem, stream, wmap, smap, P);
 }
 
 struct ActLayout {

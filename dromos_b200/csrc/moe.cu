@@ -219,20 +219,21 @@ bool stack_streams(const lx_weight& w, int K) {
 }
 
 template <int MODE>
-int launch_expert_stage(const StreamParams& P, int type, dim3 grid, cudaStream_t s) {
+int launch_expert_stage(const StreamParams& P, int type, dim3 grid, cudaStream_t s, int64_t stack_rows) {
   switch (type) {
-    case LX_W_BF16: return launch_stream<LX_W_BF16, 1, 2, 1, 2, 4, MODE>(P, grid, s);
-    case LX_W_INT8: return launch_stream<LX_W_INT8, 1, 2, 1, 2, 4, MODE>(P, grid, s);
-    case LX_W_FP8: return launch_stream<LX_W_FP8, 1, 2, 1, 2, 4, MODE>(P, grid, s);
-    case LX_W_NVFP4: return launch_stream<LX_W_NVFP4, 1, 2, 1, 2, 4, MODE>(P, grid, s);
-    case LX_W_BF16X: return launch_stream<LX_W_BF16X, 1, 2, 1, 2, 4, MODE>(P, grid, s);
+    case LX_W_BF16: return launch_stream<LX_W_BF16, 1, 2, 1, 2, 4, MODE>(P, grid, s, stack_rows);
+    case LX_W_INT8: return launch_stream<LX_W_INT8, 1, 2, 1, 2, 4, MODE>(P, grid, s, stack_rows);
+    case LX_W_FP8: return launch_stream<LX_W_FP8, 1, 2, 1, 2, 4, MODE>(P, grid, s, stack_rows);
+    case LX_W_NVFP4: return launch_stream<LX_W_NVFP4, 1, 2, 1, 2, 4, MODE>(P, grid, s, stack_rows);
+    case LX_W_BF16X: return launch_stream<LX_W_BF16X, 1, 2, 1, 2, 4, MODE>(P, grid, s, stack_rows);
   }
   return kInvalid;
 }
 
 // Stages 2-4 on grouping tables already in the workspace. groups = grid extent over expert groups.
 int run_experts(const void* latent, const float* weights, const lx_weight& gate_up, const lx_weight& down, float* out,
-                uint8_t* ws, const Layout& l, bool indirect, int groups, int T, int L, int I, int top_k, cudaStream_t s) {
+                uint8_t* ws, const Layout& l, bool indirect, int groups, int experts, int T, int L, int I, int top_k,
+                cudaStream_t s) {
   StreamParams g{};
   g.w = static_cast<const uint8_t*>(gate_up.data);
   g.scale = static_cast<const uint8_t*>(gate_up.scale);
@@ -241,6 +242,7 @@ int run_experts(const void* latent, const float* weights, const lx_weight& gate_
   g.row_bytes = row_bytes_of(gate_up.type, L);
   g.N = 2 * I, g.K = L;
   g.x = latent, g.x_dtype = LX_BF16, g.ld_x = L, g.M = T;
+  g.x_vec = aligned(latent, 16) && L % 8 == 0;
   g.offsets = reinterpret_cast<const int32_t*>(ws + l.offsets);
   g.group_expert = indirect ? reinterpret_cast<const int32_t*>(ws + l.group_expert) : nullptr;
   g.pairs = reinterpret_cast<const int32_t*>(ws + l.pairs);
@@ -248,7 +250,7 @@ int run_experts(const void* latent, const float* weights, const lx_weight& gate_
   g.top_k = top_k, g.I = I;
   g.moe_out = ws + l.mid;
   g.status = status_word();
-  if (int e = launch_expert_stage<kGateUp>(g, gate_up.type, dim3((I + 15) / 16, groups), s)) return e;
+  if (int e = launch_expert_stage<kGateUp>(g, gate_up.type, dim3((I + 15) / 16, groups), s, static_cast<int64_t>(experts) * 2 * I)) return e;
 
   StreamParams d = g;
   d.w = static_cast<const uint8_t*>(down.data);
@@ -258,8 +260,9 @@ int run_experts(const void* latent, const float* weights, const lx_weight& gate_
   d.row_bytes = row_bytes_of(down.type, I);
   d.N = L, d.K = I;
   d.x = ws + l.mid, d.ld_x = I;
+  d.x_vec = I % 8 == 0;
   d.moe_out = ws + l.rows;
-  if (int e = launch_expert_stage<kDown>(d, down.type, dim3((L + 31) / 32, groups), s)) return e;
+  if (int e = launch_expert_stage<kDown>(d, down.type, dim3((L + 31) / 32, groups), s, static_cast<int64_t>(experts) * L)) return e;
 
   const int64_t n = static_cast<int64_t>(T) * L;
   return launch_kernel(ordered_sum_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, s,
@@ -305,5 +308,5 @@ extern "C" int lx_moe_experts_grouped(const void* latent, const int32_t* ids, co
   if (int e = launch_kernel(group_kernel, dim3(1), dim3(1024), 0, s, ids, P, E, reinterpret_cast<int32_t*>(ws + l.offsets),
                             reinterpret_cast<int32_t*>(ws + l.pairs)))
     return e;
-  return run_experts(latent, weights, *gate_up, *down, out, ws, l, false, E, T, L, I, top_k, s);
+  return run_experts(latent, weights, *gate_up, *down, out, ws, l, false, E, E, T, L, I, top_k, s);
 }

@@ -9,7 +9,7 @@
 #include <tuple>
 #include <vector>
 
-#include "common.cuh"
+#include "launch.cuh"
 #include "variants.h"
 
 namespace b200 {
@@ -33,6 +33,20 @@ int* status_word() {
     words[dev] = p;
   }
   return words[dev];
+}
+
+TensorMapEncodeFn tensor_map_encoder() {
+  static TensorMapEncodeFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      p = nullptr;
+    }
+    return reinterpret_cast<TensorMapEncodeFn>(p);
+  }();
+  return fn;
 }
 
 namespace {

@@ -20,6 +20,7 @@
 //   * Every wait is bounded (common.cuh mbar_wait): a stage that never arrives ends the kernel with a status code.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_fp4.h>
 
 #include "common.cuh"
@@ -43,6 +44,7 @@ struct StreamParams {
   // the activations
   const void* x;
   int x_dtype, ld_x, M;
+  int x_vec;                  // bf16 activation rows all start on 16-byte boundaries
   // dense epilogue
   const void* bias;
   int bias_dtype;
@@ -57,6 +59,7 @@ struct StreamParams {
   int top_k, I;
   void* moe_out;           // gate_up: bf16 [P, I] in grouped order; down: f32 [P, L] by pair index
   int* status;
+  int tiled;               // the weight rows come as 2-D tile copies through the tensor maps (else row by row)
 };
 
 template <int F>
@@ -109,16 +112,15 @@ struct StreamCfg {
   static constexpr int KSTAGE = STEPS * kStepValues;    // values of K in a stage
   static constexpr bool kX16 = F == LX_W_BF16X;
   static constexpr int SEG = kX16 ? (KSTAGE / 128) * 192 : STEPS * 64;  // weight bytes per row per stage
-  // Row pitch in the stage. 16-byte lane loads of two rows per quarter-warp want pitch = 64 mod 128; the 8-byte
-  // loads of BF16X (four rows per half-warp) want 32 mod 128, after 16 bytes of slack for rows that start 8 bytes
-  // off a 16-byte boundary.
-  static constexpr int PITCH = kX16 ? ((SEG + 16 + 127) / 128 * 128 + 32) : SEG + 64;
+  // Row pitch in the stage: a tile copy lands its rows back to back (pitch SEG). BF16X records that are not
+  // 16-byte aligned come row by row instead, each with 16 bytes of slack for the 8 bytes it may start late.
+  static constexpr int PITCH_ROWWISE = SEG + 16;
   static constexpr int SCALE_SEG = F == LX_W_NVFP4 ? KSTAGE / 16 : 0;
-  static constexpr int SCALE_PITCH = F == LX_W_NVFP4 ? SCALE_SEG + 16 : 0;
-  static constexpr int STAGE_BYTES = R * (PITCH + SCALE_PITCH);
-  static constexpr int XSTAGE_BYTES = STEPS * NT * JJ2 * 512;  // activation fragments for one stage
-  static constexpr int XG = (16384 / XSTAGE_BYTES) > 0 ? (16384 / XSTAGE_BYTES) : 1;  // stages per activation chunk
-  static constexpr int XBYTES = XG * XSTAGE_BYTES;
+  static constexpr int STAGE_BYTES = (R * ((kX16 ? PITCH_ROWWISE : SEG) + SCALE_SEG) + 127) / 128 * 128;
+  static constexpr int XSTAGE_BYTES = STEPS * NT * JJ2 * 512;  // activation fragments for one stage, all 8 columns
+  // Activations are staged into two halves (one chunk of K each); a half holds at least one stage's fragments.
+  static constexpr int XHALF = XSTAGE_BYTES > 16384 ? XSTAGE_BYTES : 16384;
+  static constexpr int XBYTES = 2 * XHALF;
   static constexpr int COLS = 8 * NT;
   static constexpr int RED_BYTES = WK * R * COLS * 4;
   static constexpr int RING_BYTES = S * STAGE_BYTES;
@@ -243,13 +245,14 @@ struct PatchCursor {
 template <int F, int RT, int WR, int NT, int U, int S>
 size_t stream_smem_bytes(int K) {
   using C = StreamCfg<F, RT, WR, NT, U, S>;
-  size_t b = C::MAIN_BYTES + C::XBYTES + 2 * S * 8 + 64 * 8 /* row scales */ + 128;
+  size_t b = C::MAIN_BYTES + C::XBYTES + 2 * S * 8 + 64 * (8 + 4 + 8) /* row pointers, maxima, chunk scales */ + 128;
   if (C::kX16) b += static_cast<size_t>(C::R) * ((x16::header_bytes(K) + 15) / 16 * 16);
   return b;
 }
 
 template <int F, int RT, int WR, int NT, int U, int S, int MODE>
-__global__ void __launch_bounds__(kThreads, 1) stream_kernel(const StreamParams P) {
+__global__ void __launch_bounds__(kThreads, 1)
+    stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap, const StreamParams P) {
   using C = StreamCfg<F, RT, WR, NT, U, S>;
   constexpr bool kHalf = Fmt<F>::kHalf;
   constexpr int R = C::R, WK = C::WK, COLS = C::COLS;
@@ -258,9 +261,10 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const StreamParams 
   uint8_t* ring = smem;                                      // S stages, then the reduction buffer
   uint8_t* xs = smem + C::MAIN_BYTES;                        // activation fragments of the current chunk
   uint64_t* bars = reinterpret_cast<uint64_t*>(xs + C::XBYTES);  // full[S], empty[S]
-  float* xscale = reinterpret_cast<float*>(bars + 2 * S);    // [64] power-of-two scale of each activation column
-  float* xinv = xscale + 64;                                 // [64] its inverse
-  uint8_t* hdr = reinterpret_cast<uint8_t*>(xinv + 64);      // BF16X: R headers
+  const uint8_t** xrow = reinterpret_cast<const uint8_t**>(bars + 2 * S);  // [64] this pass's activation rows
+  uint32_t* runmax = reinterpret_cast<uint32_t*>(xrow + 64);  // [64] bits of each row's largest magnitude so far
+  float* bufscale = reinterpret_cast<float*>(runmax + 64);    // [2][64] the scale each half's columns were stored in
+  uint8_t* hdr = reinterpret_cast<uint8_t*>(bufscale + 128);  // BF16X: R headers
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int K = P.K;
@@ -330,69 +334,67 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const StreamParams 
   if (warp == kConsumerWarps) {
     pdl_trigger();
     const int hb = C::kX16 ? x16::header_bytes(K) : 0;
+    // first row of this CTA in the (stacked) weight, as the tile copies address it
+    const int64_t stack_row0 = static_cast<int64_t>(e) * P.N + row0;
+    if (P.tiled && lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
+      if constexpr (F == LX_W_NVFP4) asm volatile("prefetch.tensormap [%0];" ::"l"(&smap) : "memory");
+    }
     for (int gs = 0; gs < total_stages; ++gs) {
       const int s = gs % n_stages, slot = gs % S;
       if (gs >= S) mbar_wait(empty_bar(slot), ((gs / S) - 1) & 1, P.status, kStatusEmptyWait);
       const uint32_t stage = smem_u32(ring) + static_cast<uint32_t>(slot) * C::STAGE_BYTES;
-      uint32_t bytes, sbytes = 0;
-      if constexpr (C::kX16) {
-        const int b0 = s * (C::KSTAGE / 128);
-        const int nb = min(C::KSTAGE / 128, x16::blocks(K) - b0);
-        bytes = nb * 192;
-      } else {
-        const int64_t rowb = P.row_bytes;
-        bytes = static_cast<uint32_t>(min(static_cast<int64_t>(C::SEG), rowb - static_cast<int64_t>(s) * C::SEG));
-        if constexpr (F == LX_W_NVFP4) sbytes = bytes / 8;
-      }
-      if constexpr (!C::kX16) {
-        if (lane == 0) mbar_arrive_expect_tx(full_bar(slot), R * (bytes + sbytes));
-        __syncwarp();
-        for (int r = lane; r < R; r += 32) {
-          const int n = matrix_row(r);
-          bulk_g2s(stage + r * C::PITCH, wbase + n * P.row_bytes + static_cast<int64_t>(s) * C::SEG, bytes,
-                   full_bar(slot));
-          if constexpr (F == LX_W_NVFP4)
-            bulk_g2s(stage + R * C::PITCH + r * C::SCALE_PITCH,
-                     sbase + static_cast<int64_t>(n) * (K / 16) + static_cast<int64_t>(s) * C::SCALE_SEG, sbytes,
-                     full_bar(slot));
+      if (P.tiled) {
+        // One tile copy per stage: R rows x SEG bytes (rows and bytes past the matrix read as zero). gate_up takes
+        // two half-height tiles, the gate rows and the up rows.
+        if (lane == 0) {
+          mbar_arrive_expect_tx(full_bar(slot), R * (C::SEG + C::SCALE_SEG));
+          const int x0 = (hb + s * C::SEG) / 4;  // the maps count the row in 4-byte elements
+          if constexpr (MODE == kGateUp) {
+            tile_g2s(stage, &wmap, x0, static_cast<int>(stack_row0), full_bar(slot));
+            tile_g2s(stage + (R / 2) * C::SEG, &wmap, x0, static_cast<int>(stack_row0 + P.I), full_bar(slot));
+          } else {
+            tile_g2s(stage, &wmap, x0, static_cast<int>(stack_row0), full_bar(slot));
+          }
+          if constexpr (F == LX_W_NVFP4) {
+            const uint32_t sdst = stage + R * C::SEG;
+            if constexpr (MODE == kGateUp) {
+              tile_g2s(sdst, &smap, s * C::SCALE_SEG, static_cast<int>(stack_row0), full_bar(slot));
+              tile_g2s(sdst + (R / 2) * C::SCALE_SEG, &smap, s * C::SCALE_SEG, static_cast<int>(stack_row0 + P.I), full_bar(slot));
+            } else {
+              tile_g2s(sdst, &smap, s * C::SCALE_SEG, static_cast<int>(stack_row0), full_bar(slot));
+            }
+          }
         }
-      } else {
-        // Records are 8-byte aligned: copy from the 16-byte boundary at or below the data, and if the rounded-up end
-        // would pass the end of the whole encoding's rows, bring the last 8 bytes with an ordinary load instead.
+        continue;
+      }
+      if constexpr (C::kX16) {
+        // Row by row. Records are 8-byte aligned: copy from the 16-byte boundary at or below the data, and if the
+        // rounded-up end would pass the end of the rows, bring the last 8 bytes with an ordinary load instead.
+        const int b0 = s * (C::KSTAGE / 128);
+        const uint32_t bytes = min(C::KSTAGE / 128, x16::blocks(K) - b0) * 192;
+        const uint8_t* end_all = wbase + static_cast<int64_t>(P.N) * P.row_bytes;
         uint32_t tx = 0;
         for (int r = lane; r < R; r += 32) {
-          const int n = matrix_row(r);
-          const uint8_t* src = wbase + n * P.row_bytes + hb + static_cast<int64_t>(s) * C::SEG;
+          const uint8_t* src = wbase + matrix_row(r) * P.row_bytes + hb + static_cast<int64_t>(s) * C::SEG;
           const uint32_t sh = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(src) & 15);
           uint32_t len = (bytes + sh + 15) & ~15u;
-          const uint8_t* end_all = wbase + static_cast<int64_t>(P.N) * P.row_bytes;
-          if (src - sh + len > end_all) len -= 16;  // the tail (8 bytes) is fetched below
+          if (src - sh + len > end_all) {
+            len -= 16;
+            *reinterpret_cast<uint64_t*>(ring + static_cast<size_t>(slot) * C::STAGE_BYTES + r * C::PITCH_ROWWISE + len) =
+                *reinterpret_cast<const uint64_t*>(src - sh + len);
+          }
           tx += len;
         }
         tx = __reduce_add_sync(0xffffffffu, tx);
-        for (int r = lane; r < R; r += 32) {
-          const int n = matrix_row(r);
-          const uint8_t* src = wbase + n * P.row_bytes + hb + static_cast<int64_t>(s) * C::SEG;
-          const uint32_t sh = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(src) & 15);
-          const uint32_t len = (bytes + sh + 15) & ~15u;
-          const uint8_t* end_all = wbase + static_cast<int64_t>(P.N) * P.row_bytes;
-          if (src - sh + len > end_all) {
-            const uint64_t tail = *reinterpret_cast<const uint64_t*>(src - sh + len - 16);
-            *reinterpret_cast<uint64_t*>(ring + static_cast<size_t>(slot) * C::STAGE_BYTES + r * C::PITCH + len - 16) =
-                tail;
-          }
-        }
-        __syncwarp();
         if (lane == 0) mbar_arrive_expect_tx(full_bar(slot), tx);
         __syncwarp();
         for (int r = lane; r < R; r += 32) {
-          const int n = matrix_row(r);
-          const uint8_t* src = wbase + n * P.row_bytes + hb + static_cast<int64_t>(s) * C::SEG;
+          const uint8_t* src = wbase + matrix_row(r) * P.row_bytes + hb + static_cast<int64_t>(s) * C::SEG;
           const uint32_t sh = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(src) & 15);
           uint32_t len = (bytes + sh + 15) & ~15u;
-          const uint8_t* end_all = wbase + static_cast<int64_t>(P.N) * P.row_bytes;
           if (src - sh + len > end_all) len -= 16;
-          if (len) bulk_g2s(stage + r * C::PITCH, src - sh, len, full_bar(slot));
+          if (len) bulk_g2s(stage + r * C::PITCH_ROWWISE, src - sh, len, full_bar(slot));
         }
       }
     }
@@ -422,40 +424,30 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const StreamParams 
   float acc[RT][NT][4];
   const bool x_bf16 = P.x_dtype == LX_BF16;
   const int hdr_slots = C::kX16 ? x16::patch_slots(K) : 0;
+  const int x_elem = x_bf16 ? 2 : 4;
+  const int pitch = P.tiled ? C::SEG : C::PITCH_ROWWISE;  // BF16X only (the other formats always come as tiles)
 
   for (int cc = 0; cc < col_chunks; ++cc) {
     const int col0 = cc * cap;
-    const int n_real = min(cap, n_cols_total - col0);  // activation rows of this chunk
+    const int n_real = min(cap, n_cols_total - col0);  // activation rows of this pass
     const int n_cols = split ? 2 * n_real : n_real;    // columns they occupy
-    // activation row (pointer) of real row j of this chunk
-    auto x_row = [&](int j) -> const uint8_t* {
+    // Fragment buffers hold 8-column tiles; a single tile is stored compactly (only its live columns).
+    const int ncp = NT == 1 ? n_cols : 8;
+    const int xs_stage = 2 * C::KSTAGE * NT * ncp;  // bytes of activations per weight stage
+    // Stages per activation chunk: as many as fit one half of the fragment buffer.
+    const int xg = max(1, C::XHALF / xs_stage);
+    const int n_xchunks = (n_stages + xg - 1) / xg;
+
+    named_bar_sync(1, kConsumerThreads);  // the previous pass's epilogue is done with the shared tables
+    // activation row pointers of this pass's rows, and the running |max| of each
+    for (int j = tid; j < n_real; j += kConsumerThreads) {
       int64_t row;
       if constexpr (MODE == kDense) row = col0 + j;
       else if constexpr (MODE == kGateUp) row = P.pairs[col_base0 + col0 + j] / P.top_k;
       else row = col_base0 + col0 + j;
-      return static_cast<const uint8_t*>(P.x) + row * P.ld_x * (x_bf16 ? 2 : 4);
-    };
-
-    named_bar_sync(1, kConsumerThreads);  // the previous chunk's reduction buffer and scales are done with
-    // ---- per-row power-of-two scales for the f16 path ----
-    if constexpr (kHalf) {
-      for (int j = warp; j < n_real; j += kConsumerWarps) {
-        const uint8_t* xr = x_row(j);
-        float m = 0.0f;
-        for (int k = lane; k < K; k += 32)
-          m = fmaxf(m, fabsf(x_bf16 ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(xr)[k])
-                                    : reinterpret_cast<const float*>(xr)[k]));
-        m = warp_max(m);
-        if (lane == 0) {
-          int ex = static_cast<int>((__float_as_uint(m) >> 23) & 0xffu);
-          ex = m > 0.0f ? min(max(ex, 30), 240) : 141;  // 2^(141 - ex) brings the row's largest into [2^14, 2^15)
-          xscale[j] = __uint_as_float(static_cast<uint32_t>(268 - ex) << 23);
-          xinv[j] = __uint_as_float(static_cast<uint32_t>(ex - 14) << 23);
-        }
-      }
+      xrow[j] = static_cast<const uint8_t*>(P.x) + row * P.ld_x * x_elem;
+      runmax[j] = 0u;
     }
-    // zero the fragment buffer once per chunk of columns: unused columns and the K tail stay zero
-    for (int i = tid; i < C::XBYTES / 16; i += kConsumerThreads) reinterpret_cast<uint4*>(xs)[i] = make_uint4(0, 0, 0, 0);
 #pragma unroll
     for (int a = 0; a < RT; ++a)
 #pragma unroll
@@ -464,7 +456,7 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const StreamParams 
         for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.0f;
 
     PatchCursor cur[RT][2];
-    uint32_t x16_shift[RT][2];  // BF16X: how far the row's data sits past the 16-byte boundary its copies start at
+    uint32_t x16_shift[RT][2];  // BF16X row by row: how far the row's data sits past the 16-byte boundary of its copy
     named_bar_sync(1, kConsumerThreads);
     if constexpr (C::kX16) {
 #pragma unroll
@@ -474,80 +466,151 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const StreamParams 
           const int r = (wr * RT + a) * 16 + g + 8 * h;
           const uint8_t* rec = wbase + matrix_row(r) * P.row_bytes;
           cur[a][h].start(reinterpret_cast<const uint32_t*>(hdr + r * hpitch), hdr_slots, rec);
-          x16_shift[a][h] = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(rec + x16::header_bytes(K)) & 15);
+          x16_shift[a][h] = P.tiled ? 0u : static_cast<uint32_t>(reinterpret_cast<uintptr_t>(rec + x16::header_bytes(K)) & 15);
         }
     }
 
-    for (int s = 0; s < n_stages; ++s) {
-      const int gs = cc * n_stages + s, slot = gs % S;
-      // ---- stage the activations of the next XG stages in fragment order ----
-      if (s % C::XG == 0) {
-        if (s) named_bar_sync(1, kConsumerThreads);
-        const int kc0 = s * C::KSTAGE;
-        constexpr int kGroups = C::XG * C::KSTAGE / 8;  // 8-value groups per column in a chunk
-        for (int i = tid; i < n_cols * kGroups; i += kConsumerThreads) {
-          const int col = i / kGroups, kg = i % kGroups;
-          const int k = kc0 + 8 * kg;
-          if (k >= K) continue;
-          const int j = split ? (col >> 1) : col;  // real row; with split, columns 2j (high) and 2j + 1 (low)
-          const uint8_t* xr = x_row(j);
-          float v[8];
-          if (x_bf16) {
-            uint4 raw;
-            if ((reinterpret_cast<uintptr_t>(xr + 2 * k) & 15) == 0 && k + 8 <= K) {
-              raw = *reinterpret_cast<const uint4*>(xr + 2 * k);
-            } else {
-              uint16_t h[8];
+    // ---- activation staging --------------------------------------------------------------------------------
+    // Chunk c covers stages [c * xg, (c + 1) * xg) and goes into half c & 1 of the fragment buffer. Its 8-value
+    // groups are the items; item i is column i / groups, group i % groups, so consecutive threads read consecutive
+    // 16 bytes of one activation row. A thread owns items tid, tid + 256, ... (at most kItems: a half holds 256 *
+    // kItems groups). bf16 rows that are 16-byte aligned are prefetched: a chunk's loads are issued one chunk ahead
+    // and sit in registers while the chunk before it is multiplied.
+    constexpr int kItems = C::XHALF / 16 / kConsumerThreads;
+    const bool x_fast = x_bf16 && P.x_vec;
+    uint4 pre[kItems];
+    auto chunk_groups = [&](int c) { return (min(K, (c + 1) * xg * C::KSTAGE) - c * xg * C::KSTAGE) / 8; };
+    auto prefetch = [&](int c) {
+      const int groups = chunk_groups(c), items = n_cols * groups, k0 = c * xg * C::KSTAGE;
 #pragma unroll
-              for (int q = 0; q < 8; ++q) h[q] = k + q < K ? reinterpret_cast<const uint16_t*>(xr)[k + q] : 0;
-              raw = make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16));
-            }
-            const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
+      for (int q = 0; q < kItems; ++q) {
+        const int i = tid + q * kConsumerThreads;
+        if (i < items) pre[q] = *reinterpret_cast<const uint4*>(xrow[i / groups] + 2 * (k0 + 8 * (i % groups)));
+      }
+    };
+    // The eight values of item i of chunk c, widened to f32.
+    auto values = [&](int c, int q, int i, int groups, float (&v)[8]) {
+      if (x_fast) {
+        const uint32_t w4[4] = {pre[q].x, pre[q].y, pre[q].z, pre[q].w};
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              v[2 * q] = __uint_as_float(w4[q] << 16);
-              v[2 * q + 1] = __uint_as_float(w4[q] & 0xffff0000u);
-            }
-          } else {
+        for (int z = 0; z < 4; ++z) {
+          v[2 * z] = __uint_as_float(w4[z] << 16);
+          v[2 * z + 1] = __uint_as_float(w4[z] & 0xffff0000u);
+        }
+      } else {
+        const int col = i / groups, k = c * xg * C::KSTAGE + 8 * (i % groups);
+        const uint8_t* xr = xrow[split ? col >> 1 : col];
 #pragma unroll
-            for (int q = 0; q < 8; ++q) v[q] = k + q < K ? reinterpret_cast<const float*>(xr)[k + q] : 0.0f;
+        for (int z = 0; z < 8; ++z)
+          v[z] = x_bf16 ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(xr)[k + z]) : reinterpret_cast<const float*>(xr)[k + z];
+      }
+    };
+    // Power-of-two scale that brings a row whose largest magnitude has the bits `m` into [2^14, 2^15).
+    auto scale_for = [](uint32_t m) -> float {
+      int ex = static_cast<int>((m >> 23) & 0xffu);
+      ex = m ? min(max(ex, 30), 240) : 141;
+      return __uint_as_float(static_cast<uint32_t>(268 - ex) << 23);
+    };
+    // Converts the chunk (from the prefetched registers, or from memory) and stores it in fragment order.
+    auto commit = [&](int c) {
+      const int groups = chunk_groups(c), items = n_cols * groups, buf = c & 1;
+      if constexpr (kHalf) {
+#pragma unroll
+        for (int q = 0; q < kItems; ++q) {
+          const int i = tid + q * kConsumerThreads;
+          if (i < items) {
+            float v[8], m = 0.0f;
+            values(c, q, i, groups, v);
+#pragma unroll
+            for (int z = 0; z < 8; ++z) m = fmaxf(m, fabsf(v[z]));
+            const int col = i / groups;
+            atomicMax(&runmax[split ? col >> 1 : col], __float_as_uint(m));
           }
-          uint32_t out[4];
-          if constexpr (kHalf) {
-            const float sc = xscale[j];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              float a0 = v[2 * q] * sc, a1 = v[2 * q + 1] * sc;
-              __half h0 = __float2half_rn(a0), h1 = __float2half_rn(a1);
-              if (split && (col & 1)) {
-                h0 = __float2half_rn(a0 - __half2float(h0));
-                h1 = __float2half_rn(a1 - __half2float(h1));
-              }
-              out[q] = static_cast<uint32_t>(__half_as_ushort(h0)) | (static_cast<uint32_t>(__half_as_ushort(h1)) << 16);
-            }
-          } else {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint32_t b0 = f32_to_bf16_bits(v[2 * q]), b1 = f32_to_bf16_bits(v[2 * q + 1]);
-              if (split && (col & 1)) {
-                b0 = f32_to_bf16_bits(v[2 * q] - bf16_bits_to_f32(b0));
-                b1 = f32_to_bf16_bits(v[2 * q + 1] - bf16_bits_to_f32(b1));
-              }
-              out[q] = b0 | (b1 << 16);
-            }
-          }
-          const int kin = 8 * kg;  // offset inside the chunk
-          const int step = kin / C::kStepValues, within = kin % C::kStepValues;
-          const int tt = within / C::VPT, jj2 = (within % C::VPT) / 8;
-          const int off = ((step * NT + (col >> 3)) * C::JJ2 + jj2) * 512 + ((col & 7) * 4 + tt) * 16;
-          *reinterpret_cast<uint4*>(xs + off) = make_uint4(out[0], out[1], out[2], out[3]);
         }
         named_bar_sync(1, kConsumerThreads);
+      }
+#pragma unroll
+      for (int q = 0; q < kItems; ++q) {
+        const int i = tid + q * kConsumerThreads;
+        if (i >= items) continue;
+        float v[8];
+        values(c, q, i, groups, v);
+        const int col = i / groups;
+        uint32_t out[4];
+        if constexpr (kHalf) {
+          const float sc = scale_for(runmax[split ? col >> 1 : col]);
+#pragma unroll
+          for (int z = 0; z < 4; ++z) {
+            const float a0 = v[2 * z] * sc, a1 = v[2 * z + 1] * sc;
+            __half h0 = __float2half_rn(a0), h1 = __float2half_rn(a1);
+            if (split && (col & 1)) {
+              h0 = __float2half_rn(a0 - __half2float(h0));
+              h1 = __float2half_rn(a1 - __half2float(h1));
+            }
+            out[z] = static_cast<uint32_t>(__half_as_ushort(h0)) | (static_cast<uint32_t>(__half_as_ushort(h1)) << 16);
+          }
+          if (i % groups == 0) bufscale[buf * 64 + col] = sc;
+        } else if (x_fast) {
+          out[0] = pre[q].x, out[1] = pre[q].y, out[2] = pre[q].z, out[3] = pre[q].w;
+        } else {
+#pragma unroll
+          for (int z = 0; z < 4; ++z) {
+            uint32_t b0 = f32_to_bf16_bits(v[2 * z]), b1 = f32_to_bf16_bits(v[2 * z + 1]);
+            if (split && (col & 1)) {
+              b0 = f32_to_bf16_bits(v[2 * z] - bf16_bits_to_f32(b0));
+              b1 = f32_to_bf16_bits(v[2 * z + 1] - bf16_bits_to_f32(b1));
+            }
+            out[z] = b0 | (b1 << 16);
+          }
+        }
+        const int kin = 8 * (i % groups);
+        const int step = kin / C::kStepValues, within = kin % C::kStepValues;
+        const int tt = within / C::VPT, jj2 = (within % C::VPT) / 8;
+        const int unit = (((step * C::JJ2 + jj2) * NT + (NT == 1 ? 0 : col >> 3)) * 4 + tt) * ncp + (NT == 1 ? col : col & 7);
+        *reinterpret_cast<uint4*>(xs + buf * C::XHALF + unit * 16) = make_uint4(out[0], out[1], out[2], out[3]);
+      }
+      named_bar_sync(1, kConsumerThreads);
+    };
+
+    float cur_scale[NT][2];  // the scale the accumulators of this lane's two columns of each tile are in
+#pragma unroll
+    for (int b = 0; b < NT; ++b) cur_scale[b][0] = cur_scale[b][1] = 0.0f;
+
+    if (x_fast) prefetch(0);
+    commit(0);
+    if (x_fast && n_xchunks > 1) prefetch(1);
+    for (int s = 0; s < n_stages; ++s) {
+      const int gs = cc * n_stages + s, slot = gs % S;
+      const int xc = s / xg, xbuf = xc & 1;
+      if (s % xg == 0) {
+        if (xc > 0) {
+          // This chunk's activations: converted from the registers its loads landed in while the previous chunk was
+          // multiplied. The half they go to was last read two chunks ago, behind the barriers since.
+          commit(xc);
+          if (x_fast && xc + 1 < n_xchunks) prefetch(xc + 1);
+        }
+        if constexpr (kHalf) {
+          // accumulators move to this chunk's scale (scales only shrink, so nothing overflows)
+#pragma unroll
+          for (int b = 0; b < NT; ++b)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int col = 8 * b + 2 * t + h;
+              const float ns = col < n_cols ? bufscale[xbuf * 64 + col] : 1.0f;
+              if (cur_scale[b][h] != ns) {
+                const float ratio = cur_scale[b][h] != 0.0f ? ns / cur_scale[b][h] : 1.0f;
+#pragma unroll
+                for (int a = 0; a < RT; ++a) acc[a][b][h] *= ratio, acc[a][b][2 + h] *= ratio;
+                cur_scale[b][h] = ns;
+              }
+            }
+        }
       }
 
       mbar_wait(full_bar(slot), (gs / S) & 1, P.status, kStatusFullWait);
       const uint8_t* stage = ring + static_cast<size_t>(slot) * C::STAGE_BYTES;
       const int k_stage0 = s * C::KSTAGE;
+      const uint8_t* xbase = xs + xbuf * C::XHALF;
 
 #pragma unroll
       for (int u = 0; u < U; ++u) {
@@ -565,7 +628,7 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const StreamParams 
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               const int r = h ? r_hi : r_lo;
-              const uint8_t* b = stage + r * C::PITCH + x16_shift[a][h] + blk * 192;
+              const uint8_t* b = stage + r * pitch + x16_shift[a][h] + blk * 192;
               const uint2 sm = *reinterpret_cast<const uint2*>(b + 32 * quarter + 8 * t);
               const uint32_t codes = *reinterpret_cast<const uint32_t*>(b + 128 + 4 * (4 * quarter + t));
               const uint32_t base = hdr[r * hpitch + 4 * hdr_slots + (k_step0 >> 7)];
@@ -577,13 +640,13 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const StreamParams 
               dst[0] = v0.x, dst[1] = v0.y, dst[2] = v1.x, dst[3] = v1.y;
             }
           } else {
-            const uint4 qlo = *reinterpret_cast<const uint4*>(stage + r_lo * C::PITCH + st * 64 + t * 16);
-            const uint4 qhi = *reinterpret_cast<const uint4*>(stage + r_hi * C::PITCH + st * 64 + t * 16);
+            const uint4 qlo = *reinterpret_cast<const uint4*>(stage + r_lo * C::SEG + st * 64 + t * 16);
+            const uint4 qhi = *reinterpret_cast<const uint4*>(stage + r_hi * C::SEG + st * 64 + t * 16);
             uint32_t sc_lo = 0, sc_hi = 0;
             if constexpr (F == LX_W_NVFP4) {
-              const uint8_t* sc = stage + R * C::PITCH + st * 8 + t * 2;
-              sc_lo = *reinterpret_cast<const uint16_t*>(sc + r_lo * C::SCALE_PITCH);
-              sc_hi = *reinterpret_cast<const uint16_t*>(sc + r_hi * C::SCALE_PITCH);
+              const uint8_t* sc = stage + R * C::SEG + st * 8 + t * 2;
+              sc_lo = *reinterpret_cast<const uint16_t*>(sc + r_lo * C::SCALE_SEG);
+              sc_hi = *reinterpret_cast<const uint16_t*>(sc + r_hi * C::SCALE_SEG);
             }
             Expand<F>::run(qlo, sc_lo, plo);
             Expand<F>::run(qhi, sc_hi, phi);
@@ -597,12 +660,14 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const StreamParams 
           }
         }
         // activation operands and the products
-        const int xstep = (s % C::XG) * C::STEPS + st;
+        const int xstep = (s - xc * xg) * C::STEPS + st;
 #pragma unroll
         for (int b = 0; b < NT; ++b) {
 #pragma unroll
           for (int jj = 0; jj < C::JJ2; ++jj) {
-            const uint4 xb = *reinterpret_cast<const uint4*>(xs + ((xstep * NT + b) * C::JJ2 + jj) * 512 + lane * 16);
+            uint4 xb = make_uint4(0, 0, 0, 0);
+            if (NT > 1 || g < ncp)
+              xb = *reinterpret_cast<const uint4*>(xbase + ((((xstep * C::JJ2 + jj) * NT + b) * 4 + t) * ncp + g) * 16);
 #pragma unroll
             for (int a = 0; a < RT; ++a) {
               mma16816<kHalf>(acc[a][b], A[a][2 * jj], xb.x, xb.y);
@@ -623,8 +688,13 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const StreamParams 
       for (int b = 0; b < NT; ++b) {
         const int r = (wr * RT + a) * 16 + g, c = 8 * b + 2 * t;
         float* o = red + (static_cast<size_t>(wk) * R + r) * COLS + c;
-        o[0] = acc[a][b][0], o[1] = acc[a][b][1];
-        o[8 * COLS] = acc[a][b][2], o[8 * COLS + 1] = acc[a][b][3];
+        float i0 = 1.0f, i1 = 1.0f;  // back from the lane's column scales to plain units
+        if constexpr (kHalf) {
+          i0 = cur_scale[b][0] != 0.0f ? 1.0f / cur_scale[b][0] : 1.0f;
+          i1 = cur_scale[b][1] != 0.0f ? 1.0f / cur_scale[b][1] : 1.0f;
+        }
+        o[0] = acc[a][b][0] * i0, o[1] = acc[a][b][1] * i1;
+        o[8 * COLS] = acc[a][b][2] * i0, o[8 * COLS + 1] = acc[a][b][3] * i1;
       }
     named_bar_sync(1, kConsumerThreads);
     auto total = [&](int r, int j) -> float {
@@ -637,7 +707,6 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const StreamParams 
 #pragma unroll
         for (int q = 0; q < WK; ++q) sum += red[(static_cast<size_t>(q) * R + r) * COLS + j];
       }
-      if constexpr (kHalf) sum *= xinv[j];
       return sum;
     };
     auto row_factor = [&](int n) -> float {

@@ -11,8 +11,9 @@ struct VariantList {
   const char* const* names;
 };
 
-constexpr int kGemvVariants = 4;
-inline const char* const kGemvVariantNames[kGemvVariants] = {"s4r32u2", "s4r16u1", "s3r32u4", "s3r64u4"};
+constexpr int kGemvVariants = 8;
+inline const char* const kGemvVariantNames[kGemvVariants] = {"s4r32u2", "s4r16u1", "s3r32u4", "s3r64u4",
+                                                                "s6r32u2", "s8r16u1", "s4r64u2", "s6r16u2"};
 
 constexpr int kVariantKernels = 5;
 inline const VariantList kVariantTable[kVariantKernels] = {

@@ -1,0 +1,133 @@
+"""Mixture-of-experts parity through the C ABI: lx_moe_route (ids exact, weights / entropy / confidence to 1e-5), the
+grouping the expert GEMM sorts by (exact), and lx_moe_experts_grouped against the float64 oracle.
+
+Mirrors the reference's tests/kernels/test_moe.py and test_moe_grouped.py.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from dromos_b200 import abi
+from oracle import dromos_oracle as O
+from tests import util
+
+pytestmark = pytest.mark.gpu
+NAMES = {O.W_BF16: "bf16", O.W_INT8: "int8", O.W_FP8: "fp8", O.W_NVFP4: "nvfp4"}
+
+
+def route(lx, logits, bias, top_k):
+    T, E = logits.shape
+    ids = torch.full((T, top_k), -1, dtype=torch.int32, device="cuda")
+    w = torch.zeros((T, top_k), dtype=torch.float32, device="cuda")
+    ent = torch.zeros(T, dtype=torch.float32, device="cuda")
+    conf = torch.zeros(T, dtype=torch.float32, device="cuda")
+    st = lx.lx_moe_route(abi.ptr(util.dev(logits)), abi.ptr(None if bias is None else util.dev(bias)), abi.ptr(ids), abi.ptr(w),
+                         abi.ptr(ent), abi.ptr(conf), T, E, top_k, util.stream_ptr())
+    assert st == 0
+    torch.cuda.synchronize()
+    return util.host(ids), util.host(w), util.host(ent), util.host(conf)
+
+
+@pytest.mark.parametrize("T,E,top_k", [(1, 8, 2), (5, 64, 8), (32, 64, 8), (33, 128, 4), (7, 1000, 32)])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_route_matches_oracle(lx, T, E, top_k, with_bias):
+    logits = util.f32_normal((T, E), 1.0, T + E)
+    bias = util.f32_normal((E,), 0.1, 3) if with_bias else None
+    ids, w, ent, conf = route(lx, logits, bias, top_k)
+    ids_o, w_o, ent_o, conf_o = O.moe_route(logits, bias, top_k)
+    assert np.array_equal(ids, ids_o)
+    assert np.abs(w - w_o).max() <= 1e-5 and np.abs(ent - ent_o).max() <= 1e-5 and np.abs(conf - conf_o).max() <= 1e-5
+
+
+def test_route_ties_go_to_the_lower_index(lx):
+    logits = np.zeros((2, 6), dtype=np.float32)
+    logits[0] = [1.0, 3.0, 3.0, 0.0, 3.0, -1.0]
+    logits[1] = 0.5
+    ids, w, _, _ = route(lx, logits, None, 3)
+    assert ids[0].tolist() == [1, 2, 4] and ids[1].tolist() == [0, 1, 2]
+    assert np.allclose(w, 1.0 / 3.0, atol=1e-6)
+    bias = np.array([0, 0, 0, 10.0, 0, 0], dtype=np.float32)  # the bias picks, the unbiased logits weigh
+    ids, w, _, _ = route(lx, logits[:1], bias, 2)
+    assert ids[0].tolist() == [3, 1]
+    e = np.exp(np.array([0.0, 3.0]) - 3.0)
+    assert np.allclose(w[0], e / e.sum(), atol=1e-6)
+
+
+def experts_case(lx, wtype, T, L, I, E, top_k, seed=0, ids_override=None, per_expert_global=False):
+    gu_bits = util.bf16_normal((E, 2 * I, L), 0.02, seed)
+    dn_bits = util.bf16_normal((E, L, I), 0.02, seed + 1)
+    gu, dn = O.quantize_weight(gu_bits, wtype), O.quantize_weight(dn_bits, wtype)
+    if per_expert_global and wtype == O.W_NVFP4:
+        gu.expert_global = (np.float32(gu.glob) * (1.0 + 0.25 * np.arange(E))).astype(np.float32)
+    latent = util.bf16_normal((T, L), 1.0, seed + 2)
+    logits = util.f32_normal((T, E), 1.0, seed + 3)
+    ids, weights, _, _ = O.moe_route(logits, None, top_k)
+    if ids_override is not None:
+        ids = ids_override(ids)
+    dgu, ddn = util.DeviceWeight(gu), util.DeviceWeight(dn)
+    out = torch.full((T, L), float("nan"), device="cuda")
+    nbytes = lx.lx_moe_grouped_workspace_bytes(T, L, I, E, top_k, abi.MATH_BF16)
+    ws = torch.full((nbytes,), 0xFF, dtype=torch.uint8, device="cuda")  # garbage: nothing may be assumed zero
+    st = lx.lx_moe_experts_grouped(abi.ptr(util.dev(latent)), abi.ptr(util.dev(ids)), abi.ptr(util.dev(weights)), dgu.ref(),
+                                   ddn.ref(), abi.MATH_BF16, abi.ptr(out), abi.ptr(ws), T, L, I, E, top_k, util.stream_ptr())
+    assert st == 0, st
+    util.check_status(lx)
+    want = O.moe_experts_reference(latent, ids, weights, gu, dn, I)
+    return util.host(out), want, (ws, ids, E)
+
+
+@pytest.mark.parametrize("wtype", [O.W_BF16, O.W_INT8, O.W_FP8, O.W_NVFP4], ids=lambda w: NAMES[w])
+@pytest.mark.parametrize("T,L,I,E,top_k", [(5, 256, 256, 8, 2), (1, 512, 128, 16, 4), (32, 512, 256, 64, 8), (40, 256, 96, 6, 3)])
+def test_grouped_experts_match_oracle(lx, wtype, T, L, I, E, top_k):
+    got, want, _ = experts_case(lx, wtype, T, L, I, E, top_k, seed=T + E)
+    # the reference suite's bound is 2e-3 of max|out| under BF16 math; the acceptance bound is rel-L2 1e-3
+    assert np.abs(got - want).max() <= 2e-3 * np.abs(want).max()
+    util.assert_close(got, want, what=NAMES[wtype])
+
+
+def test_grouping_tables_are_exact(lx):
+    T, L, I, E, top_k = 32, 256, 64, 64, 8
+    _, _, (ws, ids, E) = experts_case(lx, O.W_FP8, T, L, I, E, top_k, seed=5)
+    counts, offsets, pairs = O.moe_group(ids, E)
+    raw = util.host(ws)
+    got_offsets = raw[: 4 * (E + 1)].view(np.int32)
+    at = (4 * (E + 1) + 255) // 256 * 256
+    at = at + (4 * E + 255) // 256 * 256
+    got_pairs = raw[at : at + 4 * T * top_k].view(np.int32)
+    assert np.array_equal(got_offsets, offsets) and np.array_equal(got_pairs, pairs)
+
+
+def test_skewed_routing_and_an_expert_chosen_twice(lx):
+    def skew(ids):
+        ids = ids.copy()
+        ids[:, 0] = 1          # every token picks expert 1: more rows than one column tile
+        ids[3, 1] = 1          # and one token picks it twice
+        return ids
+
+    got, want, _ = experts_case(lx, O.W_INT8, 24, 256, 128, 8, 2, seed=9, ids_override=skew)
+    util.assert_close(got, want, what="skewed")
+
+
+def test_per_expert_nvfp4_globals(lx):
+    got, want, _ = experts_case(lx, O.W_NVFP4, 6, 256, 256, 4, 2, seed=2, per_expert_global=True)
+    util.assert_close(got, want, what="expert_global")
+
+
+def test_token_bits_do_not_depend_on_batch(lx):
+    T, L, I, E, top_k = 8, 512, 256, 16, 4
+    gu = O.quantize_weight(util.bf16_normal((E, 2 * I, L), 0.02, 1), O.W_FP8)
+    dn = O.quantize_weight(util.bf16_normal((E, L, I), 0.02, 2), O.W_FP8)
+    dgu, ddn = util.DeviceWeight(gu), util.DeviceWeight(dn)
+    latent = util.bf16_normal((T, L), 1.0, 3)
+    ids, weights, _, _ = O.moe_route(util.f32_normal((T, E), 1.0, 4), None, top_k)
+    outs = {}
+    for t in (1, 3, 8):
+        out = torch.full((t, L), float("nan"), device="cuda")
+        ws = torch.empty(lx.lx_moe_grouped_workspace_bytes(t, L, I, E, top_k, 0), dtype=torch.uint8, device="cuda")
+        assert lx.lx_moe_experts_grouped(abi.ptr(util.dev(latent[:t])), abi.ptr(util.dev(ids[:t])), abi.ptr(util.dev(weights[:t])),
+                                         dgu.ref(), ddn.ref(), 0, abi.ptr(out), abi.ptr(ws), t, L, I, E, top_k,
+                                         util.stream_ptr()) == 0
+        util.check_status(lx)
+        outs[t] = util.host(out).view(np.uint32).copy()
+    assert np.array_equal(outs[1], outs[8][:1]) and np.array_equal(outs[3], outs[8][:3])
