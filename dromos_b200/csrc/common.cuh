@@ -22,6 +22,7 @@ constexpr int kNotSupported = LX_ERR_NOT_SUPPORTED;
 constexpr int kStatusFullWait = 1;   // a consumer waited for a weight stage that never arrived
 constexpr int kStatusEmptyWait = 2;  // the producer waited for a ring slot that was never released
 constexpr int kStatusDrainWait = 3;  // the final drain of in-flight copies ran out
+constexpr int kStatusPartWait = 4;   // a CTA waited for another CTA's partial sums that never came
 
 // ---- host: launch accounting and status -----------------------------------------------------------------
 extern std::atomic<int64_t> g_launches;
@@ -129,6 +130,35 @@ __device__ __forceinline__ void tile_g2s(uint32_t dst, const void* tmap, int x, 
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
       "l"(tmap), "r"(x), "r"(y), "r"(bar)
       : "memory");
+}
+// Asks L2 to fetch the box of a tensor map at (x, y); nothing lands in shared memory.
+__device__ __forceinline__ void tile_prefetch_l2(const void* tmap, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y) : "memory");
+}
+// Release store / acquire load on a flag another CTA polls, and a bounded wait for it to become nonzero.
+__device__ __forceinline__ void st_release(int* p, int v) { asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ int ld_acquire(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_cg(const float* p) {
+  float v;
+  asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ bool flag_wait(const int* flag, int* status) {
+  if (ld_acquire(flag)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (ld_acquire(flag)) return true;
+    if (global_timer_ns() - t0 > kWaitBudgetNs) {
+      if (status) atomicExch(status, kStatusPartWait);
+      return false;
+    }
+  }
 }
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");

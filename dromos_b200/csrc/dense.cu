@@ -6,52 +6,14 @@
 #include <cstring>
 
 #include "launch.cuh"
+#include "scalar.cuh"
 #include "variants.h"
 
 namespace b200 {
+unsigned long long* g_debug_trace = nullptr;
 namespace {
 
 // ---- scalar path: one warp per weight row, any K, any alignment ------------------------------------------------
-// Element k of weight row n as f32 without the row factor.
-template <int F>
-__device__ __forceinline__ float weight_element(const StreamParams& P, int64_t n, int k) {
-  const int K = P.K;
-  if constexpr (F == LX_W_BF16) {
-    return bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(P.w)[n * K + k]);
-  } else if constexpr (F == LX_W_INT8) {
-    return static_cast<float>(reinterpret_cast<const int8_t*>(P.w)[n * K + k]);
-  } else if constexpr (F == LX_W_FP8) {
-    return e4m3_to_f32(P.w[n * K + k]);
-  } else if constexpr (F == LX_W_NVFP4) {
-    const uint32_t byte = P.w[n * (K / 2) + k / 2];
-    return e2m1_to_f32((k & 1) ? (byte >> 4) : (byte & 15u)) * e4m3_to_f32(P.scale[n * (K / 16) + k / 16]);
-  } else {
-    // BF16X: sign|mantissa byte, 4-bit code below the block's base exponent, then the row's patches
-    const uint8_t* rec = P.w + n * P.row_bytes;
-    const int H = x16::header_bytes(K), slots = x16::patch_slots(K);
-    const int blk = k >> 7, off = k & 127;
-    const uint8_t* b = rec + H + blk * 192;
-    const uint32_t sm = b[off];
-    const uint32_t cbyte = b[128 + (off >> 3) * 4 + (off & 3)];
-    const uint32_t code = (off & 4) ? cbyte >> 4 : cbyte & 15u;
-    uint32_t e = (rec[4 * slots + blk] - code) & 0xffu;
-    const uint32_t* list = reinterpret_cast<const uint32_t*>(rec);
-    int n_list = slots;
-    const uint32_t s0 = list[0];
-    if (s0 != x16::kNoPatch && (s0 & 0x80000000u)) {
-      const uint32_t* r = reinterpret_cast<const uint32_t*>(rec + static_cast<int64_t>(s0 & 0x7fffffffu) * 8);
-      n_list = static_cast<int>(r[0]);
-      list = r + 1;
-    }
-    for (int i = 0; i < n_list; ++i) {
-      const uint32_t p = list[i];
-      if (p == x16::kNoPatch || (p >> 8) > static_cast<uint32_t>(k)) break;
-      if ((p >> 8) == static_cast<uint32_t>(k)) e = p & 0xffu;
-    }
-    return __uint_as_float(((sm & 0x80u) << 24) | (e << 23) | ((sm & 0x7fu) << 16));
-  }
-}
-
 template <int F>
 __global__ void __launch_bounds__(256) scalar_kernel(const StreamParams P) {
   pdl_trigger();
@@ -94,9 +56,6 @@ int launch_scalar(const StreamParams& P, cudaStream_t stream) {
 }
 
 // ---- choosing a streaming configuration ---------------------------------------------------------------------
-// Columns a call needs: one per activation row, two for f32 activations (high and low halves).
-int columns_needed(int M, int x_dtype) { return x_dtype == LX_BF16 ? M : 2 * M; }
-
 // Can the streaming kernel take this weight? Rows must be whole 64-byte steps and 16-byte aligned (NVFP4 scale rows
 // too); BF16X records are 8-byte aligned by contract and K must be whole 32-value steps.
 bool stream_ok(const lx_weight& w, int K) {
@@ -112,24 +71,40 @@ bool stream_ok(const lx_weight& w, int K) {
 
 template <int F>
 int launch_dense_format(const StreamParams& P, cudaStream_t stream) {
-  const int cols = columns_needed(std::min(P.M, 64), P.x_dtype);
-  constexpr int UW = F == LX_W_NVFP4 ? 1 : 2;  // NVFP4 holds four times the values per byte: shorter stages
+  constexpr int kMma = Fmt<F>::kMma;
+  constexpr bool k8 = kMma == kMmaE4m3 || kMma == kMmaS8;
+  // Columns the call needs: one per activation row and digit (see stream.cuh); more than 64 are served in passes.
+  const int T = terms_for(kMma, P.x_dtype == LX_BF16);
+  const int cols = std::min(P.M * T, 64);
+  // NVFP4 holds four times the values per byte, so its stages span four times the K: shorter stages for wide tiles.
+  constexpr int UW = F == LX_W_NVFP4 ? 1 : 2;
   if (cols <= 8) {
+    // Bytes of activation units for the whole of K; up to 32 KB stays resident in the small buffer.
+    const int64_t unit_bytes = static_cast<int64_t>(P.K) / (k8 ? 16 : 8) * 16 * cols;
+    if (unit_bytes > 32 * 1024) return launch_stream<F, 8, 1, 2, 1, 2, 4, 64, kDense>(P, stream, P.N);
     // decode GEMV: the variant the table holds for this shape (keyed on M's power-of-two bucket), else variant 0
     switch (lx_tune_get(gemv_kernel_name(F), P.M, P.N, P.K)) {
-      case 1: return launch_stream<F, 1, 1, 1, 1, 4, kDense>(P, dim3((P.N + 15) / 16), stream, P.N);
-      case 2: return launch_stream<F, 1, 2, 1, 4, 3, kDense>(P, dim3((P.N + 31) / 32), stream, P.N);
-      case 3: return launch_stream<F, 1, 4, 1, 4, 3, kDense>(P, dim3((P.N + 63) / 64), stream, P.N);
-      case 4: return launch_stream<F, 1, 2, 1, 2, 6, kDense>(P, dim3((P.N + 31) / 32), stream, P.N);
-      case 5: return launch_stream<F, 1, 1, 1, 1, 8, kDense>(P, dim3((P.N + 15) / 16), stream, P.N);
-      case 6: return launch_stream<F, 1, 4, 1, 2, 4, kDense>(P, dim3((P.N + 63) / 64), stream, P.N);
-      case 7: return launch_stream<F, 1, 1, 1, 2, 6, kDense>(P, dim3((P.N + 15) / 16), stream, P.N);
-      default: return launch_stream<F, 1, 2, 1, 2, 4, kDense>(P, dim3((P.N + 31) / 32), stream, P.N);
+      case 1: return launch_stream<F, 8, 1, 2, 1, 2, 8, 16, kDense>(P, stream, P.N);
+      case 2: return launch_stream<F, 8, 1, 2, 1, 2 * UW, 4, 16, kDense>(P, stream, P.N);
+      case 3: return launch_stream<F, 16, 1, 4, 1, 2, 4, 16, kDense>(P, stream, P.N);
+      case 4: return launch_stream<F, 8, 1, 1, 1, 1, 6, 16, kDense>(P, stream, P.N);
+      case 5: return launch_stream<F, 16, 1, 2, 1, 1, 6, 16, kDense>(P, stream, P.N);
+      case 6: return launch_stream<F, 8, 1, 1, 1, 2 * UW, 4, 32, kDense>(P, stream, P.N);
+      case 7: return launch_stream<F, 16, 1, 2, 1, UW, 4, 16, kDense>(P, stream, P.N);
+      case 8: return launch_stream<F, 16, 1, 2, 1, UW, 5, 16, kDense>(P, stream, P.N);
+      case 9: return launch_stream<F, 16, 1, 4, 1, 2 * UW, 3, 16, kDense>(P, stream, P.N);
+      // the deepest rings shared memory allows, for activations of at most 16 KB (32 KB for NVFP4)
+      case 10: return launch_stream<F, 8, 1, 2, 1, 2 * UW, (F == LX_W_NVFP4 ? 9 : 6), (F == LX_W_NVFP4 ? 16 : 8), kDense>(P, stream, P.N);
+      case 11: return launch_stream<F, 16, 1, 2, 1, UW, (F == LX_W_NVFP4 ? 9 : 6), (F == LX_W_NVFP4 ? 16 : 8), kDense>(P, stream, P.N);
+      case 12: return launch_stream<F, 8, 1, 2, 1, UW, (F == LX_W_NVFP4 ? 18 : 12), (F == LX_W_NVFP4 ? 16 : 8), kDense>(P, stream, P.N);
+      case 13: return launch_stream<F, 16, 1, 4, 1, UW, (F == LX_W_NVFP4 ? 9 : 6), (F == LX_W_NVFP4 ? 16 : 8), kDense>(P, stream, P.N);
+      default: return launch_stream<F, 8, 1, 2, 1, 2, 4, 16, kDense>(P, stream, P.N);
     }
   }
-  if (cols <= 16) return launch_stream<F, 1, 2, 2, 2, 4, kDense>(P, dim3((P.N + 31) / 32), stream, P.N);
-  if (cols <= 32) return launch_stream<F, 2, 2, 4, UW, 3, kDense>(P, dim3((P.N + 63) / 64), stream, P.N);
-  return launch_stream<F, 2, 4, 8, UW, 2, kDense>(P, dim3((P.N + 127) / 128), stream, P.N);
+  if (cols <= 16) return launch_stream<F, 8, 1, 2, 2, 2, 4, 64, kDense>(P, stream, P.N);
+  if (cols <= 24) return launch_stream<F, 8, 1, 2, 3, 2, 4, 64, kDense>(P, stream, P.N);
+  if (cols <= 32) return launch_stream<F, 8, 2, 2, 4, UW, 3, 32, kDense>(P, stream, P.N);
+  return launch_stream<F, 8, 2, 4, 8, UW, 2, 32, kDense>(P, stream, P.N);
 }
 
 int row_bytes_of(int type, int K) {
@@ -157,6 +132,8 @@ int dense_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, cons
   P.y = y, P.y_dtype = y_dtype, P.ld_y = ld_y;
   P.alpha = alpha, P.beta = beta;
   P.status = status_word();
+  P.debug_skip = std::getenv("LX_B200_DEBUG_SKIP") ? std::atoi(std::getenv("LX_B200_DEBUG_SKIP")) : 0;
+  P.trace = g_debug_trace;
   const bool fast = stream_ok(w, K) && !force_scalar();
   switch (w.type) {
     case LX_W_BF16: return fast ? launch_dense_format<LX_W_BF16>(P, stream) : launch_scalar<LX_W_BF16>(P, stream);
@@ -286,3 +263,5 @@ extern "C" int lx_gemm_skinny(const void* x, lx_dtype x_dtype, int ld_x, const l
   return dense_product(x, x_dtype, ld_x, *w, bias, bias_dtype, y, y_dtype, ld_y, M, N, K, alpha, beta,
                        static_cast<cudaStream_t>(stream));
 }
+
+extern "C" LX_API void lx_b200_debug_trace(void* buf) { b200::g_debug_trace = static_cast<unsigned long long*>(buf); }

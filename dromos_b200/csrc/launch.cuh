@@ -3,6 +3,7 @@
 // calls griddepcontrol.wait before reading anything the predecessor wrote) and returns the launch status.
 #pragma once
 
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -47,6 +48,23 @@ int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, 
   return kOk;
 }
 
+// Scratch for the stage-granular split of dense products: per device, a few regions handed out in turn (consecutive
+// launches never share one), each holding kSplitMaxCtas partial-sum slots of kSplitBytesPerCta bytes and their flags.
+// Allocated on first use and kept for the life of the process; the flags are zero whenever no kernel is running.
+constexpr int kSplitMaxCtas = 1024;
+constexpr int kSplitBytesPerCta = 8192;
+constexpr int kSplitRegions = 4;
+int split_scratch(float** partials, int** flags);
+// Off unless LX_B200_SPLIT_K=1: measured on B200, the hand-off between CTAs (fence, flag, partial loads, about 3 us)
+// costs more than the better balance wins at decode sizes, so by default every tile stays whole in one CTA.
+inline bool split_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("LX_B200_SPLIT_K");
+    return v && v[0] == '1';
+  }();
+  return on;
+}
+
 // cuTensorMapEncodeTiled, fetched from the driver through the runtime (the library does not link libcuda).
 using TensorMapEncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                        const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -69,45 +87,71 @@ inline int make_tile_map(CUtensorMap* map, const void* base, int64_t row_bytes, 
   return r == CUDA_SUCCESS ? kOk : kInvalid;
 }
 
-// stack_rows: rows of the whole weight the kernel may address (N, or E * N for a stack of experts).
-template <int F, int RT, int WR, int NT, int U, int S, int MODE>
-int launch_stream(StreamParams P, dim3 grid, cudaStream_t stream, int64_t stack_rows) {
-  using C = StreamCfg<F, RT, WR, NT, U, S>;
-  auto kernel = stream_kernel<F, RT, WR, NT, U, S, MODE>;
-  const size_t smem = stream_smem_bytes<F, RT, WR, NT, U, S>(P.K);
+// Launches the persistent streaming kernel: as many CTAs as the device holds at once (or one per tile when there are
+// fewer tiles). stack_rows: rows of the whole weight the kernel may address (N, or E * N for a stack of experts).
+template <int F, int NW, int RT, int WR, int NT, int U, int S, int XKB, int MODE>
+int launch_stream(StreamParams P, cudaStream_t stream, int64_t stack_rows) {
+  using C = StreamCfg<F, NW, RT, WR, NT, U, S, XKB>;
+  auto kernel = stream_kernel<F, NW, RT, WR, NT, U, S, XKB, MODE>;
+  const size_t smem = stream_smem_bytes<F, NW, RT, WR, NT, U, S, XKB>(P.K);
   if (smem > 226 * 1024) return kNotSupported;
   // The opt-in to more than 48 KB of dynamic shared memory is per device and per kernel; set it once per device,
   // with the whole of the SM's L1 given to shared memory so that as many CTAs fit as their sizes allow.
   static std::mutex mu;
-  static unsigned long long done_mask = 0;  // bit per device ordinal (< 64)
+  static int ctas_per_sm[64] = {};  // per device ordinal; 0 = not set up yet
+  static int sm_count[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
+  dev &= 63;
   {
     std::lock_guard<std::mutex> lock(mu);
-    if (!(done_mask >> (dev & 63) & 1ull)) {
+    if (!ctas_per_sm[dev]) {
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
       if (e == cudaSuccess)
         e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+      int n = 0, sms = 0;
+      if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, C::kThreads, smem);
+      if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
       if (e != cudaSuccess) {
         cudaGetLastError();
         return static_cast<int>(e);
       }
-      done_mask |= 1ull << (dev & 63);
+      if (n < 1) return kNotSupported;
+      ctas_per_sm[dev] = n;
+      sm_count[dev] = sms;
     }
   }
   alignas(64) CUtensorMap wmap, smap;
   memset(&wmap, 0, sizeof(wmap));
   memset(&smap, 0, sizeof(smap));
   // BF16X records come as tiles when they and their data start on 16-byte boundaries; every other format always does
-  // (the callers check stream_ok).
+  // (the callers check that the weight streams).
   P.tiled = !C::kX16 || (aligned(P.w, 16) && P.row_bytes % 16 == 0 && x16::header_bytes(P.K) % 16 == 0);
   if (P.tiled) {
     const int box_rows = MODE == kGateUp ? C::R / 2 : C::R;
-    if (int e = make_tile_map(&wmap, P.w, P.row_bytes, stack_rows, C::SEG, box_rows, 4)) return e;
+    if (int e = make_tile_map(&wmap, P.w, P.row_bytes, stack_rows, C::BOXW, box_rows, 4)) return e;
     if constexpr (F == LX_W_NVFP4)
       if (int e = make_tile_map(&smap, P.scale, P.K / 16, stack_rows, C::SCALE_SEG, box_rows, 1)) return e;
   }
-  return launch_kernel(kernel, grid, dim3(kThreads), smem, stream, wmap, smap, P);
+  const int rows_per_tile = MODE == kGateUp ? C::R / 2 : C::R;
+  const int64_t rows_total = MODE == kGateUp ? P.I : P.N;
+  const int64_t tiles = (rows_total + rows_per_tile - 1) / rows_per_tile * (MODE == kDense ? 1 : P.groups);
+  const int64_t resident = static_cast<int64_t>(ctas_per_sm[dev]) * sm_count[dev];
+  int64_t units = tiles;
+  P.split_k = 0;
+  if constexpr (MODE == kDense && C::R * C::COLS * 4 <= kSplitBytesPerCta) {
+    // Stage-granular split: one pass over the weights, activations resident in the unit buffer, and scratch at hand.
+    const int T = terms_for(C::kMma, P.x_dtype == LX_BF16), n_cols = P.M * T;
+    const int64_t n_stages = (P.K + C::KSTAGE - 1) / C::KSTAGE;
+    const int64_t x_bytes = n_stages * (C::KSTAGE / C::GV) * 16 * NT * (NT == 1 ? n_cols : 8);
+    if (n_cols <= C::COLS && x_bytes <= C::XBYTES && resident <= kSplitMaxCtas && split_enabled() &&
+        split_scratch(&P.partials, &P.flags) == kOk) {
+      P.split_k = 1;
+      units = tiles * n_stages;
+    }
+  }
+  const unsigned grid = static_cast<unsigned>(std::max<int64_t>(1, std::min(units, resident)));
+  return launch_kernel(kernel, dim3(grid), dim3(C::kThreads), smem, stream, wmap, smap, P);
 }
 
 struct ActLayout {

@@ -13,6 +13,7 @@
 #include <algorithm>
 
 #include "launch.cuh"
+#include "scalar.cuh"
 
 namespace b200 {
 namespace {
@@ -49,14 +50,16 @@ __global__ void __launch_bounds__(256) route_kernel(const float* __restrict__ lo
     if (confidence) confidence[t] = 1.0f / z;
   }
   // top_k by logit + bias, descending, ties to the lower index: top_k rounds of a warp arg-max over what is left
-  int mine = -1;        // lane j keeps pick j
+  __shared__ int picks[8][32];
+  int* mine_picks = picks[threadIdx.x >> 5];
+  int mine = -1;  // lane j keeps pick j
   float mine_logit = -INFINITY;
   for (int r = 0; r < top_k; ++r) {
     float best = -INFINITY;
     int best_i = E;
     for (int i = lane; i < E; i += 32) {
       bool taken = false;
-      for (int j = 0; j < r; ++j) taken |= __shfl_sync(0xffffffffu, mine, j) == i;
+      for (int j = 0; j < r; ++j) taken |= mine_picks[j] == i;
       if (taken) continue;
       const float v = row[i] + (bias ? bias[i] : 0.0f);
       if (v > best || (v == best && i < best_i)) best = v, best_i = i;
@@ -68,6 +71,8 @@ __global__ void __launch_bounds__(256) route_kernel(const float* __restrict__ lo
       if (ov > best || (ov == best && oi < best_i)) best = ov, best_i = oi;
     }
     if (lane == r) mine = best_i, mine_logit = best_i < E ? row[best_i] : -INFINITY;
+    if (lane == 0) mine_picks[r] = best_i;
+    __syncwarp();
   }
   // weights: softmax over the picks of their unbiased logits
   const bool live = lane < top_k && mine >= 0 && mine < E;
@@ -175,6 +180,64 @@ __global__ void __launch_bounds__(256) ordered_sum_kernel(const float* __restric
   out[i] = acc;
 }
 
+// ---- scalar expert stages (shapes the streaming kernel does not take): one warp per output value --------------------
+// mid[p, i] = bf16(silu(s_g * gate_i . x) * (s_u * up_i . x)) for pair p = t * top_k + k, rows by pair index.
+template <int F>
+__global__ void __launch_bounds__(256) scalar_gate_up_kernel(const StreamParams P, const int32_t* __restrict__ ids, int pairs) {
+  pdl_trigger();
+  pdl_wait();
+  const int64_t w = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (w >= static_cast<int64_t>(pairs) * P.I) return;
+  const int p = static_cast<int>(w / P.I), i = static_cast<int>(w % P.I), lane = threadIdx.x & 31;
+  const int e = ids[p];
+  const uint16_t* x = static_cast<const uint16_t*>(P.x) + static_cast<int64_t>(p / P.top_k) * P.ld_x;
+  const int64_t ng = static_cast<int64_t>(e) * P.N + i, nu = ng + P.I;
+  float g = 0.0f, u = 0.0f;
+  for (int k = lane; k < P.K; k += 32) {
+    const float xv = bf16_bits_to_f32(x[k]);
+    g = fmaf(xv, weight_element<F>(P, ng, k), g);
+    u = fmaf(xv, weight_element<F>(P, nu, k), u);
+  }
+  g = warp_sum(g) * scalar_row_factor<F>(P, ng, e);
+  u = warp_sum(u) * scalar_row_factor<F>(P, nu, e);
+  if (lane == 0) static_cast<uint16_t*>(P.moe_out)[w] = static_cast<uint16_t>(f32_to_bf16_bits(g / (1.0f + expf(-g)) * u));
+}
+
+// rows[p, l] = weight[p] * (s_l * down_l . mid[p])
+template <int F>
+__global__ void __launch_bounds__(256) scalar_down_kernel(const StreamParams P, const int32_t* __restrict__ ids, int pairs) {
+  pdl_trigger();
+  pdl_wait();
+  const int64_t w = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (w >= static_cast<int64_t>(pairs) * P.N) return;
+  const int p = static_cast<int>(w / P.N), l = static_cast<int>(w % P.N), lane = threadIdx.x & 31;
+  const int e = ids[p];
+  const uint16_t* x = static_cast<const uint16_t*>(P.x) + static_cast<int64_t>(p) * P.ld_x;
+  const int64_t n = static_cast<int64_t>(e) * P.N + l;
+  float acc = 0.0f;
+  for (int k = lane; k < P.K; k += 32) acc = fmaf(bf16_bits_to_f32(x[k]), weight_element<F>(P, n, k), acc);
+  acc = warp_sum(acc);
+  if (lane == 0) static_cast<float*>(P.moe_out)[w] = P.route_w[p] * (scalar_row_factor<F>(P, n, e) * acc);
+}
+
+template <int F>
+int launch_scalar_stage(bool gate_up, const StreamParams& P, const int32_t* ids, int pairs, cudaStream_t s) {
+  const int64_t warps = static_cast<int64_t>(pairs) * (gate_up ? P.I : P.N);
+  const dim3 grid(static_cast<unsigned>((warps + 7) / 8));
+  return gate_up ? launch_kernel(scalar_gate_up_kernel<F>, grid, dim3(256), 0, s, P, ids, pairs)
+                 : launch_kernel(scalar_down_kernel<F>, grid, dim3(256), 0, s, P, ids, pairs);
+}
+int launch_scalar_stage(bool gate_up, int type, const StreamParams& P, const int32_t* ids, int pairs, cudaStream_t s) {
+  switch (type) {
+    case LX_W_BF16: return launch_scalar_stage<LX_W_BF16>(gate_up, P, ids, pairs, s);
+    case LX_W_INT8: return launch_scalar_stage<LX_W_INT8>(gate_up, P, ids, pairs, s);
+    case LX_W_FP8: return launch_scalar_stage<LX_W_FP8>(gate_up, P, ids, pairs, s);
+    case LX_W_NVFP4: return launch_scalar_stage<LX_W_NVFP4>(gate_up, P, ids, pairs, s);
+    case LX_W_BF16X: return launch_scalar_stage<LX_W_BF16X>(gate_up, P, ids, pairs, s);
+  }
+  return kInvalid;
+}
+
 int64_t round_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
 struct Layout {
@@ -219,19 +282,20 @@ bool stack_streams(const lx_weight& w, int K) {
 }
 
 template <int MODE>
-int launch_expert_stage(const StreamParams& P, int type, dim3 grid, cudaStream_t s, int64_t stack_rows) {
+int launch_expert_stage(const StreamParams& P, int type, cudaStream_t s, int64_t stack_rows) {
   switch (type) {
-    case LX_W_BF16: return launch_stream<LX_W_BF16, 1, 2, 1, 2, 4, MODE>(P, grid, s, stack_rows);
-    case LX_W_INT8: return launch_stream<LX_W_INT8, 1, 2, 1, 2, 4, MODE>(P, grid, s, stack_rows);
-    case LX_W_FP8: return launch_stream<LX_W_FP8, 1, 2, 1, 2, 4, MODE>(P, grid, s, stack_rows);
-    case LX_W_NVFP4: return launch_stream<LX_W_NVFP4, 1, 2, 1, 2, 4, MODE>(P, grid, s, stack_rows);
-    case LX_W_BF16X: return launch_stream<LX_W_BF16X, 1, 2, 1, 2, 4, MODE>(P, grid, s, stack_rows);
+    case LX_W_BF16: return launch_stream<LX_W_BF16, 8, 1, 2, 2, 2, 4, 32, MODE>(P, s, stack_rows);
+    case LX_W_INT8: return launch_stream<LX_W_INT8, 8, 1, 2, 2, 2, 4, 32, MODE>(P, s, stack_rows);
+    case LX_W_FP8: return launch_stream<LX_W_FP8, 8, 1, 2, 2, 2, 4, 32, MODE>(P, s, stack_rows);
+    case LX_W_NVFP4: return launch_stream<LX_W_NVFP4, 8, 1, 2, 2, 2, 4, 32, MODE>(P, s, stack_rows);
+    case LX_W_BF16X: return launch_stream<LX_W_BF16X, 8, 1, 2, 2, 2, 4, 32, MODE>(P, s, stack_rows);
   }
   return kInvalid;
 }
 
 // Stages 2-4 on grouping tables already in the workspace. groups = grid extent over expert groups.
-int run_experts(const void* latent, const float* weights, const lx_weight& gate_up, const lx_weight& down, float* out,
+int run_experts(const void* latent, const int32_t* ids, const float* weights, const lx_weight& gate_up, const lx_weight& down,
+                float* out,
                 uint8_t* ws, const Layout& l, bool indirect, int groups, int experts, int T, int L, int I, int top_k,
                 cudaStream_t s) {
   StreamParams g{};
@@ -243,6 +307,7 @@ int run_experts(const void* latent, const float* weights, const lx_weight& gate_
   g.N = 2 * I, g.K = L;
   g.x = latent, g.x_dtype = LX_BF16, g.ld_x = L, g.M = T;
   g.x_vec = aligned(latent, 16) && L % 8 == 0;
+  g.groups = groups;
   g.offsets = reinterpret_cast<const int32_t*>(ws + l.offsets);
   g.group_expert = indirect ? reinterpret_cast<const int32_t*>(ws + l.group_expert) : nullptr;
   g.pairs = reinterpret_cast<const int32_t*>(ws + l.pairs);
@@ -250,7 +315,11 @@ int run_experts(const void* latent, const float* weights, const lx_weight& gate_
   g.top_k = top_k, g.I = I;
   g.moe_out = ws + l.mid;
   g.status = status_word();
-  if (int e = launch_expert_stage<kGateUp>(g, gate_up.type, dim3((I + 15) / 16, groups), s, static_cast<int64_t>(experts) * 2 * I)) return e;
+  // weights the streaming kernel cannot take run both stages on the scalar kernels (intermediate rows by pair index)
+  const bool fast_gu = stack_streams(gate_up, L) && stack_streams(down, I), fast_dn = fast_gu;
+  if (int e = fast_gu ? launch_expert_stage<kGateUp>(g, gate_up.type, s, static_cast<int64_t>(experts) * 2 * I)
+                      : launch_scalar_stage(true, gate_up.type, g, ids, T * top_k, s))
+    return e;
 
   StreamParams d = g;
   d.w = static_cast<const uint8_t*>(down.data);
@@ -262,7 +331,9 @@ int run_experts(const void* latent, const float* weights, const lx_weight& gate_
   d.x = ws + l.mid, d.ld_x = I;
   d.x_vec = I % 8 == 0;
   d.moe_out = ws + l.rows;
-  if (int e = launch_expert_stage<kDown>(d, down.type, dim3((L + 31) / 32, groups), s, static_cast<int64_t>(experts) * L)) return e;
+  if (int e = fast_dn ? launch_expert_stage<kDown>(d, down.type, s, static_cast<int64_t>(experts) * L)
+                      : launch_scalar_stage(false, down.type, d, ids, T * top_k, s))
+    return e;
 
   const int64_t n = static_cast<int64_t>(T) * L;
   return launch_kernel(ordered_sum_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, s,
@@ -300,7 +371,8 @@ extern "C" int lx_moe_experts_grouped(const void* latent, const int32_t* ids, co
   if (gate_up->type < LX_W_BF16 || gate_up->type > LX_W_NVFP4 || down->type < LX_W_BF16 || down->type > LX_W_NVFP4)
     return kNotSupported;
   if (math != LX_MATH_BF16) return kNotSupported;  // activations stay bf16: weight-only products
-  if (I % 8 != 0 || L % 8 != 0 || !stack_streams(*gate_up, L) || !stack_streams(*down, I)) return kNotSupported;
+  if (I % 8 != 0 || L % 8 != 0) return kNotSupported;
+  if (gate_up->type == LX_W_NVFP4 && (L % 16 != 0 || I % 16 != 0)) return kInvalid;
   auto s = static_cast<cudaStream_t>(stream);
   const int P = T * top_k;
   const Layout l = layout(P, E, L, I);
@@ -308,5 +380,5 @@ extern "C" int lx_moe_experts_grouped(const void* latent, const int32_t* ids, co
   if (int e = launch_kernel(group_kernel, dim3(1), dim3(1024), 0, s, ids, P, E, reinterpret_cast<int32_t*>(ws + l.offsets),
                             reinterpret_cast<int32_t*>(ws + l.pairs)))
     return e;
-  return run_experts(latent, weights, *gate_up, *down, out, ws, l, false, E, E, T, L, I, top_k, s);
+  return run_experts(latent, ids, weights, *gate_up, *down, out, ws, l, false, E, E, T, L, I, top_k, s);
 }

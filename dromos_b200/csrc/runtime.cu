@@ -35,6 +35,30 @@ int* status_word() {
   return words[dev];
 }
 
+int split_scratch(float** partials, int** flags) {
+  static std::mutex mu;
+  static uint8_t* base[64] = {};
+  static unsigned next[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 63;
+  std::lock_guard<std::mutex> lock(mu);
+  const size_t region = static_cast<size_t>(kSplitMaxCtas) * (kSplitBytesPerCta + sizeof(int));
+  if (!base[dev]) {
+    void* p = nullptr;
+    if (cudaMalloc(&p, region * kSplitRegions) != cudaSuccess) {
+      cudaGetLastError();
+      return kNotSupported;
+    }
+    cudaMemset(p, 0, region * kSplitRegions);
+    base[dev] = static_cast<uint8_t*>(p);
+  }
+  uint8_t* r = base[dev] + region * (next[dev]++ % kSplitRegions);
+  *partials = reinterpret_cast<float*>(r);
+  *flags = reinterpret_cast<int*>(r + static_cast<size_t>(kSplitMaxCtas) * kSplitBytesPerCta);
+  return kOk;
+}
+
 TensorMapEncodeFn tensor_map_encoder() {
   static TensorMapEncodeFn fn = [] {
     void* p = nullptr;

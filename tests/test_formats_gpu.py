@@ -71,7 +71,8 @@ def test_quantize_w8_matches(lx):
     want = O.quantize_weight(w, O.W_INT8)
     q = torch.zeros((rows, K), dtype=torch.int8, device="cuda")
     s = torch.zeros(rows, dtype=torch.float32, device="cuda")
-    assert lx.lx_quantize_w8(abi.ptr(util.dev(w)), abi.ptr(q), abi.ptr(s), rows, K, util.stream_ptr()) == 0
+    w_dev = util.dev(w)
+    assert lx.lx_quantize_w8(abi.ptr(w_dev), abi.ptr(q), abi.ptr(s), rows, K, util.stream_ptr()) == 0
     torch.cuda.synchronize()
     assert np.array_equal(util.host(q), want.data) and np.array_equal(util.host(s), want.scale)
 
@@ -93,7 +94,8 @@ def test_quantize_act_bytes(lx, math, x_f32):
     q = torch.zeros((M, ld_q), dtype=torch.uint8, device="cuda")
     s = torch.zeros(M, dtype=torch.float32, device="cuda")
     bs = torch.zeros((M, K // 16), dtype=torch.uint8, device="cuda")
-    st = lx.lx_quantize_act(abi.ptr(util.dev(x)), abi.F32 if x_f32 else abi.BF16, K, math, abi.ptr(q), ld_q, abi.ptr(s),
+    x_dev = util.dev(x)
+    st = lx.lx_quantize_act(abi.ptr(x_dev), abi.F32 if x_f32 else abi.BF16, K, math, abi.ptr(q), ld_q, abi.ptr(s),
                             abi.ptr(bs), K // 16, M, K, util.stream_ptr())
     assert st == 0
     torch.cuda.synchronize()

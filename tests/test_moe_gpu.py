@@ -22,8 +22,10 @@ def route(lx, logits, bias, top_k):
     w = torch.zeros((T, top_k), dtype=torch.float32, device="cuda")
     ent = torch.zeros(T, dtype=torch.float32, device="cuda")
     conf = torch.zeros(T, dtype=torch.float32, device="cuda")
-    st = lx.lx_moe_route(abi.ptr(util.dev(logits)), abi.ptr(None if bias is None else util.dev(bias)), abi.ptr(ids), abi.ptr(w),
-                         abi.ptr(ent), abi.ptr(conf), T, E, top_k, util.stream_ptr())
+    logits_d = util.dev(logits)
+    bias_d = None if bias is None else util.dev(bias)
+    st = lx.lx_moe_route(abi.ptr(logits_d), abi.ptr(bias_d), abi.ptr(ids), abi.ptr(w), abi.ptr(ent), abi.ptr(conf), T, E, top_k,
+                         util.stream_ptr())
     assert st == 0
     torch.cuda.synchronize()
     return util.host(ids), util.host(w), util.host(ent), util.host(conf)
@@ -69,8 +71,9 @@ def experts_case(lx, wtype, T, L, I, E, top_k, seed=0, ids_override=None, per_ex
     out = torch.full((T, L), float("nan"), device="cuda")
     nbytes = lx.lx_moe_grouped_workspace_bytes(T, L, I, E, top_k, abi.MATH_BF16)
     ws = torch.full((nbytes,), 0xFF, dtype=torch.uint8, device="cuda")  # garbage: nothing may be assumed zero
-    st = lx.lx_moe_experts_grouped(abi.ptr(util.dev(latent)), abi.ptr(util.dev(ids)), abi.ptr(util.dev(weights)), dgu.ref(),
-                                   ddn.ref(), abi.MATH_BF16, abi.ptr(out), abi.ptr(ws), T, L, I, E, top_k, util.stream_ptr())
+    latent_d, ids_d, weights_d = util.dev(latent), util.dev(ids), util.dev(weights)  # kept alive across the call
+    st = lx.lx_moe_experts_grouped(abi.ptr(latent_d), abi.ptr(ids_d), abi.ptr(weights_d), dgu.ref(), ddn.ref(), abi.MATH_BF16,
+                                   abi.ptr(out), abi.ptr(ws), T, L, I, E, top_k, util.stream_ptr())
     assert st == 0, st
     util.check_status(lx)
     want = O.moe_experts_reference(latent, ids, weights, gu, dn, I)
@@ -125,9 +128,9 @@ def test_token_bits_do_not_depend_on_batch(lx):
     for t in (1, 3, 8):
         out = torch.full((t, L), float("nan"), device="cuda")
         ws = torch.empty(lx.lx_moe_grouped_workspace_bytes(t, L, I, E, top_k, 0), dtype=torch.uint8, device="cuda")
-        assert lx.lx_moe_experts_grouped(abi.ptr(util.dev(latent[:t])), abi.ptr(util.dev(ids[:t])), abi.ptr(util.dev(weights[:t])),
-                                         dgu.ref(), ddn.ref(), 0, abi.ptr(out), abi.ptr(ws), t, L, I, E, top_k,
-                                         util.stream_ptr()) == 0
+        latent_d, ids_d, weights_d = util.dev(latent[:t]), util.dev(ids[:t]), util.dev(weights[:t])
+        assert lx.lx_moe_experts_grouped(abi.ptr(latent_d), abi.ptr(ids_d), abi.ptr(weights_d), dgu.ref(), ddn.ref(), 0,
+                                         abi.ptr(out), abi.ptr(ws), t, L, I, E, top_k, util.stream_ptr()) == 0
         util.check_status(lx)
         outs[t] = util.host(out).view(np.uint32).copy()
     assert np.array_equal(outs[1], outs[8][:1]) and np.array_equal(outs[3], outs[8][:3])
