@@ -1,0 +1,338 @@
+"""Headline benchmark: decode matmul effective HBM TB/s (weights + scales streamed per product / time).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+A step is one pass of the hot path over one batch of synthetic input: for the default workload (the INT8 weight-only
+product, K = 4096, N = 14336, M in {1, 8, 32}) one product per M against a weight copy that has not been touched for
+at least 1 GiB of other weights, so every byte comes from HBM. With N > 1 GPUs (launched under torchrun) the weight
+rows are split over the ranks and the output slices meet in an NCCL all-gather inside the timed region.
+
+Prints ONE JSON line (rank 0). `value` is the whole-job figure with inputs resident in HBM; `e2e` is the same metric
+through the host-buffer API (pinned host activations copied in, outputs copied out, every step); `roofline` is the
+streaming kernel alone against the measured HBM copy bandwidth; `cpu_baseline` is the reference's own CPU backend on
+the host cores of this machine. `--impl reference` times that CPU backend on the same steps instead.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from dromos_b200 import abi  # noqa: E402
+
+WORKLOADS = {
+    # name: (weight format, N, K, Ms, description)
+    "c1_bf16": (abi.W_BF16, 4096, 4096, (1,), "BF16 GEMV M=1 K=4096 N=4096"),
+    "c2_int8": (abi.W_INT8, 14336, 4096, (1, 8, 32), "INT8 weight-only gemm_w M in {1,8,32} K=4096 N=14336"),
+    "c3_fp8": (abi.W_FP8, 28672, 8192, (1, 16, 64), "FP8 E4M3 (per-row scale) gemm_w M in {1,16,64} K=8192 N=28672"),
+    "c3_nvfp4": (abi.W_NVFP4, 28672, 8192, (1, 16, 64), "NVFP4 gemm_w M in {1,16,64} K=8192 N=28672"),
+    "c4_bf16x": (abi.W_BF16X, 14336, 4096, (1,), "BF16X lossless GEMV M=1 K=4096 N=14336"),
+}
+DTYPE = {abi.W_BF16: "bf16", abi.W_INT8: "int8xbf16->s32/f32", abi.W_FP8: "e4m3xbf16->f32", abi.W_NVFP4: "e2m1xbf16->f32",
+         abi.W_BF16X: "bf16"}
+ROTATE_BYTES = 1 << 30  # weights touched between two uses of the same copy (L2 is 126 MB)
+
+
+def measured_peak_gbs():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except Exception:
+                continue
+            for name, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# The reference's CPU backend (oracle/_ref) on host arrays: the cpu_baseline leg and the --impl reference arm.
+# ---------------------------------------------------------------------------------------------------------------------
+
+
+def cpu_library():
+    path = os.path.join(ROOT, "oracle", "_ref", "libdromos_cpu.so")
+    return abi.Library(path) if os.path.exists(path) else None
+
+
+def cpu_inputs(wtype, N, K, Ms, copies):
+    """Seeded host inputs in the stored format, quantized by the CPU library itself."""
+    from oracle import dromos_oracle as O
+
+    rng = np.random.default_rng(0)
+    lib = cpu_library()
+    weights = []
+    for _ in range(copies):
+        w = O.f32_to_bf16_bits((rng.standard_normal((N, K), dtype=np.float32) * np.float32(0.02)))
+        if wtype == abi.W_BF16:
+            weights.append((abi.make_weight(wtype, w), w, None))
+        elif wtype == abi.W_BF16X:
+            n = lib.lx_bf16x_bytes(abi.ptr(w), N, K, None)
+            buf = np.zeros(n, dtype=np.uint8)
+            assert lib.lx_bf16x_encode(abi.ptr(w), N, K, abi.ptr(buf), n, None) == 0
+            weights.append((abi.make_weight(wtype, buf), buf, None))
+        else:
+            data = np.zeros(N * (K // 2 if wtype == abi.W_NVFP4 else K), dtype=np.uint8)
+            scale = np.zeros(N * K // 16, dtype=np.uint8) if wtype == abi.W_NVFP4 else np.zeros(N, dtype=np.float32)
+            lw = abi.make_weight(wtype, data, scale)
+            assert lib.lx_quantize_weight(abi.ptr(w), ctypes.byref(lw), N, K, None) == 0
+            weights.append((lw, data, scale))
+    xs = {M: O.f32_to_bf16_bits(rng.standard_normal((M, K), dtype=np.float32)) for M in Ms}
+    ys = {M: np.zeros((M, N), dtype=np.float32) for M in Ms}
+    return lib, weights, xs, ys
+
+
+def cpu_step(lib, weights, xs, ys, N, K, Ms, i):
+    for j, M in enumerate(Ms):
+        lw = weights[(i * len(Ms) + j) % len(weights)][0]
+        if M <= 8:
+            st = lib.lx_gemv_w(abi.ptr(xs[M]), abi.BF16, K, ctypes.byref(lw), None, abi.BF16, abi.ptr(ys[M]), abi.F32, N, M, N, K,
+                               1.0, 0.0, None)
+        else:
+            st = lib.lx_gemm_w(abi.ptr(xs[M]), abi.BF16, K, ctypes.byref(lw), abi.MATH_BF16, None, abi.BF16, abi.ptr(ys[M]), abi.F32,
+                               N, M, N, K, 1.0, 0.0, None, None)
+        assert st == 0, st
+
+
+def weight_bytes(wtype, N, K, bf16x_bytes=None):
+    from oracle import dromos_oracle as O
+
+    return O.weight_bytes(wtype, N, K, bf16x_bytes)
+
+
+def run_cpu(wtype, N, K, Ms, steps, warmup, bf16x_bytes=None):
+    """Times `steps` steps of the reference CPU backend; returns (TB/s, ms per step, cores, sample text)."""
+    one = weight_bytes(wtype, N, K, bf16x_bytes)
+    copies = max(3, min(8, -(-(256 << 20) // one)))  # rotate at least 256 MiB so reads come from DRAM
+    lib, weights, xs, ys = cpu_inputs(wtype, N, K, Ms, copies)
+    for i in range(warmup):
+        cpu_step(lib, weights, xs, ys, N, K, Ms, i)
+    t0 = time.perf_counter()
+    for i in range(steps):
+        cpu_step(lib, weights, xs, ys, N, K, Ms, warmup + i)
+    dt = time.perf_counter() - t0
+    cores = os.cpu_count() or 1
+    tbs = one * len(Ms) * steps / dt / 1e12
+    return tbs, dt / steps * 1e3, cores, f"{steps} steps of the full workload ({len(Ms)} products each), {copies} weight copies rotated"
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2_int8", choices=sorted(WORKLOADS))
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    wtype, N, K, Ms, desc = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    metric = "decode matmul effective HBM TB/s"
+    config = {"workload": desc, "rotation": "weight copies >= 1 GiB between reuses (inputs larger than L2)",
+              "parallelism": f"rows of W split over {world} GPU(s), all-gather of y" if world > 1 else "single GPU"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        if cpu_library() is None:
+            print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libdromos_cpu.so is not built (make -C oracle ref)"}))
+            return
+        steps = max(1, min(args.steps, 20))
+        tbs, ms, cores, sample = run_cpu(wtype, N, K, Ms, steps, min(args.warmup, 3))
+        print(json.dumps({"impl": "reference", "metric": metric, "value": tbs, "unit": "TB/s", "n_gpus": args.gpus, "steps": steps,
+                          "warmup": min(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                          "vs_baseline": None, "dtype": DTYPE[wtype], "data": "synthetic", "config": config,
+                          "cpu_baseline": {"value": tbs, "unit": "TB/s", "cores": cores, "kind": "reference", "sample": sample},
+                          "e2e": {"value": tbs, "unit": "TB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from dromos_b200 import host
+
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib = abi.Library()  # raises when the CUDA library is missing: there is no other path
+    dev = torch.device("cuda", local)
+
+    # ---- synthetic weights: the same seeded matrix on every rank, each rank keeps its rows ----
+    n0, n1 = host.shard_rows(N, rank, world)
+    gen = torch.Generator(device=dev).manual_seed(0)
+    w_full = (torch.randn((N, K), generator=gen, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    w_shard = w_full[n0:n1].contiguous()
+    del w_full
+    first = host.store_weight(lib, w_shard, wtype)
+    shard_bytes = first.nbytes()
+    copies = max(3, -(-ROTATE_BYTES // (shard_bytes * len(Ms))) * len(Ms))
+    stored = [first]
+    for _ in range(copies - 1):
+        stored.append(host.StoredWeight(wtype, first.data.clone(), None if first.scale is None else first.scale.clone(), first.glob,
+                                        rows=first.rows, cols=first.cols))
+    layers = [host.Linear(lib, s, n1 - n0, K) for s in stored]
+    xs = {M: torch.randn((M, K), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16) for M in Ms}
+    ys = {M: torch.empty((M, n1 - n0), dtype=torch.float32, device=dev) for M in Ms}
+    gathered = {M: torch.empty((world, M, n1 - n0), dtype=torch.float32, device=dev) for M in Ms} if world > 1 else None
+    # whole-job bytes a step streams: every shard of every product (all ranks' shards are the same size up to rounding)
+    total_step_bytes = torch.tensor([float(shard_bytes * len(Ms))], device=dev)
+    if world > 1:
+        dist.all_reduce(total_step_bytes)
+    total_step_bytes = float(total_step_bytes.item())
+
+    def step(i):
+        for j, M in enumerate(Ms):
+            layers[(i * len(Ms) + j) % copies](xs[M], ys[M])
+            if world > 1:
+                dist.all_gather_into_tensor(gathered[M], ys[M])
+
+    def timed(fn, n):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(n):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for i in range(args.warmup):
+        step(i)
+    launches0 = lib.lx_b200_kernel_launches()
+    with ClockSampler(local) as clocks:
+        ms = timed(lambda i: step(args.warmup + i), args.steps)
+    launches = lib.lx_b200_kernel_launches() - launches0
+    value = total_step_bytes * args.steps / (ms * 1e-3) / 1e12
+
+    # ---- the streaming kernel alone, per M (events on the launching stream, no collective) ----
+    per_m, k_bytes, k_ms = {}, 0.0, 0.0
+    reps = max(10, min(200, int(2e9 // shard_bytes)))
+    for M in Ms:
+        def one(i, M=M):
+            layers[i % copies](xs[M], ys[M])
+        for i in range(3):
+            one(i)
+        t = timed(one, reps) / reps
+        per_m[str(M)] = {"us": t * 1e3, "GB/s": shard_bytes / (t * 1e-3) / 1e9}
+        k_bytes += shard_bytes
+        k_ms += t
+    peak, peak_kind = measured_peak_gbs()
+    achieved = k_bytes / (k_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                "peak_source": f"{peak_kind} copy bandwidth (burst)", "kernel": "stream_kernel", "per_m": per_m,
+                "algorithmic_bytes_per_launch": shard_bytes}
+
+    # ---- end to end through the host-buffer API: pinned activations in, outputs out, every step ----
+    xh = {M: xs[M].cpu().pin_memory() for M in Ms}
+    yh = {M: torch.empty((M, (n1 - n0) * (world if world > 1 else 1)), dtype=torch.float32).pin_memory() for M in Ms}
+    xd = {M: torch.empty_like(xs[M]) for M in Ms}
+
+    def e2e_step(i):
+        for j, M in enumerate(Ms):
+            xd[M].copy_(xh[M], non_blocking=True)
+            layers[(i * len(Ms) + j) % copies](xd[M], ys[M])
+            if world > 1:
+                dist.all_gather_into_tensor(gathered[M], ys[M])
+                yh[M].copy_(gathered[M].permute(1, 0, 2).reshape(M, -1), non_blocking=True)
+            else:
+                yh[M].copy_(ys[M], non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller reads the result before the next step
+
+    for i in range(3):
+        e2e_step(i)
+    e2e_ms = timed(e2e_step, args.steps)
+    e2e = {"value": total_step_bytes * args.steps / (e2e_ms * 1e-3) / 1e12, "unit": "TB/s",
+           "h2d_bytes_per_step": sum(M * K * 2 for M in Ms), "d2h_bytes_per_step": sum(M * N * 4 for M in Ms)}
+
+    status = lib.lx_b200_last_error()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    out = {"metric": metric, "value": value, "unit": "TB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+           "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+           "vs_baseline": None, "dtype": DTYPE[wtype], "data": "synthetic", "config": config, "roofline": roofline, "e2e": e2e,
+           "gpu_launches": int(launches), "clocks": clocks.summary(), "pct_of_8TBs": value / 8.0 / max(world, 1),
+           "kernel_status": status}
+    if world == 1:
+        if cpu_library() is not None:
+            bx = shard_bytes if wtype == abi.W_BF16X else None
+            tbs, _, cores, sample = run_cpu(wtype, N, K, Ms, 8, 2, bx)
+            out["cpu_baseline"] = {"value": tbs, "unit": "TB/s", "cores": cores, "kind": "reference", "sample": sample}
+        else:
+            out["cpu_baseline"] = {"value": None, "unit": "TB/s", "cores": os.cpu_count(), "kind": "reference",
+                                   "sample": "oracle/_ref/libdromos_cpu.so not built"}
+    print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,269 @@
+"""Host-side mirror of the reference's operator interface for the decode weight-streaming path.
+
+The reference engine reaches the path through three calls of its backend ABI (lernex/dromos
+engine/model/metis.cpp:1232-1310): `linear()` picks lx_gemv_w for M <= 8 rows (in chunks of 8) and lx_gemm_w above,
+and `routed_experts()` picks lx_moe_experts_grouped for more than 8 tokens. The classes here make the same choices
+on top of the C ABI of this package's library, own the device buffers a caller of the engine would own (weights,
+workspaces), and add what the reference does not have: weights sharded by output rows over the ranks of a
+torch.distributed group (each rank streams N / G rows, the slices meet in an all-gather) and experts sharded over
+ranks (each rank runs the experts it owns on the tokens routed to them; per-pair rows return to every rank and are
+summed in k order).
+
+torch is used for device memory, streams and the process group only. Nothing here computes a product on the host.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import abi
+
+GEMV_MAX_ROWS = 8  # lx_gemv_w takes at most 8 activation rows (engine/cuda/gemv.cu:59)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class StoredWeight:
+    """A weight in one stored format on the device: the buffers and the lx_weight that points at them."""
+
+    def __init__(self, wtype: int, data: torch.Tensor, scale: torch.Tensor | None = None, glob: float = 1.0,
+                 expert_global: torch.Tensor | None = None, rows: int = 0, cols: int = 0):
+        self.wtype, self.data, self.scale, self.glob, self.expert_global = wtype, data, scale, float(glob), expert_global
+        self.rows, self.cols = rows, cols
+        self.struct = abi.make_weight(wtype, data, scale, glob, expert_global)
+
+    def ref(self):
+        return ctypes.byref(self.struct)
+
+    def nbytes(self) -> int:
+        """Bytes a product streams from this weight: values and their scales (the reference's accounting,
+        bench/bench_gemv.py:51-56)."""
+        n = self.data.numel() * self.data.element_size()
+        if self.scale is not None:
+            n += self.scale.numel() * self.scale.element_size()
+        return n + (4 if self.wtype == abi.W_NVFP4 else 0)
+
+
+def store_weight(lib: abi.Library, w_bf16: torch.Tensor, wtype: int) -> StoredWeight:
+    """Converts a bf16 [rows, cols] (or stacked [E, rows, cols]) device tensor into a stored format with the library's
+    own load-time entry points (lx_quantize_weight / lx_bf16x_encode)."""
+    assert w_bf16.is_cuda and w_bf16.dtype == torch.bfloat16 and w_bf16.is_contiguous()
+    cols = w_bf16.shape[-1]
+    rows = w_bf16.numel() // cols
+    if wtype == abi.W_BF16:
+        return StoredWeight(wtype, w_bf16, rows=rows, cols=cols)
+    if wtype == abi.W_BF16X:
+        n = lib.lx_bf16x_bytes(abi.ptr(w_bf16), rows, cols, _stream())
+        if n <= 0:
+            raise RuntimeError(f"lx_bf16x_bytes failed: {n}")
+        data = torch.empty(n, dtype=torch.uint8, device=w_bf16.device)
+        st = lib.lx_bf16x_encode(abi.ptr(w_bf16), rows, cols, abi.ptr(data), n, _stream())
+        if st:
+            raise RuntimeError(f"lx_bf16x_encode failed: {st}")
+        return StoredWeight(wtype, data, rows=rows, cols=cols)
+    if wtype == abi.W_NVFP4:
+        data = torch.empty(rows * cols // 2, dtype=torch.uint8, device=w_bf16.device)
+        scale = torch.empty(rows * cols // 16, dtype=torch.uint8, device=w_bf16.device)
+    else:
+        data = torch.empty(rows * cols, dtype=torch.uint8, device=w_bf16.device)
+        scale = torch.empty(rows, dtype=torch.float32, device=w_bf16.device)
+    lw = abi.make_weight(wtype, data, scale)
+    st = lib.lx_quantize_weight(abi.ptr(w_bf16), ctypes.byref(lw), rows, cols, _stream())
+    if st:
+        raise RuntimeError(f"lx_quantize_weight failed: {st}")
+    return StoredWeight(wtype, data, scale, lw.glob, rows=rows, cols=cols)
+
+
+class Linear:
+    """y = x @ W^T for one stored weight [N, K], choosing the entry point as the engine's linear() does."""
+
+    def __init__(self, lib: abi.Library, weight: StoredWeight, N: int, K: int):
+        self.lib, self.weight, self.N, self.K = lib, weight, N, K
+        self._ws = None
+
+    def __call__(self, x: torch.Tensor, y: torch.Tensor | None = None) -> torch.Tensor:
+        """x: bf16 or f32 [M, K] on the device; y: f32 [M, N] (allocated when absent)."""
+        M = x.shape[0]
+        if y is None:
+            y = torch.empty((M, self.N), dtype=torch.float32, device=x.device)
+        x_dt = abi.BF16 if x.dtype == torch.bfloat16 else abi.F32
+        y_dt = abi.BF16 if y.dtype == torch.bfloat16 else abi.F32
+        ld_x, ld_y = x.stride(0), y.stride(0)
+        if M <= GEMV_MAX_ROWS or self.weight.wtype == abi.W_BF16X:
+            for m0 in range(0, M, GEMV_MAX_ROWS):  # chunks of 8 rows (metis.cpp:1234-1253)
+                mc = min(GEMV_MAX_ROWS, M - m0)
+                st = self.lib.lx_gemv_w(abi.ptr(x[m0:]), x_dt, ld_x, self.weight.ref(), None, abi.BF16, abi.ptr(y[m0:]), y_dt,
+                                        ld_y, mc, self.N, self.K, 1.0, 0.0, _stream())
+                if st:
+                    raise RuntimeError(f"lx_gemv_w failed: {st}")
+            return y
+        need = self.lib.lx_gemm_workspace_bytes(M, self.K, abi.MATH_BF16)
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = torch.empty(max(need, 256), dtype=torch.uint8, device=x.device)
+        st = self.lib.lx_gemm_w(abi.ptr(x), x_dt, ld_x, self.weight.ref(), abi.MATH_BF16, None, abi.BF16, abi.ptr(y), y_dt, ld_y,
+                                M, self.N, self.K, 1.0, 0.0, abi.ptr(self._ws), _stream())
+        if st:
+            raise RuntimeError(f"lx_gemm_w failed: {st}")
+        return y
+
+
+def shard_rows(N: int, rank: int, world: int) -> tuple[int, int]:
+    """The contiguous range of output rows rank `rank` of `world` owns: [n0, n1)."""
+    return N * rank // world, N * (rank + 1) // world
+
+
+class ShardedLinear:
+    """A Linear whose rows are split over the ranks of a process group. Each rank holds rows [n0, n1) of the weight (with
+    their scales; a BF16X shard is encoded on its own), multiplies the replicated activations by them and the slices
+    meet in an all-gather: no collective touches the weight stream."""
+
+    def __init__(self, lib, w_bf16_shard: torch.Tensor, wtype: int, N: int, K: int, group=None):
+        import torch.distributed as dist
+
+        self.dist, self.group = dist, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.N, self.K = N, K
+        self.n0, self.n1 = shard_rows(N, self.rank, self.world)
+        assert w_bf16_shard.shape == (self.n1 - self.n0, K)
+        self.local = Linear(lib, store_weight(lib, w_bf16_shard, wtype), self.n1 - self.n0, K)
+        self.uniform = N % self.world == 0
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        M = x.shape[0]
+        y_local = self.local(x)  # [M, N / G]
+        if self.world == 1:
+            return y_local
+        if self.uniform:
+            gathered = torch.empty((self.world, M, self.n1 - self.n0), dtype=y_local.dtype, device=y_local.device)
+            self.dist.all_gather_into_tensor(gathered, y_local, group=self.group)
+            return gathered.permute(1, 0, 2).reshape(M, self.N)
+        parts = [torch.empty((M, shard_rows(self.N, r, self.world)[1] - shard_rows(self.N, r, self.world)[0]),
+                             dtype=y_local.dtype, device=y_local.device) for r in range(self.world)]
+        self.dist.all_gather(parts, y_local, group=self.group)
+        return torch.cat(parts, dim=1)
+
+
+class Experts:
+    """Routed experts on stored stacks gate_up [E, 2I, L] and down [E, L, I] (lx_moe_route + lx_moe_experts_grouped)."""
+
+    def __init__(self, lib, gate_up: StoredWeight, down: StoredWeight, E: int, L: int, I: int, top_k: int):
+        self.lib, self.gate_up, self.down, self.E, self.L, self.I, self.top_k = lib, gate_up, down, E, L, I, top_k
+        self._ws = None
+
+    def route(self, logits: torch.Tensor, bias: torch.Tensor | None = None):
+        T = logits.shape[0]
+        ids = torch.empty((T, self.top_k), dtype=torch.int32, device=logits.device)
+        weights = torch.empty((T, self.top_k), dtype=torch.float32, device=logits.device)
+        st = self.lib.lx_moe_route(abi.ptr(logits), abi.ptr(bias), abi.ptr(ids), abi.ptr(weights), None, None, T,
+                                   logits.shape[1], self.top_k, _stream())
+        if st:
+            raise RuntimeError(f"lx_moe_route failed: {st}")
+        return ids, weights
+
+    def __call__(self, latent: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, out: torch.Tensor | None = None):
+        T = latent.shape[0]
+        if out is None:
+            out = torch.empty((T, self.L), dtype=torch.float32, device=latent.device)
+        need = self.lib.lx_moe_grouped_workspace_bytes(T, self.L, self.I, self.E, self.top_k, abi.MATH_BF16)
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = torch.empty(need, dtype=torch.uint8, device=latent.device)
+        st = self.lib.lx_moe_experts_grouped(abi.ptr(latent), abi.ptr(ids), abi.ptr(weights), self.gate_up.ref(), self.down.ref(),
+                                             abi.MATH_BF16, abi.ptr(out), abi.ptr(self._ws), T, self.L, self.I, self.E,
+                                             self.top_k, _stream())
+        if st:
+            raise RuntimeError(f"lx_moe_experts_grouped failed: {st}")
+        return out
+
+
+def expert_range(E: int, rank: int, world: int) -> tuple[int, int]:
+    return E * rank // world, E * (rank + 1) // world
+
+
+def remap_for_owner(ids: torch.Tensor, weights: torch.Tensor, e0: int, e1: int):
+    """The routing as the owner of experts [e0, e1) sees it: pairs routed elsewhere keep a valid local expert id but
+    weight zero, so they add nothing; owned pairs keep their weight. Pure index arithmetic (also used by the CPU tests)."""
+    mine = (ids >= e0) & (ids < e1)
+    local_ids = torch.where(mine, ids - e0, torch.zeros_like(ids))
+    local_w = torch.where(mine, weights, torch.zeros_like(weights))
+    return local_ids, local_w, mine
+
+
+class ExpertParallel:
+    """Experts split over ranks: rank g holds experts [g E / G, (g + 1) E / G). Tokens are split over ranks too (rank g
+    is home to tokens [g T / G, (g + 1) T / G)); the routed rows are exchanged with one all-to-all each way:
+
+      dispatch  every rank sends each peer the latent rows of its own tokens that route to that peer's experts, with
+                the pair's local expert id, weight and home position;
+      compute   the owner runs its experts on the rows it received (one pair per row, top_k = 1);
+      combine   the weighted rows go back to the token's home rank, which adds each token's top_k rows in k order.
+
+    Routing itself is replicated: every rank computes lx_moe_route on its own tokens' logits."""
+
+    def __init__(self, lib, gate_up_local: StoredWeight, down_local: StoredWeight, E: int, L: int, I: int, top_k: int, group=None):
+        import torch.distributed as dist
+
+        self.dist, self.group = dist, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.E, self.L, self.I, self.top_k = E, L, I, top_k
+        self.e0, self.e1 = expert_range(E, self.rank, self.world)
+        # the owner sees one (expert, weight) pair per received row
+        self.local = Experts(lib, gate_up_local, down_local, self.e1 - self.e0, L, I, 1)
+
+    def plan(self, ids: torch.Tensor):
+        """Which of this rank's (token, k) pairs go to which rank, in destination order. Returns (order, counts): `order`
+        lists pair indices sorted by destination rank (stable), counts[r] how many go to rank r."""
+        flat = ids.reshape(-1).to(torch.int64)
+        dest = torch.zeros_like(flat)
+        for r in range(1, self.world):
+            dest += (flat >= expert_range(self.E, r, self.world)[0]).to(torch.int64)
+        order = torch.sort(dest, stable=True).indices
+        counts = torch.bincount(dest, minlength=self.world)
+        return order, counts
+
+    def __call__(self, latent: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+        """latent bf16 [T_local, L], ids / weights [T_local, top_k] of this rank's tokens -> f32 [T_local, L]."""
+        dist, W = self.dist, self.world
+        T, k = ids.shape
+        order, counts = self.plan(ids)
+        send_counts = counts.tolist()
+        recv_counts_t = torch.empty_like(counts)
+        if W > 1:
+            dist.all_to_all_single(recv_counts_t, counts, group=self.group)
+        else:
+            recv_counts_t = counts.clone()
+        recv_counts = recv_counts_t.tolist()
+        n_send, n_recv = sum(send_counts), sum(recv_counts)
+        tok = torch.div(order, k, rounding_mode="floor")
+        send_rows = latent[tok].contiguous()                                   # [n_send, L] bf16
+        send_meta = torch.stack([ids.reshape(-1)[order].to(torch.float32), weights.reshape(-1)[order]], dim=1).contiguous()
+        recv_rows = torch.empty((n_recv, self.L), dtype=latent.dtype, device=latent.device)
+        recv_meta = torch.empty((n_recv, 2), dtype=torch.float32, device=latent.device)
+        if W > 1:
+            dist.all_to_all_single(recv_rows, send_rows, recv_counts, send_counts, group=self.group)
+            dist.all_to_all_single(recv_meta, send_meta, recv_counts, send_counts, group=self.group)
+        else:
+            recv_rows, recv_meta = send_rows, send_meta
+        out_rows = torch.zeros((n_recv, self.L), dtype=torch.float32, device=latent.device)
+        if n_recv:
+            local_ids = (recv_meta[:, 0].to(torch.int32) - self.e0).reshape(n_recv, 1).contiguous()
+            local_w = recv_meta[:, 1].reshape(n_recv, 1).contiguous()
+            self.local(recv_rows, local_ids, local_w, out_rows)
+        back = torch.empty((n_send, self.L), dtype=torch.float32, device=latent.device)
+        if W > 1:
+            dist.all_to_all_single(back, out_rows, send_counts, recv_counts, group=self.group)
+        else:
+            back = out_rows
+        # back[i] belongs to pair order[i]; add each token's rows in k order (fixed order: deterministic)
+        per_pair = torch.empty((T * k, self.L), dtype=torch.float32, device=latent.device)
+        per_pair[order] = back
+        per_pair = per_pair.reshape(T, k, self.L)
+        out = per_pair[:, 0].clone()
+        for j in range(1, k):
+            out += per_pair[:, j]
+        return out
