@@ -369,6 +369,9 @@ __global__ void __launch_bounds__(32 * NW + 32, 1)
   // =========================================================================================================
   if (warp == NW) {
     pdl_trigger();
+    // Expert tiles are laid out by the grouping tables, which the previous kernel in the stream wrote: wait for it.
+    // (A dense product reads nothing but the weight here and starts streaming at once.)
+    if constexpr (MODE != kDense) pdl_wait();
     const int hb = C::kX16 ? x16::header_bytes(K) : 0;
     if (P.tiled && lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
