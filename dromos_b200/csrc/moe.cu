@@ -11,6 +11,7 @@
 // Every stage reads each chosen expert's weights once; no float atomics anywhere, so a token's bits do not depend on
 // the batch or the run.
 #include <algorithm>
+#include <mutex>
 
 #include "launch.cuh"
 #include "scalar.cuh"
@@ -297,7 +298,7 @@ int launch_expert_stage(const StreamParams& P, int type, cudaStream_t s, int64_t
 int run_experts(const void* latent, const int32_t* ids, const float* weights, const lx_weight& gate_up, const lx_weight& down,
                 float* out,
                 uint8_t* ws, const Layout& l, bool indirect, int groups, int experts, int T, int L, int I, int top_k,
-                cudaStream_t s) {
+                cudaStream_t s, int* status = nullptr) {
   StreamParams g{};
   g.w = static_cast<const uint8_t*>(gate_up.data);
   g.scale = static_cast<const uint8_t*>(gate_up.scale);
@@ -314,7 +315,7 @@ int run_experts(const void* latent, const int32_t* ids, const float* weights, co
   g.route_w = weights;
   g.top_k = top_k, g.I = I;
   g.moe_out = ws + l.mid;
-  g.status = status_word();
+  g.status = status ? status : status_word();
   // weights the streaming kernel cannot take run both stages on the scalar kernels (intermediate rows by pair index)
   const bool fast_gu = stack_streams(gate_up, L) && stack_streams(down, I), fast_dn = fast_gu;
   if (int e = fast_gu ? launch_expert_stage<kGateUp>(g, gate_up.type, s, static_cast<int64_t>(experts) * 2 * I)
@@ -381,4 +382,68 @@ extern "C" int lx_moe_experts_grouped(const void* latent, const int32_t* ids, co
                             reinterpret_cast<int32_t*>(ws + l.pairs)))
     return e;
   return run_experts(latent, ids, weights, *gate_up, *down, out, ws, l, false, E, E, T, L, I, top_k, s);
+}
+
+// ---- the same routed experts with no allocation anywhere -------------------------------------------------------------
+// Some callers cannot let a library allocate: a server that has already handed every free byte of device memory to its
+// own arena (so a later cudaMalloc fails or evicts), or a decode loop that is forbidden to enter the driver's allocator
+// because that takes a device-wide lock at an unpredictable moment. For them the scratch of lx_moe_experts_grouped
+// (grouping tables, the bf16 intermediate, the per-pair rows) lives in a fixed array inside the library image instead of
+// a caller workspace. Every GPU that loads the library holds these kStaticScratchBytes until the process exits.
+constexpr int64_t kStaticScratchBytes = 8ll << 20;
+constexpr int64_t kStaticHeaderBytes = 256;  // the first bytes hold this entry point's kernel status word
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+// In host code `g_static_scratch` is only a handle: the address kernels can use comes from cudaGetSymbolAddress, asked
+// once per device with that device current.
+int static_scratch(uint8_t** ptr) {
+  static std::mutex mu;
+  static uint8_t* base[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return static_cast<int>(cudaGetLastError());
+  dev &= 63;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!base[dev]) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return static_cast<int>(e);
+    }
+    base[dev] = static_cast<uint8_t*>(p);
+  }
+  *ptr = base[dev];
+  return kOk;
+}
+}  // namespace
+
+extern "C" int64_t lx_b200_moe_static_scratch_bytes(void) { return kStaticScratchBytes - kStaticHeaderBytes; }
+
+extern "C" int lx_b200_moe_experts_grouped_static(const void* latent, const int32_t* ids, const float* weights,
+                                                  const lx_weight* gate_up, const lx_weight* down, lx_math math, float* out,
+                                                  int T, int L, int I, int E, int top_k, void* stream) {
+  if (T < 0 || L <= 0 || I <= 0 || E <= 0 || top_k <= 0 || top_k > E || !gate_up || !down) return kInvalid;
+  if (math < LX_MATH_BF16 || math > LX_MATH_FP4) return kInvalid;
+  if (T == 0) return kOk;
+  if (!latent || !ids || !weights || !out || !gate_up->data || !down->data) return kInvalid;
+  if ((gate_up->type != LX_W_BF16 && !gate_up->scale) || (down->type != LX_W_BF16 && !down->scale)) return kInvalid;
+  if (E > kMaxExperts || static_cast<int64_t>(T) * top_k > (1ll << 30)) return kNotSupported;
+  if (gate_up->type < LX_W_BF16 || gate_up->type > LX_W_NVFP4 || down->type < LX_W_BF16 || down->type > LX_W_NVFP4)
+    return kNotSupported;
+  if (math != LX_MATH_BF16) return kNotSupported;
+  if (I % 8 != 0 || L % 8 != 0) return kNotSupported;
+  if (gate_up->type == LX_W_NVFP4 && (L % 16 != 0 || I % 16 != 0)) return kInvalid;
+  const int P = T * top_k;
+  const Layout l = layout(P, E, L, I);
+  if (l.total > kStaticScratchBytes - kStaticHeaderBytes) return LX_B200_ERR_SCRATCH;  // larger than the fixed array
+  uint8_t* base = nullptr;
+  if (int e = static_scratch(&base)) return e;
+  auto s = static_cast<cudaStream_t>(stream);
+  uint8_t* ws = base + kStaticHeaderBytes;
+  if (int e = launch_kernel(group_kernel, dim3(1), dim3(1024), 0, s, ids, P, E, reinterpret_cast<int32_t*>(ws + l.offsets),
+                            reinterpret_cast<int32_t*>(ws + l.pairs)))
+    return e;
+  return run_experts(latent, ids, weights, *gate_up, *down, out, ws, l, false, E, E, T, L, I, top_k, s,
+                     reinterpret_cast<int*>(base));
 }

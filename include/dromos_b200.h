@@ -163,6 +163,22 @@ LX_API int64_t lx_b200_kernel_launches(void);
  * Synchronizes the device. */
 LX_API int lx_b200_last_error(void);
 
+/* Routed experts for callers that must not allocate. No counterpart in the reference: its lx_moe_experts_grouped always
+ * takes a caller workspace. Same arguments, result and error codes as lx_moe_experts_grouped above minus the workspace:
+ * the scratch is a fixed 8 MiB array inside the library image, of which lx_b200_moe_static_scratch_bytes() are usable
+ * (every GPU that loads the library holds the array until the process exits). A call whose scratch need,
+ * lx_moe_grouped_workspace_bytes(T, L, I, E, top_k, math), exceeds that returns LX_B200_ERR_SCRATCH and launches
+ * nothing. The call itself allocates nothing: no cudaMalloc, no cudaFree, no stream-ordered pool. The first call on
+ * each device looks the array's device address up (cudaGetSymbolAddress, with that device current) and keeps it; make
+ * that first call outside any stream capture. All calls on a device share the one array, which keeps whatever the last
+ * call left in it (nothing in it needs to start at zero): calls that overlap on the GPU, on any streams, race on it and
+ * are the caller's to serialize. */
+#define LX_B200_ERR_SCRATCH 804
+LX_API int lx_b200_moe_experts_grouped_static(const void* latent, const int32_t* ids, const float* weights,
+                                              const lx_weight* gate_up, const lx_weight* down, lx_math math, float* out,
+                                              int T, int L, int I, int E, int top_k, void* stream);
+LX_API int64_t lx_b200_moe_static_scratch_bytes(void);
+
 #ifdef __cplusplus
 }
 #endif
