@@ -246,7 +246,7 @@ def main():
         for j, M in enumerate(Ms):
             layers[(i * len(Ms) + j) % copies](xs[M], ys[M])
             if world > 1:
-                dist.all_gather_into_tensor(gathered[M], ys[M])
+                dist.all_gather_into_tensor(gathered[M].view(world * M, n1 - n0), ys[M])
 
     def timed(fn, n):
         if world > 1:
@@ -299,7 +299,7 @@ def main():
             xd[M].copy_(xh[M], non_blocking=True)
             layers[(i * len(Ms) + j) % copies](xd[M], ys[M])
             if world > 1:
-                dist.all_gather_into_tensor(gathered[M], ys[M])
+                dist.all_gather_into_tensor(gathered[M].view(world * M, n1 - n0), ys[M])
                 yh[M].copy_(gathered[M].permute(1, 0, 2).reshape(M, -1), non_blocking=True)
             else:
                 yh[M].copy_(ys[M], non_blocking=True)

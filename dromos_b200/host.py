@@ -140,7 +140,7 @@ class ShardedLinear:
             return y_local
         if self.uniform:
             gathered = torch.empty((self.world, M, self.n1 - self.n0), dtype=y_local.dtype, device=y_local.device)
-            self.dist.all_gather_into_tensor(gathered, y_local, group=self.group)
+            self.dist.all_gather_into_tensor(gathered.view(self.world * M, self.n1 - self.n0), y_local, group=self.group)
             return gathered.permute(1, 0, 2).reshape(M, self.N)
         parts = [torch.empty((M, shard_rows(self.N, r, self.world)[1] - shard_rows(self.N, r, self.world)[0]),
                              dtype=y_local.dtype, device=y_local.device) for r in range(self.world)]

@@ -1,0 +1,55 @@
+"""The C-ABI library loads without a GPU and exports every symbol include/dromos_b200.h declares, with the bindings of
+dromos_b200/abi.py covering each of them. No compute call is made here."""
+
+import os
+import re
+
+from dromos_b200 import abi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "dromos_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"LX_API[^;(]*?\b(lx_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = abi.Library(abi.default_library_path())
+    names = declared_symbols()
+    assert len(names) >= 30
+    for name in names:
+        assert lib.has(name), f"{name} is declared in include/dromos_b200.h but not exported"
+        lib.fn(name)  # and bound with a signature
+
+
+def test_no_binding_without_a_declaration():
+    names = set(declared_symbols())
+    for name in list(abi.SIGNATURES) + list(abi.EXTENSIONS):
+        assert name in names, f"{name} is bound in abi.py but not declared in the header"
+
+
+def test_host_only_entry_points_answer_without_a_gpu():
+    lib = abi.Library(abi.default_library_path())
+    assert lib.lx_rt_backend() == 0
+    assert lib.lx_bf16x_row_bytes(4096) == 6192 and lib.lx_bf16x_row_bytes(0) == -1
+    assert lib.lx_gemm_workspace_bytes(0, 4096, 0) == 0 and lib.lx_gemm_workspace_bytes(32, 4096, 0) > 0
+    assert lib.lx_moe_grouped_workspace_bytes(32, 4096, 1536, 64, 8, 0) > 0
+    n = lib.lx_tune_kernels(None, 0)
+    assert n == 5
+    assert lib.lx_tune_variants(b"gemv_w_fp8") >= 1 and lib.lx_tune_variants(b"nope") == 0
+    assert re.match(rb"s\d+", lib.lx_tune_variant_name(b"gemv_w_fp8", 0))
+    assert lib.lx_tune_set(b"gemv_w_fp8", 1, 64, 64, 10**6) == abi.ERR_TUNE_VARIANT
+    assert lib.lx_tune_set(b"gemv_w_fp8", 3, 64, 64, 1) == 0 and lib.lx_tune_get(b"gemv_w_fp8", 4, 64, 64) == 1  # M bucket 4
+    lib.lx_tune_clear()
+    assert lib.lx_tune_get(b"gemv_w_fp8", 4, 64, 64) == -1
+
+
+def test_product_never_imports_the_oracle():
+    pkg = os.path.join(ROOT, "dromos_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.replace("# oracle", ""), f"{f} mentions the oracle"
