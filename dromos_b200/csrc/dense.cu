@@ -230,13 +230,13 @@ ActLayout act_layout(int M, int K, int math) {
 
 extern "C" int64_t lx_gemm_workspace_bytes(int M, int K, lx_math math) {
   if (M <= 0 || K <= 0) return 0;
-  return act_layout(M, K, math).total;
+  // the reference's layout, or what the prepared activations of the tensor-core product take, whichever is larger
+  return std::max(act_layout(M, K, math).total, tc_prep_bytes(std::min(M, 32), K, false));
 }
 
 extern "C" int lx_gemm_w(const void* x, lx_dtype x_dtype, int ld_x, const lx_weight* w, lx_math math, const void* bias,
                          lx_dtype bias_dtype, void* y, lx_dtype y_dtype, int ld_y, int M, int N, int K, float alpha,
                          float beta, void* workspace, void* stream) {
-  (void)workspace;
   if (M < 0 || N < 0 || K <= 0 || ld_x < K || ld_y < N || !w) return kInvalid;
   if (M == 0 || N == 0) return kOk;
   if (!x || !y || !w->data) return kInvalid;
@@ -248,6 +248,14 @@ extern "C" int lx_gemm_w(const void* x, lx_dtype x_dtype, int ld_x, const lx_wei
   // Weight rows must be whole 16-byte chunks, as for the reference's tensor-core kernels.
   const int64_t rowb = row_bytes_of(w->type, K);
   if (rowb % 16 != 0 || !aligned(w->data, 16) || (w->type == LX_W_NVFP4 && K % 64 != 0)) return kNotSupported;
+  // More than 8 rows with a workspace: the tcgen05 product (LX_B200_TC=0 keeps the mma.sync streaming kernel).
+  static const bool tc_on = [] {
+    const char* v = std::getenv("LX_B200_TC");
+    return !(v && v[0] == '0');
+  }();
+  if (tc_on && M > 8 && workspace && aligned(workspace, 16) && (w->type != LX_W_NVFP4 || (K % 256 == 0 && aligned(w->scale, 16))))
+    return tc_product(x, x_dtype, ld_x, *w, bias, bias_dtype, y, y_dtype, ld_y, M, N, K, alpha, beta, workspace,
+                      static_cast<cudaStream_t>(stream));
   return dense_product(x, x_dtype, ld_x, *w, bias, bias_dtype, y, y_dtype, ld_y, M, N, K, alpha, beta,
                        static_cast<cudaStream_t>(stream));
 }

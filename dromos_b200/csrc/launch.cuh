@@ -72,9 +72,10 @@ using TensorMapEncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint
 TensorMapEncodeFn tensor_map_encoder();
 
 // A 2-D map over `rows` rows of `row_bytes` bytes each (row pitch = row_bytes, a multiple of 16; base 16-byte aligned),
-// copied in boxes of box_rows x box_bytes. elem_bytes (1 or 4) is the unit the kernel gives x coordinates in.
+// copied in boxes of box_rows x box_bytes. elem_bytes (1 or 4) is the unit the kernel gives x coordinates in. With
+// swizzle128 (boxes 128 bytes wide) the 16-byte pieces of row r land at piece ^ (r % 8).
 inline int make_tile_map(CUtensorMap* map, const void* base, int64_t row_bytes, int64_t rows, int box_bytes, int box_rows,
-                         int elem_bytes) {
+                         int elem_bytes, bool swizzle128 = false) {
   TensorMapEncodeFn encode = tensor_map_encoder();
   if (!encode) return kNotSupported;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_bytes / elem_bytes), static_cast<cuuint64_t>(rows)};
@@ -83,7 +84,7 @@ inline int make_tile_map(CUtensorMap* map, const void* base, int64_t row_bytes, 
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = encode(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
                             const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                            swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? kOk : kInvalid;
 }
 
@@ -153,6 +154,11 @@ int launch_stream(StreamParams P, cudaStream_t stream, int64_t stack_rows) {
   const unsigned grid = static_cast<unsigned>(std::max<int64_t>(1, std::min(units, resident)));
   return launch_kernel(kernel, dim3(grid), dim3(C::kThreads), smem, stream, wmap, smap, P);
 }
+
+// gemm_tc.cu: the tcgen05 product for batched decode rows, and the workspace its prepared activations need.
+int tc_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const void* bias, int bias_dtype, void* y, int y_dtype,
+               int ld_y, int M, int N, int K, float alpha, float beta, void* workspace, cudaStream_t stream);
+int64_t tc_prep_bytes(int M, int K, bool x_bf16);
 
 struct ActLayout {
   int64_t ld_q, ld_bs;
