@@ -231,7 +231,7 @@ ActLayout act_layout(int M, int K, int math) {
 extern "C" int64_t lx_gemm_workspace_bytes(int M, int K, lx_math math) {
   if (M <= 0 || K <= 0) return 0;
   // the reference's layout, or what the prepared activations of the tensor-core product take, whichever is larger
-  return std::max(act_layout(M, K, math).total, tc_prep_bytes(std::min(M, 32), K, false));
+  return std::max(act_layout(M, K, math).total, tc_workspace_bytes(M, K));
 }
 
 extern "C" int lx_gemm_w(const void* x, lx_dtype x_dtype, int ld_x, const lx_weight* w, lx_math math, const void* bias,

@@ -158,7 +158,7 @@ int launch_stream(StreamParams P, cudaStream_t stream, int64_t stack_rows) {
 // gemm_tc.cu: the tcgen05 product for batched decode rows, and the workspace its prepared activations need.
 int tc_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const void* bias, int bias_dtype, void* y, int y_dtype,
                int ld_y, int M, int N, int K, float alpha, float beta, void* workspace, cudaStream_t stream);
-int64_t tc_prep_bytes(int M, int K, bool x_bf16);
+int64_t tc_workspace_bytes(int M, int K);
 
 struct ActLayout {
   int64_t ld_q, ld_bs;

@@ -125,6 +125,23 @@ def test_gemm_w_small_m(lx, fmt, M):
 
 
 @pytest.mark.parametrize("fmt", FORMATS, ids=lambda f: NAMES[f])
+@pytest.mark.parametrize("case", [(16, 264, 4096, False), (24, 1000, 2304, False), (20, 1000, 2304, True), (64, 520, 8192, False)],
+                         ids=lambda c: f"M{c[0]}N{c[1]}K{c[2]}{'f32' if c[3] else ''}")
+def test_gemm_w_tiles_shared_between_ctas(lx, fmt, case):
+    """Shapes whose 128-row tiles are summed from the partial results of several CTAs (stage ranges that start and end
+    inside tiles), with bias, alpha and beta, twice in a row on the same workspace: the two results are bitwise equal."""
+    if fmt == O.W_BF16X:
+        pytest.skip("lx_gemm_w takes BF16X through lx_bf16x_decode in the engine")
+    M, N, K, x_f32 = case
+    outs = []
+    for _ in range(2):
+        got, want, y0 = run(lx, fmt, M, N, K, seed=7, fn="lx_gemm_w", x_f32=x_f32, bias_dtype=abi.F32, alpha=0.5, beta=0.25)
+        check(got, want, y0, N, True, f"{NAMES[fmt]} {case}")
+        outs.append(got.view(np.uint32).copy())
+    assert np.array_equal(outs[0], outs[1]), "two runs differ"
+
+
+@pytest.mark.parametrize("fmt", FORMATS, ids=lambda f: NAMES[f])
 def test_rows_do_not_depend_on_batch_and_runs_repeat(lx, fmt):
     N, K = 256, 2048
     w_bits = util.bf16_normal((N, K), 0.02, 11)
