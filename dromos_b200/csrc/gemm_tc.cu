@@ -22,14 +22,13 @@
 // beta, store). The direct formats keep two accumulators in tensor memory so that the next tile's products run while
 // the epilogue of the last one is still reading.
 //
-// Work is split by STAGE, not by tile: the n_tiles * n_stages stages are dealt out in equal contiguous ranges, one per
-// CTA, so every SM streams the same number of bytes whatever N is. A tile whose stages fall to several CTAs is summed
-// without any CTA waiting for another: each contributor writes its partial accumulator to the workspace and counts
-// itself on the tile's counter; the one that arrives last adds the partials in the fixed order of the ranges (its own
-// included, read back from the workspace) and finishes the tile. The sum therefore does not depend on arrival order.
+// Work is split by ROWS: a tile is R <= 128 weight rows with R chosen so that the tiles divide evenly among the SMs
+// (N = 14336 on 148 SMs: 148 tiles of 97 rows), and a CTA streams its tiles whole, all of K. The tensor core always
+// multiplies 128 rows; the lanes past R hold whatever shared memory held and are never read. Every output element
+// is thus the work of one CTA: no partial sums, no counters, and the same bits whatever the grid.
 //
 // Activations are prepared once per call by a small kernel into the caller's workspace, in the K-major core-matrix
-// order the B descriptor reads. The same kernel clears the tile counters.
+// order the B descriptor reads.
 //
 // Every wait is bounded; a wait that gives up writes a code to the status word and the kernel still frees its TMEM.
 #include <algorithm>
@@ -40,11 +39,10 @@
 namespace b200 {
 namespace {
 
-constexpr int kBM = 128;          // weight rows per tile = TMEM lanes
+constexpr int kBM = 128;          // rows the tensor core multiplies = TMEM lanes; a tile uses the first R of them
 constexpr int kKS = 256;          // values of K per stage
 constexpr int kTmemColumns = 512;
-constexpr int kMaxCtas = 160;     // bound on the grid (one CTA per SM), sizes the counters and the partial slots
-constexpr int kMinStagesPerCta = 4;
+constexpr int kMinTileRows = 32;  // below this the instruction rate of the tensor pipe, not HBM, would bound a stage
 constexpr int kMaxRows = 64;      // activation rows per pass
 constexpr int kStatusTcWait = 5;  // a bounded wait of this kernel gave up
 
@@ -55,6 +53,8 @@ struct TcParams {
   const uint8_t* scale;   // f32 [N] (INT8 / FP8); NVFP4 block scales come through the tensor map
   float global;
   int N, K, M;            // M: activation rows of this pass
+  int R;                  // weight rows per tile
+  int box_bytes;          // shared memory one 128-byte-wide tile copy takes: R rounded up to 8, times 128
   int NC;                 // accumulator columns, a multiple of 16: column j * Mp + m is digit j of row m
   int Mp;                 // M rounded up to 8
   int planes;             // digits (or halves) per activation row
@@ -62,8 +62,6 @@ struct TcParams {
   const uint8_t* xprep;   // prepared activations: n_stages blocks of x_bytes
   int x_bytes;            // NC * 256 * bytes per element
   const float* inv_scales;  // M f32: what each row's sum is multiplied by
-  int* counters;          // kMaxCtas tile counters, zero when the kernel starts
-  uint32_t* partials;     // 2 slots of 128 * NC words per CTA
   const void* bias;
   int bias_dtype;
   void* y;
@@ -75,12 +73,10 @@ struct TcParams {
 
 // Where the parts of the workspace begin, for a pass of NC columns of `elem` bytes over n_stages stages.
 struct TcLayout {
-  int64_t scales, counters, partials, total;
+  int64_t scales, total;
   TcLayout(int NC, int elem, int64_t n_stages) {
     scales = n_stages * NC * kKS * elem;
-    counters = scales + 256;
-    partials = counters + ((kMaxCtas * 4 + 255) / 256) * 256;
-    total = partials + 2ll * kMaxCtas * kBM * NC * 4;
+    total = scales + 256;
   }
 };
 
@@ -212,16 +208,13 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, int* stat
 // that no row owns are never written (their accumulator columns are never read).
 template <int ACT, bool XBF>
 __global__ void __launch_bounds__(128) tc_prep_kernel(const void* __restrict__ x, int ld_x, int rows, int K, int NC, int Mp, int planes,
-                                                      uint8_t* __restrict__ out, float* __restrict__ inv_scales, int* __restrict__ counters,
-                                                      int n_stages) {
+                                                      uint8_t* __restrict__ out, float* __restrict__ inv_scales, int n_stages) {
   constexpr int kElem = act_elem(ACT), V = 16 / kElem;
   constexpr int kXDtype = XBF ? LX_BF16 : LX_F32;
   pdl_trigger();
   pdl_wait();  // the kernel before this one may still be reading the workspace
   __shared__ float part[4];
   const int u = blockIdx.y, tid = threadIdx.x;
-  if (blockIdx.x == 0 && u == 0)
-    for (int i = tid; i < kMaxCtas; i += 128) counters[i] = 0;
   const int k0 = (blockIdx.x * 128 + tid) * V;
   const bool in_range = k0 < n_stages * kKS;
   const int kb = (k0 % kKS) * kElem;
@@ -355,47 +348,9 @@ __device__ __forceinline__ void expand_nvfp4(uint32_t w0, uint32_t w1, uint32_t 
   }
 }
 
-// ---- dealing stages to CTAs ----------------------------------------------------------------------------------------
-// First stage of CTA b's range when `total` stages are dealt to `ctas` CTAs.
-__host__ __device__ __forceinline__ int range_begin(int total, int ctas, int b) {
-  return static_cast<int>(static_cast<int64_t>(total) * b / ctas);
-}
-// The CTA whose range holds stage g.
-__device__ __forceinline__ int owner_of(int total, int ctas, int g) {
-  int b = static_cast<int>(static_cast<int64_t>(g) * ctas / total);
-  while (b + 1 < ctas && range_begin(total, ctas, b + 1) <= g) ++b;
-  while (b > 0 && range_begin(total, ctas, b) > g) --b;
-  return b;
-}
-
-// ---- finishing a segment (this CTA's stages of one tile) --------------------------------------------------------------
-// The epilogue warps of a CTA: `warps` of them meet on group_bar; the calling thread owns weight row r of the tile
-// (accumulator lane r, its warp's lane quarter already in d_addr) and the 8-row chunks chunk0, chunk0 + chunk_step, ...
-struct Epilogue {
-  uint32_t group_bar;
-  int warps;
-  int meetings;
-  volatile int* flags;  // two words, used alternately, so that a flag is not rewritten while a slow warp still reads it
-  bool leader;
-  int lane;
-  int chunk0, chunk_step;
-  // All epilogue warps meet (a bounded wait, unlike bar.sync); what they wrote before is visible after.
-  __device__ __forceinline__ bool meet(int* status) {
-    __syncwarp();
-    if (lane == 0) mbar_arrive(group_bar);
-    return tc_wait(group_bar, (meetings++) & 1, status);
-  }
-};
-
-__device__ __forceinline__ uint4 ld_cg_u128(const uint32_t* p) {
-  uint4 v;
-  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
-}
-
+// ---- the epilogue of a tile ---------------------------------------------------------------------------------------------
 template <int kAct>
 __device__ __forceinline__ void combine_and_store(const TcParams& P, const uint32_t (&raw)[3][8], int m0, int n, float rf, float bias) {
-  if (n >= P.N) return;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const int m = m0 + j;
@@ -416,32 +371,18 @@ __device__ __forceinline__ void combine_and_store(const TcParams& P, const uint3
   }
 }
 
-template <int kAct>
-__device__ __forceinline__ uint32_t add_raw(uint32_t a, uint32_t b) {
-  if constexpr (kAct == kActS8) return a + b;  // two's complement: the s32 sums add exactly
-  else return __float_as_uint(__uint_as_float(a) + __uint_as_float(b));
-}
-
-// A partial accumulator in the workspace: word (column c, row r) at ((c / 4) * 128 + r) * 4 + c % 4, so that a thread
-// moves four columns of its row with one 16-byte access and a warp's accesses are contiguous.
-__device__ __forceinline__ uint32_t* partial_at(uint32_t* slot, int column, int r) { return slot + ((column >> 2) * kBM + r) * 4; }
-
-// Returns false when a bounded wait gave up. release_bar (0 = none) gets one arrival per warp as soon as the
-// accumulator has been read.
-//
-// A tile shared by CTAs b_lo .. b_hi is finished by whichever of them comes last, and the sum always runs in the order
-// b_lo, b_lo + 1, ...: a contributor first looks at the tile's counter; if all the others have counted themselves it
-// adds their partials (from the workspace) and its own (from tensor memory, at its place in the order) and stores the
-// result. Otherwise it writes its partial, counts itself, and only if the others arrived in between does it finish
-// the tile after all, now reading every part from the workspace. Nobody waits for anybody.
+// The calling thread owns row r of the tile (accumulator lane r, its warp's lane quarter already in d_addr) and the
+// 8-row chunks of activations chunk0, chunk0 + chunk_step, ... release_bar (0 = none) gets one arrival per warp as
+// soon as the warp has read the accumulator.
 template <int F>
-__device__ __forceinline__ bool finish_segment(const TcParams& P, Epilogue& E, uint32_t d_addr, int tile, int r, bool whole, bool first_of_range,
-                                               int total, int ctas, int n_stages, uint32_t release_bar) {
+__device__ __forceinline__ void finish_tile(const TcParams& P, uint32_t d_addr, int tile, int r, int lane, int chunk0, int chunk_step,
+                                            uint32_t release_bar) {
   constexpr int kAct = TcFmt<F>::kAct;
-  const int n = tile * kBM + r;
+  const int n = tile * P.R + r;
+  const bool live = r < P.R && n < P.N;
   const int Mp = P.Mp, chunks = Mp / 8;
   float rf = 1.0f, bias = 0.0f;
-  if (n < P.N) {
+  if (live) {
     if constexpr (F == LX_W_INT8 || F == LX_W_FP8) rf = reinterpret_cast<const float*>(P.scale)[n];
     if constexpr (F == LX_W_NVFP4) rf = P.global;
     if (P.bias) bias = load_f32(P.bias, P.bias_dtype, n);
@@ -449,107 +390,18 @@ __device__ __forceinline__ bool finish_segment(const TcParams& P, Epilogue& E, u
   auto release = [&]() {
     tc_fence_before();
     __syncwarp();
-    if (release_bar && E.lane == 0) mbar_arrive(release_bar);
-  };
-  auto slot_of = [&](int b) {
-    return P.partials + (2 * static_cast<size_t>(b) + (range_begin(total, ctas, b) / n_stages == tile ? 0 : 1)) * (kBM * P.NC);
+    if (release_bar && lane == 0) mbar_arrive(release_bar);
   };
   uint32_t raw[3][8];
-  if (whole) {
-    for (int c = E.chunk0; c < chunks; c += E.chunk_step) {
-#pragma unroll
-      for (int p = 0; p < 3; ++p)
-        if (p < P.planes) tmem_ld8(d_addr + p * Mp + c * 8, raw[p]);
-      tmem_wait_ld();
-      if (c + E.chunk_step >= chunks) release();
-      combine_and_store<kAct>(P, raw, c * 8, n, rf, bias);
-    }
-    if (E.chunk0 >= chunks) release();
-    return true;
-  }
-  const int me = blockIdx.x;
-  const int b_lo = owner_of(total, ctas, tile * n_stages), b_hi = owner_of(total, ctas, tile * n_stages + n_stages - 1);
-  // Have all the others counted themselves already?
-  volatile int* flag = E.flags + (E.meetings & 1);
-  if (E.leader) *flag = ld_acquire(P.counters + b_lo) == b_hi - b_lo ? 1 : 0;
-  if (!E.meet(P.status)) return false;
-  if (*flag) {
-    __threadfence();
-    for (int c = E.chunk0; c < chunks; c += E.chunk_step) {
-      uint32_t own[3][8];
-#pragma unroll
-      for (int p = 0; p < 3; ++p)
-        if (p < P.planes) tmem_ld8(d_addr + p * Mp + c * 8, own[p]);
-      bool started = false;
-      for (int b = b_lo; b <= b_hi; ++b) {
-        uint32_t part[3][8];
-        if (b == me) {
-          tmem_wait_ld();
-          if (c + E.chunk_step >= chunks) release();
-#pragma unroll
-          for (int p = 0; p < 3; ++p)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) part[p][j] = own[p][j];
-        } else {
-          uint32_t* theirs = slot_of(b);
-#pragma unroll
-          for (int p = 0; p < 3; ++p) {
-            if (p >= P.planes) break;
-            const uint4 lo = ld_cg_u128(partial_at(theirs, p * Mp + c * 8, r)), hi = ld_cg_u128(partial_at(theirs, p * Mp + c * 8 + 4, r));
-            part[p][0] = lo.x, part[p][1] = lo.y, part[p][2] = lo.z, part[p][3] = lo.w;
-            part[p][4] = hi.x, part[p][5] = hi.y, part[p][6] = hi.z, part[p][7] = hi.w;
-          }
-        }
-#pragma unroll
-        for (int p = 0; p < 3; ++p)
-#pragma unroll
-          for (int j = 0; j < 8; ++j) raw[p][j] = started ? add_raw<kAct>(raw[p][j], part[p][j]) : add_raw<kAct>(0u, part[p][j]);
-        started = true;
-      }
-      combine_and_store<kAct>(P, raw, c * 8, n, rf, bias);
-    }
-    if (E.chunk0 >= chunks) release();
-    return true;
-  }
-  // Not the last one (as far as it could tell): the partial goes to this CTA's slot (0 when the segment is the first
-  // of its range, else 1), then the CTA counts itself.
-  uint32_t* mine = P.partials + (2 * static_cast<size_t>(me) + (first_of_range ? 0 : 1)) * (kBM * P.NC);
-  for (int c = E.chunk0; c < chunks; c += E.chunk_step) {
+  for (int c = chunk0; c < chunks; c += chunk_step) {
 #pragma unroll
     for (int p = 0; p < 3; ++p)
       if (p < P.planes) tmem_ld8(d_addr + p * Mp + c * 8, raw[p]);
     tmem_wait_ld();
-#pragma unroll
-    for (int p = 0; p < 3; ++p) {
-      if (p >= P.planes) break;
-      *reinterpret_cast<uint4*>(partial_at(mine, p * Mp + c * 8, r)) = make_uint4(raw[p][0], raw[p][1], raw[p][2], raw[p][3]);
-      *reinterpret_cast<uint4*>(partial_at(mine, p * Mp + c * 8 + 4, r)) = make_uint4(raw[p][4], raw[p][5], raw[p][6], raw[p][7]);
-    }
+    if (c + chunk_step >= chunks) release();
+    if (live) combine_and_store<kAct>(P, raw, c * 8, n, rf, bias);
   }
-  release();
-  __threadfence();
-  if (!E.meet(P.status)) return false;
-  flag = E.flags + (E.meetings & 1);
-  if (E.leader) *flag = atomicAdd(P.counters + b_lo, 1) == b_hi - b_lo ? 1 : 0;
-  if (!E.meet(P.status)) return false;
-  if (!*flag) return true;
-  // The others arrived in between: every part is in the workspace now, this CTA's too.
-  __threadfence();
-  for (int c = E.chunk0; c < chunks; c += E.chunk_step) {
-    for (int b = b_lo; b <= b_hi; ++b) {
-      uint32_t* theirs = slot_of(b);
-#pragma unroll
-      for (int p = 0; p < 3; ++p) {
-        if (p >= P.planes) break;
-        const uint4 lo = ld_cg_u128(partial_at(theirs, p * Mp + c * 8, r)), hi = ld_cg_u128(partial_at(theirs, p * Mp + c * 8 + 4, r));
-        const uint32_t part[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-#pragma unroll
-        for (int j = 0; j < 8; ++j) raw[p][j] = b == b_lo ? add_raw<kAct>(0u, part[j]) : add_raw<kAct>(raw[p][j], part[j]);
-      }
-    }
-    combine_and_store<kAct>(P, raw, c * 8, n, rf, bias);
-  }
-  return true;
+  if (chunk0 >= chunks) release();
 }
 
 // ---- BF16 / FP8 / INT8: weights go from shared memory straight into the tensor core ------------------------------------
@@ -560,12 +412,14 @@ template <int F>
 __global__ void __launch_bounds__(kDirectThreads, 1) tc_direct_kernel(const __grid_constant__ CUtensorMap wmap, const TcParams P) {
   using Fm = TcFmt<F>;
   constexpr int kAct = Fm::kAct;
-  constexpr int kWStage = kBM * Fm::kRowBytes;   // weight bytes per stage, a multiple of 1024
   constexpr int kBoxes = Fm::kRowBytes / 128;    // 128-byte-wide tile copies per stage
   extern __shared__ __align__(1024) uint8_t smem[];
   const int NC = P.NC, SW = P.SW, SX = P.SX;
-  const int x_bytes = P.x_bytes;
-  uint8_t* const xring = smem + static_cast<size_t>(SW) * kWStage;
+  const int x_bytes = P.x_bytes, box_bytes = P.box_bytes;
+  const int w_stage = kBoxes * box_bytes;        // a multiple of 1024
+  // The tensor core reads 128 rows from every box, whatever R is: behind the weight ring come at least 16 KB of this
+  // CTA's own shared memory (the activation ring and padding).
+  uint8_t* const xring = smem + static_cast<size_t>(SW) * w_stage;
   uint64_t* bars = reinterpret_cast<uint64_t*>(xring + static_cast<size_t>(SX) * x_bytes);
   const uint32_t bar0 = smem_u32(bars);
   auto w_full = [&](int s) { return bar0 + 8u * s; };                     // weight stage landed
@@ -574,15 +428,13 @@ __global__ void __launch_bounds__(kDirectThreads, 1) tc_direct_kernel(const __gr
   auto x_empty = [&](int s) { return bar0 + 8u * (2 * SW + SX + s); };    // its products are done
   auto d_full = [&](int b) { return bar0 + 8u * (2 * SW + 2 * SX + b); };       // accumulator b is complete
   auto d_empty = [&](int b) { return bar0 + 8u * (2 * SW + 2 * SX + 2 + b); };  // accumulator b has been read
-  const uint32_t group_bar = bar0 + 8u * (2 * SW + 2 * SX + 4);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * SW + 2 * SX + 5);
-  int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * SW + 2 * SX + 4);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_stages = (P.K + kKS - 1) / kKS;
-  const int n_tiles = (P.N + kBM - 1) / kBM;
-  const int total = n_tiles * n_stages, ctas = gridDim.x;
-  const int g_begin = range_begin(total, ctas, blockIdx.x), g_end = range_begin(total, ctas, blockIdx.x + 1);
+  const int n_tiles = (P.N + P.R - 1) / P.R;
+  const int tile_begin = static_cast<int>(static_cast<int64_t>(n_tiles) * blockIdx.x / gridDim.x);
+  const int tile_end = static_cast<int>(static_cast<int64_t>(n_tiles) * (blockIdx.x + 1) / gridDim.x);
 
   if (tid == 0) {
     for (int s = 0; s < SW; ++s) {
@@ -597,7 +449,6 @@ __global__ void __launch_bounds__(kDirectThreads, 1) tc_direct_kernel(const __gr
       mbar_init(d_full(b), 1);
       mbar_init(d_empty(b), 4);
     }
-    mbar_init(group_bar, 4);
     mbar_init_fence();
   }
   if (warp == 5) {
@@ -613,26 +464,26 @@ __global__ void __launch_bounds__(kDirectThreads, 1) tc_direct_kernel(const __gr
     // ================================ producers ================================
     pdl_trigger();
     if (lane == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
-    // Everything earlier in the stream is complete after this: the preparation kernel (activations, counters) and
-    // whatever wrote the weights before it.
+    // Everything earlier in the stream is complete after this: the preparation kernel (activations) and whatever
+    // wrote the weights before it.
     pdl_wait();
+    const int total = (tile_end - tile_begin) * n_stages;
     if (lane == 0) {
-      for (int g = g_begin; g < g_end; ++g) {
-        const int i = g - g_begin, slot = i % SW;
-        const int tile = g / n_stages, s = g % n_stages;
+      for (int i = 0; i < total; ++i) {
+        const int slot = i % SW, tile = tile_begin + i / n_stages, s = i % n_stages;
         if (i >= SW && !tc_wait(w_empty(slot), ((i / SW) - 1) & 1, P.status)) break;
-        const uint32_t dst = smem_u32(smem) + static_cast<uint32_t>(slot) * kWStage;
-        mbar_arrive_expect_tx(w_full(slot), kWStage);
+        const uint32_t dst = smem_u32(smem) + static_cast<uint32_t>(slot) * w_stage;
+        mbar_arrive_expect_tx(w_full(slot), kBoxes * P.R * 128);
 #pragma unroll
         for (int b = 0; b < kBoxes; ++b)
-          tile_g2s(dst + b * (kBM * 128), &wmap, (s * Fm::kRowBytes + b * 128) / 4, tile * kBM, w_full(slot));
+          tile_g2s(dst + b * box_bytes, &wmap, (s * Fm::kRowBytes + b * 128) / 4, tile * P.R, w_full(slot));
       }
     } else if (lane == 1) {
-      for (int g = g_begin; g < g_end; ++g) {
-        const int i = g - g_begin, slot = i % SX;
+      for (int i = 0; i < total; ++i) {
+        const int slot = i % SX;
         if (i >= SX && !tc_wait(x_empty(slot), ((i / SX) - 1) & 1, P.status)) break;
         mbar_arrive_expect_tx(x_full(slot), x_bytes);
-        bulk_g2s(smem_u32(xring) + static_cast<uint32_t>(slot) * x_bytes, P.xprep + static_cast<size_t>(g % n_stages) * x_bytes, x_bytes,
+        bulk_g2s(smem_u32(xring) + static_cast<uint32_t>(slot) * x_bytes, P.xprep + static_cast<size_t>(i % n_stages) * x_bytes, x_bytes,
                  x_full(slot));
       }
     }
@@ -645,57 +496,50 @@ __global__ void __launch_bounds__(kDirectThreads, 1) tc_direct_kernel(const __gr
       const uint32_t idesc = (cfmt << 4) | (abfmt << 7) | (abfmt << 10) | (static_cast<uint32_t>(NC >> 3) << 17) |
                              (static_cast<uint32_t>(kBM >> 4) << 24);
       const uint32_t lbo = static_cast<uint32_t>(NC / 8) * 128, sbo = 128;
-      int seg = 0;
-      uint32_t d_tmem = tmem_base;
-      for (int g = g_begin; g < g_end; ++g) {
-        const int i = g - g_begin, slot = i % SW, xs = i % SX;
-        const int s = g % n_stages;
-        const bool first = (g == g_begin) || s == 0;  // the first stage of a segment starts the sum anew
-        if (first) {
-          d_tmem = tmem_base + (seg & 1) * kDBufColumns;
-          if (seg >= 2) {  // the epilogue of the segment before last has read this accumulator
-            if (!tc_wait(d_empty(seg & 1), ((seg >> 1) - 1) & 1, P.status)) break;
-            tc_fence_after();
+      int i = 0;
+      bool ok = true;
+      for (int tile = tile_begin; tile < tile_end && ok; ++tile) {
+        const int t = tile - tile_begin, buf = t & 1;
+        const uint32_t d_tmem = tmem_base + buf * kDBufColumns;
+        if (t >= 2) {  // the epilogue of the tile before last has read this accumulator
+          if (!tc_wait(d_empty(buf), ((t >> 1) - 1) & 1, P.status)) break;
+          tc_fence_after();
+        }
+        for (int s = 0; s < n_stages; ++s, ++i) {
+          const int slot = i % SW, xs = i % SX;
+          if (!tc_wait(w_full(slot), (i / SW) & 1, P.status) || !tc_wait(x_full(xs), (i / SX) & 1, P.status)) {
+            ok = false;
+            break;
           }
-        }
-        if (!tc_wait(w_full(slot), (i / SW) & 1, P.status) || !tc_wait(x_full(xs), (i / SX) & 1, P.status)) break;
-        tc_fence_after();
-        const uint32_t wb = smem_u32(smem) + static_cast<uint32_t>(slot) * kWStage;
-        const uint32_t xb = smem_u32(xring) + static_cast<uint32_t>(xs) * x_bytes;
+          tc_fence_after();
+          const uint32_t wb = smem_u32(smem) + static_cast<uint32_t>(slot) * w_stage;
+          const uint32_t xb = smem_u32(xring) + static_cast<uint32_t>(xs) * x_bytes;
 #pragma unroll
-        for (int b = 0; b < kBoxes; ++b) {
+          for (int b = 0; b < kBoxes; ++b) {
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            const int c = b * 4 + ks;  // 32 bytes of K per instruction
-            const uint64_t adesc = smem_desc_sw128(wb + b * (kBM * 128) + ks * 32);
-            const uint64_t bdesc = smem_desc(xb + static_cast<uint32_t>(2 * c) * lbo, lbo, sbo);
-            umma_ss<kAct>(d_tmem, adesc, bdesc, idesc, (!first || c) ? 1u : 0u);
+            for (int ks = 0; ks < 4; ++ks) {
+              const int c = b * 4 + ks;  // 32 bytes of K per instruction
+              const uint64_t adesc = smem_desc_sw128(wb + b * box_bytes + ks * 32);
+              const uint64_t bdesc = smem_desc(xb + static_cast<uint32_t>(2 * c) * lbo, lbo, sbo);
+              umma_ss<kAct>(d_tmem, adesc, bdesc, idesc, (s | c) ? 1u : 0u);
+            }
           }
+          umma_commit(w_empty(slot));
+          umma_commit(x_empty(xs));
         }
-        umma_commit(w_empty(slot));
-        umma_commit(x_empty(xs));
-        if (s == n_stages - 1 || g == g_end - 1) {
-          umma_commit(d_full(seg & 1));
-          ++seg;
-        }
+        if (ok) umma_commit(d_full(buf));
       }
     }
   } else {
     // ================================ epilogue ================================
     const int r = tid;  // weight row of the tile = TMEM lane
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    Epilogue E{group_bar, 4, 0, last_flag, tid == 0, lane, 0, 1};
-    int seg = 0;
-    for (int g = g_begin; g < g_end; ++seg) {
-      const int tile = g / n_stages;
-      const int seg_end = min(g_end, (tile + 1) * n_stages);
-      if (!tc_wait(d_full(seg & 1), (seg >> 1) & 1, P.status)) break;
+    for (int tile = tile_begin; tile < tile_end; ++tile) {
+      const int t = tile - tile_begin, buf = t & 1;
+      if (!tc_wait(d_full(buf), (t >> 1) & 1, P.status)) break;
       tc_fence_after();
       pdl_wait();  // bias, y and the activation scales may come from earlier kernels
-      const bool whole = g == tile * n_stages && seg_end == (tile + 1) * n_stages;
-      if (!finish_segment<F>(P, E, lane_addr + (seg & 1) * kDBufColumns, tile, r, whole, g == g_begin, total, ctas, n_stages, d_empty(seg & 1)))
-        break;
-      g = seg_end;
+      finish_tile<F>(P, lane_addr + buf * kDBufColumns, tile, r, lane, 0, 1, d_empty(buf));
     }
   }
   __syncthreads();
@@ -713,13 +557,11 @@ __global__ void __launch_bounds__(kConvThreads, 1)
     tc_nvfp4_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap, const TcParams P) {
   constexpr int F = LX_W_NVFP4;
   using Fm = TcFmt<F>;
-  constexpr int kRawBytes = kBM * Fm::kRowBytes;   // weight bytes per stage: one 128-byte-wide box
-  constexpr int kScaleBytes = kBM * 16;            // 16 block scales per row per stage
-  constexpr int kWStage = kRawBytes + kScaleBytes; // a multiple of 1024
   extern __shared__ __align__(1024) uint8_t smem[];
   const int NC = P.NC, SW = P.SW, SX = P.SX;
-  const int x_bytes = P.x_bytes;
-  uint8_t* const xring = smem + static_cast<size_t>(SW) * kWStage;
+  const int x_bytes = P.x_bytes, box_bytes = P.box_bytes;
+  // a slot is the stage's box (R rows of 128 bytes, 1024-aligned) and, box_bytes further, its 16 block scales per row
+  uint8_t* const xring = smem + static_cast<size_t>(SW) * box_bytes * 2;
   uint64_t* bars = reinterpret_cast<uint64_t*>(xring + static_cast<size_t>(SX) * x_bytes);
   const uint32_t bar0 = smem_u32(bars);
   auto w_full = [&](int s) { return bar0 + 8u * s; };                               // weight stage landed
@@ -728,16 +570,16 @@ __global__ void __launch_bounds__(kConvThreads, 1)
   auto x_empty = [&](int s) { return bar0 + 8u * (2 * SW + SX + s); };              // its products are done
   auto a_full = [&](int a) { return bar0 + 8u * (2 * SW + 2 * SX + a); };           // A slot written
   auto a_empty = [&](int a) { return bar0 + 8u * (2 * SW + 2 * SX + kASlots + a); };// A slot consumed
-  const uint32_t d_full = bar0 + 8u * (2 * SW + 2 * SX + 2 * kASlots);              // the segment's accumulator is complete
-  const uint32_t group_bar = d_full + 8u;                                           // the converter warps meet here
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * SW + 2 * SX + 2 * kASlots + 2);
-  int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
+  const uint32_t d_full = bar0 + 8u * (2 * SW + 2 * SX + 2 * kASlots);              // the tile's accumulator is complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * SW + 2 * SX + 2 * kASlots + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_stages = (P.K + kKS - 1) / kKS;
-  const int n_tiles = (P.N + kBM - 1) / kBM;
-  const int total = n_tiles * n_stages, ctas = gridDim.x;
-  const int g_begin = range_begin(total, ctas, blockIdx.x), g_end = range_begin(total, ctas, blockIdx.x + 1);
+  const int n_tiles = (P.N + P.R - 1) / P.R;
+  const int tile_begin = static_cast<int>(static_cast<int64_t>(n_tiles) * blockIdx.x / gridDim.x);
+  const int tile_end = static_cast<int>(static_cast<int64_t>(n_tiles) * (blockIdx.x + 1) / gridDim.x);
+  const int total = (tile_end - tile_begin) * n_stages;
+  const int slot_bytes = 2 * box_bytes;
 
   if (tid == 0) {
     for (int s = 0; s < SW; ++s) {
@@ -753,7 +595,6 @@ __global__ void __launch_bounds__(kConvThreads, 1)
       mbar_init(a_empty(a), 1);
     }
     mbar_init(d_full, 1);
-    mbar_init(group_bar, kConvWarps);
     mbar_init_fence();
   }
   if (warp == 9) {
@@ -772,23 +613,22 @@ __global__ void __launch_bounds__(kConvThreads, 1)
       asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&smap) : "memory");
     }
-    pdl_wait();  // everything earlier in the stream is complete: prepared activations, counters, weights
+    pdl_wait();  // everything earlier in the stream is complete: prepared activations, weights
     if (lane == 0) {
-      for (int g = g_begin; g < g_end; ++g) {
-        const int i = g - g_begin, slot = i % SW;
-        const int tile = g / n_stages, s = g % n_stages;
+      for (int i = 0; i < total; ++i) {
+        const int slot = i % SW, tile = tile_begin + i / n_stages, s = i % n_stages;
         if (i >= SW && !tc_wait(w_empty(slot), ((i / SW) - 1) & 1, P.status)) break;
-        const uint32_t dst = smem_u32(smem) + static_cast<uint32_t>(slot) * kWStage;
-        mbar_arrive_expect_tx(w_full(slot), kWStage);
-        tile_g2s(dst, &wmap, (s * Fm::kRowBytes) / 4, tile * kBM, w_full(slot));
-        tile_g2s(dst + kRawBytes, &smap, s * 16, tile * kBM, w_full(slot));
+        const uint32_t dst = smem_u32(smem) + static_cast<uint32_t>(slot) * slot_bytes;
+        mbar_arrive_expect_tx(w_full(slot), P.R * (128 + 16));
+        tile_g2s(dst, &wmap, (s * Fm::kRowBytes) / 4, tile * P.R, w_full(slot));
+        tile_g2s(dst + box_bytes, &smap, s * 16, tile * P.R, w_full(slot));
       }
     } else if (lane == 1) {
-      for (int g = g_begin; g < g_end; ++g) {
-        const int i = g - g_begin, slot = i % SX;
+      for (int i = 0; i < total; ++i) {
+        const int slot = i % SX;
         if (i >= SX && !tc_wait(x_empty(slot), ((i / SX) - 1) & 1, P.status)) break;
         mbar_arrive_expect_tx(x_full(slot), x_bytes);
-        bulk_g2s(smem_u32(xring) + static_cast<uint32_t>(slot) * x_bytes, P.xprep + static_cast<size_t>(g % n_stages) * x_bytes, x_bytes,
+        bulk_g2s(smem_u32(xring) + static_cast<uint32_t>(slot) * x_bytes, P.xprep + static_cast<size_t>(i % n_stages) * x_bytes, x_bytes,
                  x_full(slot));
       }
     }
@@ -797,24 +637,22 @@ __global__ void __launch_bounds__(kConvThreads, 1)
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(NC >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);  // f16 x f16 -> f32
       const uint32_t lbo = static_cast<uint32_t>(NC / 8) * 128, sbo = 128;
-      for (int g = g_begin; g < g_end; ++g) {
-        const int i = g - g_begin, xs = i % SX, a = i % kASlots;
-        const int s = g % n_stages;
+      for (int i = 0; i < total; ++i) {
+        const int xs = i % SX, a = i % kASlots, s = i % n_stages;
         // the activations of this stage are in shared memory, the converted weights in tensor memory
         if (!tc_wait(x_full(xs), (i / SX) & 1, P.status) || !tc_wait(a_full(a), (i / kASlots) & 1, P.status)) break;
         tc_fence_after();
         const uint32_t xb = smem_u32(xring) + static_cast<uint32_t>(xs) * x_bytes;
-        const bool first = (g == g_begin) || s == 0;  // the first stage of a segment starts the sum anew
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
           const uint64_t bdesc = smem_desc(xb + static_cast<uint32_t>(2 * c) * lbo, lbo, sbo);
-          umma_ts(tmem_base + kDColumn, tmem_base + a * kAColumns + c * 8, bdesc, idesc, (!first || c) ? 1u : 0u);
+          umma_ts(tmem_base + kDColumn, tmem_base + a * kAColumns + c * 8, bdesc, idesc, (s | c) ? 1u : 0u);
         }
         umma_commit(a_empty(a));    // the A slot may be overwritten once these products are done
         umma_commit(x_empty(xs));   // and so may the activation block
-        // A segment ends here: its accumulator is complete when everything issued so far is. The next segment's first
+        // A tile ends here: its accumulator is complete when everything issued so far is. The next tile's first
         // product overwrites it, but waits for an A slot the converters fill only after they have read the accumulator.
-        if (s == n_stages - 1 || g == g_end - 1) umma_commit(d_full);
+        if (s == n_stages - 1) umma_commit(d_full);
       }
     }
   } else {
@@ -822,14 +660,13 @@ __global__ void __launch_bounds__(kConvThreads, 1)
     const int quarter = warp & 3, half = warp >> 2;
     const int r = quarter * 32 + lane;  // weight row of the tile = TMEM lane
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    Epilogue E{group_bar, kConvWarps, 0, last_flag, tid == 0, lane, half, 2};
-    int segment = 0;
-    for (int g = g_begin; g < g_end; ++g) {
-      const int i = g - g_begin, slot = i % SW, a = i % kASlots;
-      const int tile = g / n_stages, s = g % n_stages;
+    for (int i = 0; i < total; ++i) {
+      const int slot = i % SW, a = i % kASlots, s = i % n_stages;
       if (!tc_wait(w_full(slot), (i / SW) & 1, P.status) || (i >= kASlots && !tc_wait(a_empty(a), ((i / kASlots) - 1) & 1, P.status))) break;
       tc_fence_after();
-      const uint8_t* stage = smem + static_cast<size_t>(slot) * kWStage;
+      // Rows past R read what shared memory holds behind the box (this CTA's own, see tc_launch); their lanes are
+      // never read back.
+      const uint8_t* stage = smem + static_cast<size_t>(slot) * slot_bytes;
       const uint32_t a_addr = lane_addr + a * kAColumns + half * (kAColumns / 2);
       const int sw = r & 7;
       // this half's 128 values = 64 bytes = pieces 4 half .. 4 half + 3 of the row's 128 bytes; 8 block scales
@@ -837,7 +674,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
       uint4 q[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) q[j] = *reinterpret_cast<const uint4*>(box + (((4 * half + j) ^ sw) << 4));
-      const uint2 sc = *reinterpret_cast<const uint2*>(stage + kRawBytes + r * 16 + half * 8);
+      const uint2 sc = *reinterpret_cast<const uint2*>(stage + box_bytes + r * 16 + half * 8);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         uint32_t p[8];
@@ -854,15 +691,13 @@ __global__ void __launch_bounds__(kConvThreads, 1)
         mbar_arrive(w_empty(slot));  // the bytes are in registers / tensor memory: the stage may be refilled
         mbar_arrive(a_full(a));
       }
-      if (s != n_stages - 1 && g != g_end - 1) continue;
-      // ---- the segment is over ----
-      if (!tc_wait(d_full, segment & 1, P.status)) break;
-      ++segment;
+      if (s != n_stages - 1) continue;
+      // ---- the tile is over ----
+      const int t = i / n_stages;
+      if (!tc_wait(d_full, t & 1, P.status)) break;
       tc_fence_after();
       pdl_wait();  // bias, y and the activation scales may come from earlier kernels
-      const int seg_first = max(g_begin, tile * n_stages);  // the segment is stages seg_first .. g of the tile
-      const bool whole = seg_first == tile * n_stages && s == n_stages - 1;
-      if (!finish_segment<F>(P, E, lane_addr + kDColumn, tile, r, whole, seg_first == g_begin, total, ctas, n_stages, 0u)) break;
+      finish_tile<F>(P, lane_addr + kDColumn, tile_begin + t, r, lane, half, 2, 0u);
     }
   }
   __syncthreads();
@@ -904,29 +739,40 @@ int allow_big_smem(Kernel kernel) {
   return kOk;
 }
 
+// Rows per tile: the fewest whole tiles per SM that keep a tile within 128 rows, then the rows that spread N evenly
+// over that many tiles.
+int tile_rows(int N, int sms) {
+  const int per_sm = (N + kBM * sms - 1) / (kBM * sms);
+  const int rows = (N + per_sm * sms - 1) / (per_sm * sms);
+  return std::min(kBM, std::max(kMinTileRows, rows));
+}
+
 template <int F>
 int tc_launch(const lx_weight& w, TcParams P, cudaStream_t stream) {
   using Fm = TcFmt<F>;
-  constexpr int kWStage = kBM * Fm::kRowBytes + (F == LX_W_NVFP4 ? kBM * 16 : 0);
-  constexpr int kBudget = 220 * 1024;
-  P.SX = P.x_bytes > 24 * 1024 ? 2 : 3;
-  P.SW = std::min(8, (kBudget - P.SX * P.x_bytes) / kWStage);
-  if (P.SW < 2) return kNotSupported;
+  constexpr int kBoxes = Fm::kRowBytes / 128;
   const int sms = sm_count();
   if (!sms) return kInvalid;
+  P.R = tile_rows(P.N, sms);
+  P.box_bytes = (P.R + 7) / 8 * 1024;
+  // NVFP4 keeps a stage's box and its block scales in a slot of twice the box, so that every box starts 1024-aligned.
+  const int w_stage = F == LX_W_NVFP4 ? 2 * P.box_bytes : kBoxes * P.box_bytes;
+  constexpr int kBudget = 204 * 1024;  // leaves room for the 16 KB the tensor core may read past the last box
+  P.SX = P.x_bytes > 24 * 1024 ? 2 : 3;
+  P.SW = std::min(12, (kBudget - P.SX * P.x_bytes) / w_stage);
+  if (P.SW < 2) return kNotSupported;
   // Tensor memory is taken whole (512 columns), so exactly one CTA may live on an SM: ask for more than half of its
   // shared memory whatever the rings need.
-  const size_t smem = std::max<size_t>(static_cast<size_t>(P.SW) * kWStage + static_cast<size_t>(P.SX) * P.x_bytes + 1024, 120 * 1024);
+  const size_t smem = std::max<size_t>(static_cast<size_t>(P.SW) * w_stage + std::max(P.SX * P.x_bytes, 16 * 1024) + 1024, 120 * 1024);
   alignas(64) CUtensorMap wmap, smap;
   memset(&wmap, 0, sizeof(wmap));
   memset(&smap, 0, sizeof(smap));
   const int64_t row_bytes = F == LX_W_BF16 ? 2ll * P.K : F == LX_W_NVFP4 ? P.K / 2 : P.K;
-  if (int e = make_tile_map(&wmap, w.data, row_bytes, P.N, 128, kBM, 4, true)) return e;
-  const int tiles = (P.N + kBM - 1) / kBM, n_stages = (P.K + kKS - 1) / kKS;
-  const int total = tiles * n_stages;
-  const int grid = std::min(total, std::max(1, std::min({sms, kMaxCtas, std::max(tiles, total / kMinStagesPerCta)})));
+  if (int e = make_tile_map(&wmap, w.data, row_bytes, P.N, 128, P.R, 4, true)) return e;
+  const int tiles = (P.N + P.R - 1) / P.R;
+  const int grid = std::min(tiles, sms);
   if constexpr (F == LX_W_NVFP4) {
-    if (int e = make_tile_map(&smap, w.scale, P.K / 16, P.N, 16, kBM, 1, false)) return e;
+    if (int e = make_tile_map(&smap, w.scale, P.K / 16, P.N, 16, P.R, 1, false)) return e;
     if (int e = allow_big_smem<F>(tc_nvfp4_kernel)) return e;
     return launch_kernel(tc_nvfp4_kernel, dim3(grid), dim3(kConvThreads), smem, stream, wmap, smap, P);
   } else {
@@ -965,8 +811,6 @@ int tc_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const v
     const TcLayout L(P.NC, elem, n_stages);
     P.xprep = ws;
     P.inv_scales = reinterpret_cast<const float*>(ws + L.scales);
-    P.counters = reinterpret_cast<int*>(ws + L.counters);
-    P.partials = reinterpret_cast<uint32_t*>(ws + L.partials);
     P.bias = bias, P.bias_dtype = bias_dtype;
     P.y = static_cast<uint8_t*>(y) + static_cast<int64_t>(m0) * ld_y * (y_dtype == LX_BF16 ? 2 : 4);
     P.y_dtype = y_dtype, P.ld_y = ld_y;
@@ -977,7 +821,7 @@ int tc_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const v
     const dim3 prep_grid((n_stages * kKS + per_block - 1) / per_block, rows);
     auto prep = [&](auto kernel) {
       return launch_kernel(kernel, prep_grid, dim3(128), 0, stream, static_cast<const void*>(xrow), ld_x, rows, K, P.NC, P.Mp, P.planes, ws,
-                           reinterpret_cast<float*>(ws + L.scales), reinterpret_cast<int*>(ws + L.counters), n_stages);
+                           reinterpret_cast<float*>(ws + L.scales), n_stages);
     };
     int pe;
     switch (act * 2 + (x_bf16 ? 1 : 0)) {
@@ -1007,14 +851,12 @@ int tc_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const v
 // Bytes of workspace the product needs for M activation rows, whatever the weight format and activation dtype.
 int64_t tc_workspace_bytes(int M, int K) {
   const int rows = std::min(M, kMaxRows);
-  const int Mp = (rows + 7) / 8 * 8;
   const int64_t n_stages = (K + kKS - 1) / kKS;
   int64_t need = 0;
   for (int act = 0; act < 4; ++act)
     for (int bf = 0; bf < 2; ++bf) {
       const int r = std::min(rows, rows_per_pass(act, bf != 0));
-      const int mp = std::min(Mp, (r + 7) / 8 * 8);
-      const int NC = (act_planes(act, bf != 0) * mp + 15) / 16 * 16;
+      const int NC = (act_planes(act, bf != 0) * ((r + 7) / 8 * 8) + 15) / 16 * 16;
       need = std::max(need, TcLayout(NC, act_elem(act), n_stages).total);
     }
   return need;
