@@ -21,7 +21,8 @@ __host__ __device__ inline int64_t record_bytes(int64_t patches) { return (4 * (
 // One warp per row: the row's number of patches.
 __global__ void __launch_bounds__(kBlock) count_kernel(const uint16_t* __restrict__ w, int64_t rows, int K,
                                                        int32_t* __restrict__ counts) {
-  pdl_trigger();
+  // no early trigger: what this kernel writes may be the weight of the next product, whose kernels read weights
+  // before their own wait
   pdl_wait();
   const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -49,7 +50,8 @@ __global__ void __launch_bounds__(kBlock) count_kernel(const uint16_t* __restric
 // One CTA: offsets[r] = bytes of overflow records of rows before r (exclusive prefix in row order), total at [rows].
 __global__ void __launch_bounds__(1024) scan_kernel(const int32_t* __restrict__ counts, int64_t rows, int slots,
                                                     int64_t* __restrict__ offsets) {
-  pdl_trigger();
+  // no early trigger: what this kernel writes may be the weight of the next product, whose kernels read weights
+  // before their own wait
   pdl_wait();
   __shared__ int64_t part[1024];
   const int t = threadIdx.x;
@@ -80,7 +82,8 @@ __global__ void __launch_bounds__(1024) scan_kernel(const int32_t* __restrict__ 
 __global__ void __launch_bounds__(kBlock) encode_kernel(const uint16_t* __restrict__ w, int64_t rows, int K,
                                                         const int32_t* __restrict__ counts,
                                                         const int64_t* __restrict__ offsets, uint8_t* __restrict__ out) {
-  pdl_trigger();
+  // no early trigger: what this kernel writes may be the weight of the next product, whose kernels read weights
+  // before their own wait
   pdl_wait();
   const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -150,7 +153,8 @@ __global__ void __launch_bounds__(kBlock) encode_kernel(const uint16_t* __restri
 // One warp per row: every value from its byte, code and base, then the row's patches over them.
 __global__ void __launch_bounds__(kBlock) decode_kernel(const uint8_t* __restrict__ data, int64_t rows, int K,
                                                         uint16_t* __restrict__ w) {
-  pdl_trigger();
+  // no early trigger: what this kernel writes may be the weight of the next product, whose kernels read weights
+  // before their own wait
   pdl_wait();
   const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
   if (row >= rows) return;

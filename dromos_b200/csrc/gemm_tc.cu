@@ -198,6 +198,19 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, int* stat
   }
 }
 
+// Position in a ring of `depth` slots: the slot and the parity of the ring's current lap (no division in the loops:
+// an integer division by a run-time depth costs more than the eight products of a stage).
+struct Ring {
+  int slot = 0;
+  uint32_t lap = 0;
+  __device__ __forceinline__ void advance(int depth) {
+    if (++slot == depth) {
+      slot = 0;
+      lap ^= 1u;
+    }
+  }
+};
+
 // ---- activation preparation ----------------------------------------------------------------------------------------
 // Block (chunk, u): 128 threads, each 16 bytes of K of every plane of activation row u. The row's largest magnitude
 // is found by every block of the row again (the row is a few KB, from L2), which saves a second kernel. With kb the
@@ -350,7 +363,8 @@ __device__ __forceinline__ void expand_nvfp4(uint32_t w0, uint32_t w1, uint32_t 
 
 // ---- the epilogue of a tile ---------------------------------------------------------------------------------------------
 template <int kAct>
-__device__ __forceinline__ void combine_and_store(const TcParams& P, const uint32_t (&raw)[3][8], int m0, int n, float rf, float bias) {
+__device__ __forceinline__ void combine_and_store(const TcParams& P, const uint32_t (&raw)[3][8], const float (&inv)[8], int m0, int n, float rf,
+                                                  float bias) {
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const int m = m0 + j;
@@ -363,7 +377,7 @@ __device__ __forceinline__ void combine_and_store(const TcParams& P, const uint3
       sum += v * digit;
       digit *= P.digit;
     }
-    sum *= P.inv_scales[m];
+    sum *= inv[j];
     float out = P.alpha * (rf * sum + bias);
     const int64_t at = static_cast<int64_t>(m) * P.ld_y + n;
     if (P.beta != 0.0f) out = fmaf(P.beta, load_f32(P.y, P.y_dtype, at), out);
@@ -371,22 +385,35 @@ __device__ __forceinline__ void combine_and_store(const TcParams& P, const uint3
   }
 }
 
-// The calling thread owns row r of the tile (accumulator lane r, its warp's lane quarter already in d_addr) and the
-// 8-row chunks of activations chunk0, chunk0 + chunk_step, ... release_bar (0 = none) gets one arrival per warp as
-// soon as the warp has read the accumulator.
+// What a thread needs for its row of a tile besides the accumulator; loaded before the wait for the accumulator.
+struct RowTerms {
+  int n;
+  bool live;
+  float rf, bias;
+};
 template <int F>
-__device__ __forceinline__ void finish_tile(const TcParams& P, uint32_t d_addr, int tile, int r, int lane, int chunk0, int chunk_step,
-                                            uint32_t release_bar) {
-  constexpr int kAct = TcFmt<F>::kAct;
-  const int n = tile * P.R + r;
-  const bool live = r < P.R && n < P.N;
-  const int Mp = P.Mp, chunks = Mp / 8;
-  float rf = 1.0f, bias = 0.0f;
-  if (live) {
-    if constexpr (F == LX_W_INT8 || F == LX_W_FP8) rf = reinterpret_cast<const float*>(P.scale)[n];
-    if constexpr (F == LX_W_NVFP4) rf = P.global;
-    if (P.bias) bias = load_f32(P.bias, P.bias_dtype, n);
+__device__ __forceinline__ RowTerms row_terms(const TcParams& P, int tile, int r) {
+  RowTerms t;
+  t.n = tile * P.R + r;
+  t.live = r < P.R && t.n < P.N;
+  t.rf = 1.0f, t.bias = 0.0f;
+  if (t.live) {  // the weight's scales and the bias are static, like the weight
+    if constexpr (F == LX_W_INT8 || F == LX_W_FP8) t.rf = reinterpret_cast<const float*>(P.scale)[t.n];
+    if constexpr (F == LX_W_NVFP4) t.rf = P.global;
+    if (P.bias) t.bias = load_f32(P.bias, P.bias_dtype, t.n);
   }
+  return t;
+}
+
+// The calling thread owns row r of the tile (accumulator lane r, its warp's lane quarter already in d_addr) and the
+// 8-row chunks of activations chunk0, chunk0 + chunk_step, ... inv_lo / inv_hi: lane l holds the inverse activation
+// scale of rows l and 32 + l. release_bar (0 = none) gets one arrival per warp as soon as the warp has read the
+// accumulator.
+template <int F>
+__device__ __forceinline__ void finish_tile(const TcParams& P, const RowTerms& T, uint32_t d_addr, int lane, int chunk0, int chunk_step,
+                                            float inv_lo, float inv_hi, uint32_t release_bar) {
+  constexpr int kAct = TcFmt<F>::kAct;
+  const int Mp = P.Mp, chunks = Mp / 8;
   auto release = [&]() {
     tc_fence_before();
     __syncwarp();
@@ -397,9 +424,12 @@ __device__ __forceinline__ void finish_tile(const TcParams& P, uint32_t d_addr, 
 #pragma unroll
     for (int p = 0; p < 3; ++p)
       if (p < P.planes) tmem_ld8(d_addr + p * Mp + c * 8, raw[p]);
+    float inv[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) inv[j] = __shfl_sync(0xffffffffu, c < 4 ? inv_lo : inv_hi, (c * 8 + j) & 31);
     tmem_wait_ld();
     if (c + chunk_step >= chunks) release();
-    if (live) combine_and_store<kAct>(P, raw, c * 8, n, rf, bias);
+    if (T.live) combine_and_store<kAct>(P, raw, inv, c * 8, T.n, T.rf, T.bias);
   }
   if (chunk0 >= chunks) release();
 }
@@ -463,28 +493,40 @@ __global__ void __launch_bounds__(kDirectThreads, 1) tc_direct_kernel(const __gr
   if (warp == 4) {
     // ================================ producers ================================
     pdl_trigger();
-    if (lane == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
-    // Everything earlier in the stream is complete after this: the preparation kernel (activations) and whatever
-    // wrote the weights before it.
-    pdl_wait();
     const int total = (tile_end - tile_begin) * n_stages;
     if (lane == 0) {
-      for (int i = 0; i < total; ++i) {
-        const int slot = i % SW, tile = tile_begin + i / n_stages, s = i % n_stages;
-        if (i >= SW && !tc_wait(w_empty(slot), ((i / SW) - 1) & 1, P.status)) break;
-        const uint32_t dst = smem_u32(smem) + static_cast<uint32_t>(slot) * w_stage;
-        mbar_arrive_expect_tx(w_full(slot), kBoxes * P.R * 128);
+      // Weights are static (nothing earlier in the stream is still writing them: the contract of the reference's
+      // kernels, which also load them before their wait), so they stream while the preparation kernel still runs.
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
+      Ring w;
+      bool ok = true, wrapped = false;
+      for (int tile = tile_begin; tile < tile_end && ok; ++tile) {
+        for (int s = 0; s < n_stages; ++s) {
+          if (wrapped && !tc_wait(w_empty(w.slot), w.lap ^ 1u, P.status)) {
+            ok = false;
+            break;
+          }
+          const uint32_t dst = smem_u32(smem) + static_cast<uint32_t>(w.slot) * w_stage;
+          mbar_arrive_expect_tx(w_full(w.slot), kBoxes * P.R * 128);
 #pragma unroll
-        for (int b = 0; b < kBoxes; ++b)
-          tile_g2s(dst + b * box_bytes, &wmap, (s * Fm::kRowBytes + b * 128) / 4, tile * P.R, w_full(slot));
+          for (int b = 0; b < kBoxes; ++b)
+            tile_g2s(dst + b * box_bytes, &wmap, (s * Fm::kRowBytes + b * 128) / 4, tile * P.R, w_full(w.slot));
+          w.advance(SW);
+          wrapped |= w.slot == 0;
+        }
       }
     } else if (lane == 1) {
+      pdl_wait();  // the prepared activations come from the kernel before this one
+      Ring x;
+      bool wrapped = false;
+      int s = 0;
       for (int i = 0; i < total; ++i) {
-        const int slot = i % SX;
-        if (i >= SX && !tc_wait(x_empty(slot), ((i / SX) - 1) & 1, P.status)) break;
-        mbar_arrive_expect_tx(x_full(slot), x_bytes);
-        bulk_g2s(smem_u32(xring) + static_cast<uint32_t>(slot) * x_bytes, P.xprep + static_cast<size_t>(i % n_stages) * x_bytes, x_bytes,
-                 x_full(slot));
+        if (wrapped && !tc_wait(x_empty(x.slot), x.lap ^ 1u, P.status)) break;
+        mbar_arrive_expect_tx(x_full(x.slot), x_bytes);
+        bulk_g2s(smem_u32(xring) + static_cast<uint32_t>(x.slot) * x_bytes, P.xprep + static_cast<size_t>(s) * x_bytes, x_bytes, x_full(x.slot));
+        x.advance(SX);
+        wrapped |= x.slot == 0;
+        if (++s == n_stages) s = 0;
       }
     }
   } else if (warp == 5) {
@@ -496,7 +538,7 @@ __global__ void __launch_bounds__(kDirectThreads, 1) tc_direct_kernel(const __gr
       const uint32_t idesc = (cfmt << 4) | (abfmt << 7) | (abfmt << 10) | (static_cast<uint32_t>(NC >> 3) << 17) |
                              (static_cast<uint32_t>(kBM >> 4) << 24);
       const uint32_t lbo = static_cast<uint32_t>(NC / 8) * 128, sbo = 128;
-      int i = 0;
+      Ring w, x;
       bool ok = true;
       for (int tile = tile_begin; tile < tile_end && ok; ++tile) {
         const int t = tile - tile_begin, buf = t & 1;
@@ -505,15 +547,14 @@ __global__ void __launch_bounds__(kDirectThreads, 1) tc_direct_kernel(const __gr
           if (!tc_wait(d_empty(buf), ((t >> 1) - 1) & 1, P.status)) break;
           tc_fence_after();
         }
-        for (int s = 0; s < n_stages; ++s, ++i) {
-          const int slot = i % SW, xs = i % SX;
-          if (!tc_wait(w_full(slot), (i / SW) & 1, P.status) || !tc_wait(x_full(xs), (i / SX) & 1, P.status)) {
+        for (int s = 0; s < n_stages; ++s) {
+          if (!tc_wait(w_full(w.slot), w.lap, P.status) || !tc_wait(x_full(x.slot), x.lap, P.status)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t wb = smem_u32(smem) + static_cast<uint32_t>(slot) * w_stage;
-          const uint32_t xb = smem_u32(xring) + static_cast<uint32_t>(xs) * x_bytes;
+          const uint32_t wb = smem_u32(smem) + static_cast<uint32_t>(w.slot) * w_stage;
+          const uint32_t xb = smem_u32(xring) + static_cast<uint32_t>(x.slot) * x_bytes;
 #pragma unroll
           for (int b = 0; b < kBoxes; ++b) {
 #pragma unroll
@@ -524,8 +565,10 @@ __global__ void __launch_bounds__(kDirectThreads, 1) tc_direct_kernel(const __gr
               umma_ss<kAct>(d_tmem, adesc, bdesc, idesc, (s | c) ? 1u : 0u);
             }
           }
-          umma_commit(w_empty(slot));
-          umma_commit(x_empty(xs));
+          umma_commit(w_empty(w.slot));
+          umma_commit(x_empty(x.slot));
+          w.advance(SW);
+          x.advance(SX);
         }
         if (ok) umma_commit(d_full(buf));
       }
@@ -534,12 +577,14 @@ __global__ void __launch_bounds__(kDirectThreads, 1) tc_direct_kernel(const __gr
     // ================================ epilogue ================================
     const int r = tid;  // weight row of the tile = TMEM lane
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    pdl_wait();  // y and the activation scales come from earlier kernels
+    const float inv_lo = lane < P.M ? P.inv_scales[lane] : 0.0f, inv_hi = 32 + lane < P.M ? P.inv_scales[32 + lane] : 0.0f;
     for (int tile = tile_begin; tile < tile_end; ++tile) {
       const int t = tile - tile_begin, buf = t & 1;
+      const RowTerms T = row_terms<F>(P, tile, r);
       if (!tc_wait(d_full(buf), (t >> 1) & 1, P.status)) break;
       tc_fence_after();
-      pdl_wait();  // bias, y and the activation scales may come from earlier kernels
-      finish_tile<F>(P, lane_addr + buf * kDBufColumns, tile, r, lane, 0, 1, d_empty(buf));
+      finish_tile<F>(P, T, lane_addr + buf * kDBufColumns, lane, 0, 1, inv_lo, inv_hi, d_empty(buf));
     }
   }
   __syncthreads();
@@ -613,23 +658,35 @@ __global__ void __launch_bounds__(kConvThreads, 1)
       asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&smap) : "memory");
     }
-    pdl_wait();  // everything earlier in the stream is complete: prepared activations, weights
-    if (lane == 0) {
-      for (int i = 0; i < total; ++i) {
-        const int slot = i % SW, tile = tile_begin + i / n_stages, s = i % n_stages;
-        if (i >= SW && !tc_wait(w_empty(slot), ((i / SW) - 1) & 1, P.status)) break;
-        const uint32_t dst = smem_u32(smem) + static_cast<uint32_t>(slot) * slot_bytes;
-        mbar_arrive_expect_tx(w_full(slot), P.R * (128 + 16));
-        tile_g2s(dst, &wmap, (s * Fm::kRowBytes) / 4, tile * P.R, w_full(slot));
-        tile_g2s(dst + box_bytes, &smap, s * 16, tile * P.R, w_full(slot));
+    if (lane == 0) {  // weights and their scales are static: no wait
+      Ring w;
+      bool ok = true, wrapped = false;
+      for (int tile = tile_begin; tile < tile_end && ok; ++tile) {
+        for (int s = 0; s < n_stages; ++s) {
+          if (wrapped && !tc_wait(w_empty(w.slot), w.lap ^ 1u, P.status)) {
+            ok = false;
+            break;
+          }
+          const uint32_t dst = smem_u32(smem) + static_cast<uint32_t>(w.slot) * slot_bytes;
+          mbar_arrive_expect_tx(w_full(w.slot), P.R * (128 + 16));
+          tile_g2s(dst, &wmap, (s * Fm::kRowBytes) / 4, tile * P.R, w_full(w.slot));
+          tile_g2s(dst + box_bytes, &smap, s * 16, tile * P.R, w_full(w.slot));
+          w.advance(SW);
+          wrapped |= w.slot == 0;
+        }
       }
     } else if (lane == 1) {
+      pdl_wait();  // the prepared activations come from the kernel before this one
+      Ring x;
+      bool wrapped = false;
+      int s = 0;
       for (int i = 0; i < total; ++i) {
-        const int slot = i % SX;
-        if (i >= SX && !tc_wait(x_empty(slot), ((i / SX) - 1) & 1, P.status)) break;
-        mbar_arrive_expect_tx(x_full(slot), x_bytes);
-        bulk_g2s(smem_u32(xring) + static_cast<uint32_t>(slot) * x_bytes, P.xprep + static_cast<size_t>(i % n_stages) * x_bytes, x_bytes,
-                 x_full(slot));
+        if (wrapped && !tc_wait(x_empty(x.slot), x.lap ^ 1u, P.status)) break;
+        mbar_arrive_expect_tx(x_full(x.slot), x_bytes);
+        bulk_g2s(smem_u32(xring) + static_cast<uint32_t>(x.slot) * x_bytes, P.xprep + static_cast<size_t>(s) * x_bytes, x_bytes, x_full(x.slot));
+        x.advance(SX);
+        wrapped |= x.slot == 0;
+        if (++s == n_stages) s = 0;
       }
     }
   } else if (warp == 9) {
@@ -637,22 +694,28 @@ __global__ void __launch_bounds__(kConvThreads, 1)
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(NC >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);  // f16 x f16 -> f32
       const uint32_t lbo = static_cast<uint32_t>(NC / 8) * 128, sbo = 128;
+      Ring x, a;
+      int s = 0;
       for (int i = 0; i < total; ++i) {
-        const int xs = i % SX, a = i % kASlots, s = i % n_stages;
         // the activations of this stage are in shared memory, the converted weights in tensor memory
-        if (!tc_wait(x_full(xs), (i / SX) & 1, P.status) || !tc_wait(a_full(a), (i / kASlots) & 1, P.status)) break;
+        if (!tc_wait(x_full(x.slot), x.lap, P.status) || !tc_wait(a_full(a.slot), a.lap, P.status)) break;
         tc_fence_after();
-        const uint32_t xb = smem_u32(xring) + static_cast<uint32_t>(xs) * x_bytes;
+        const uint32_t xb = smem_u32(xring) + static_cast<uint32_t>(x.slot) * x_bytes;
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
           const uint64_t bdesc = smem_desc(xb + static_cast<uint32_t>(2 * c) * lbo, lbo, sbo);
-          umma_ts(tmem_base + kDColumn, tmem_base + a * kAColumns + c * 8, bdesc, idesc, (s | c) ? 1u : 0u);
+          umma_ts(tmem_base + kDColumn, tmem_base + a.slot * kAColumns + c * 8, bdesc, idesc, (s | c) ? 1u : 0u);
         }
-        umma_commit(a_empty(a));    // the A slot may be overwritten once these products are done
-        umma_commit(x_empty(xs));   // and so may the activation block
+        umma_commit(a_empty(a.slot));    // the A slot may be overwritten once these products are done
+        umma_commit(x_empty(x.slot));    // and so may the activation block
         // A tile ends here: its accumulator is complete when everything issued so far is. The next tile's first
         // product overwrites it, but waits for an A slot the converters fill only after they have read the accumulator.
-        if (s == n_stages - 1) umma_commit(d_full);
+        if (++s == n_stages) {
+          s = 0;
+          umma_commit(d_full);
+        }
+        x.advance(SX);
+        a.advance(kASlots);
       }
     }
   } else {
@@ -660,14 +723,16 @@ __global__ void __launch_bounds__(kConvThreads, 1)
     const int quarter = warp & 3, half = warp >> 2;
     const int r = quarter * 32 + lane;  // weight row of the tile = TMEM lane
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    Ring w, a;
+    int s = 0, t = 0;
+    bool a_wrapped = false;
     for (int i = 0; i < total; ++i) {
-      const int slot = i % SW, a = i % kASlots, s = i % n_stages;
-      if (!tc_wait(w_full(slot), (i / SW) & 1, P.status) || (i >= kASlots && !tc_wait(a_empty(a), ((i / kASlots) - 1) & 1, P.status))) break;
+      if (!tc_wait(w_full(w.slot), w.lap, P.status) || (a_wrapped && !tc_wait(a_empty(a.slot), a.lap ^ 1u, P.status))) break;
       tc_fence_after();
       // Rows past R read what shared memory holds behind the box (this CTA's own, see tc_launch); their lanes are
       // never read back.
-      const uint8_t* stage = smem + static_cast<size_t>(slot) * slot_bytes;
-      const uint32_t a_addr = lane_addr + a * kAColumns + half * (kAColumns / 2);
+      const uint8_t* stage = smem + static_cast<size_t>(w.slot) * slot_bytes;
+      const uint32_t a_addr = lane_addr + a.slot * kAColumns + half * (kAColumns / 2);
       const int sw = r & 7;
       // this half's 128 values = 64 bytes = pieces 4 half .. 4 half + 3 of the row's 128 bytes; 8 block scales
       const uint8_t* box = stage + r * 128;
@@ -688,16 +753,22 @@ __global__ void __launch_bounds__(kConvThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(w_empty(slot));  // the bytes are in registers / tensor memory: the stage may be refilled
-        mbar_arrive(a_full(a));
+        mbar_arrive(w_empty(w.slot));  // the bytes are in registers / tensor memory: the stage may be refilled
+        mbar_arrive(a_full(a.slot));
       }
-      if (s != n_stages - 1) continue;
+      w.advance(SW);
+      a.advance(kASlots);
+      a_wrapped |= a.slot == 0;
+      if (++s != n_stages) continue;
+      s = 0;
       // ---- the tile is over ----
-      const int t = i / n_stages;
+      const RowTerms T = row_terms<F>(P, tile_begin + t, r);
       if (!tc_wait(d_full, t & 1, P.status)) break;
       tc_fence_after();
-      pdl_wait();  // bias, y and the activation scales may come from earlier kernels
-      finish_tile<F>(P, lane_addr + kDColumn, tile_begin + t, r, lane, half, 2, 0u);
+      pdl_wait();  // y and the activation scales come from earlier kernels
+      const float inv_lo = lane < P.M ? P.inv_scales[lane] : 0.0f, inv_hi = 32 + lane < P.M ? P.inv_scales[32 + lane] : 0.0f;
+      finish_tile<F>(P, T, lane_addr + kDColumn, lane, half, 2, inv_lo, inv_hi, 0u);
+      ++t;
     }
   }
   __syncthreads();

@@ -27,7 +27,8 @@ __device__ __forceinline__ uint32_t e2m1_encode(float x) {
 template <bool kFp8>
 __global__ void __launch_bounds__(kBlock) quantize_rows_kernel(const uint16_t* __restrict__ w, uint8_t* __restrict__ q,
                                                                float* __restrict__ scale, int64_t rows, int cols) {
-  pdl_trigger();
+  // no early trigger: what this kernel writes may be the weight of the next product, whose kernels read weights
+  // before their own wait
   pdl_wait();
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (kBlock / 32) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -52,7 +53,8 @@ __global__ void __launch_bounds__(kBlock) quantize_rows_kernel(const uint16_t* _
 
 // max |w| of the whole matrix, as the bit pattern of a non-negative float (which orders like the value).
 __global__ void __launch_bounds__(kBlock) absmax_kernel(const uint16_t* __restrict__ w, int64_t n, unsigned int* out) {
-  pdl_trigger();
+  // no early trigger: what this kernel writes may be the weight of the next product, whose kernels read weights
+  // before their own wait
   pdl_wait();
   float m = 0.0f;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * kBlock + threadIdx.x; i < n; i += static_cast<int64_t>(gridDim.x) * kBlock)
@@ -65,7 +67,8 @@ __global__ void __launch_bounds__(kBlock) absmax_kernel(const uint16_t* __restri
 __global__ void __launch_bounds__(kBlock) quantize_nvfp4_kernel(const uint16_t* __restrict__ w, uint8_t* __restrict__ q,
                                                                 uint8_t* __restrict__ scale, float global, int64_t rows,
                                                                 int cols) {
-  pdl_trigger();
+  // no early trigger: what this kernel writes may be the weight of the next product, whose kernels read weights
+  // before their own wait
   pdl_wait();
   const int64_t per_row = cols / 16;
   const int64_t i = static_cast<int64_t>(blockIdx.x) * kBlock + threadIdx.x;
@@ -96,7 +99,8 @@ __global__ void __launch_bounds__(kBlock) quantize_nvfp4_kernel(const uint16_t* 
 template <int F>
 __global__ void __launch_bounds__(kBlock) dequantize_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ scale,
                                                             float global, uint16_t* __restrict__ out, int64_t rows, int cols) {
-  pdl_trigger();
+  // no early trigger: what this kernel writes may be the weight of the next product, whose kernels read weights
+  // before their own wait
   pdl_wait();
   const int64_t i = static_cast<int64_t>(blockIdx.x) * kBlock + threadIdx.x;
   if (i >= rows * cols) return;
@@ -117,7 +121,8 @@ __global__ void __launch_bounds__(kBlock) dequantize_kernel(const uint8_t* __res
 __global__ void __launch_bounds__(kBlock) quantize_act_kernel(const void* __restrict__ x, int x_dtype, int ld_x, int math,
                                                               uint8_t* __restrict__ q, int ld_q, float* __restrict__ scale,
                                                               uint8_t* __restrict__ block_scale, int ld_bs, int K) {
-  pdl_trigger();
+  // no early trigger: what this kernel writes may be the weight of the next product, whose kernels read weights
+  // before their own wait
   pdl_wait();
   __shared__ float part[kBlock / 32];
   const int m = blockIdx.x;
