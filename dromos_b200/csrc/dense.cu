@@ -119,6 +119,9 @@ int row_bytes_of(int type, int K) {
 // The product itself, arguments already validated.
 int dense_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const void* bias, int bias_dtype, void* y,
                   int y_dtype, int ld_y, int M, int N, int K, float alpha, float beta, cudaStream_t stream) {
+  // Up to 8 rows of INT8 / FP8 weights with enough rows per SM: the tensor-core product (the choice never depends on M)
+  if (M <= 8 && !force_scalar() && tc_rows_ok(w, N, K))
+    return tc_product_rows(x, x_dtype, ld_x, w, bias, bias_dtype, y, y_dtype, ld_y, M, N, K, alpha, beta, stream);
   StreamParams P{};
   P.w = static_cast<const uint8_t*>(w.data);
   P.scale = static_cast<const uint8_t*>(w.scale);
@@ -248,12 +251,11 @@ extern "C" int lx_gemm_w(const void* x, lx_dtype x_dtype, int ld_x, const lx_wei
   // Weight rows must be whole 16-byte chunks, as for the reference's tensor-core kernels.
   const int64_t rowb = row_bytes_of(w->type, K);
   if (rowb % 16 != 0 || !aligned(w->data, 16) || (w->type == LX_W_NVFP4 && K % 64 != 0)) return kNotSupported;
-  // More than 8 rows with a workspace: the tcgen05 product (LX_B200_TC=0 keeps the mma.sync streaming kernel).
-  static const bool tc_on = [] {
-    const char* v = std::getenv("LX_B200_TC");
-    return !(v && v[0] == '0');
-  }();
-  if (tc_on && M > 8 && workspace && aligned(workspace, 16) && (w->type != LX_W_NVFP4 || (K % 256 == 0 && aligned(w->scale, 16))))
+  // With a workspace every row count goes through the tcgen05 product, so that a row's bits do not depend on M
+  // (up to 8 rows of INT8 / FP8 prepare their own activations there and give the same bits). LX_B200_TC=0 keeps the
+  // mma.sync streaming kernel.
+  if (tc_enabled() && workspace && aligned(workspace, 16) && !(M <= 8 && tc_rows_ok(*w, N, K)) &&
+      (w->type != LX_W_NVFP4 || (K % 256 == 0 && aligned(w->scale, 16))))
     return tc_product(x, x_dtype, ld_x, *w, bias, bias_dtype, y, y_dtype, ld_y, M, N, K, alpha, beta, workspace,
                       static_cast<cudaStream_t>(stream));
   return dense_product(x, x_dtype, ld_x, *w, bias, bias_dtype, y, y_dtype, ld_y, M, N, K, alpha, beta,

@@ -62,6 +62,8 @@ struct TcParams {
   const uint8_t* xprep;   // prepared activations: n_stages blocks of x_bytes
   int x_bytes;            // NC * 256 * bytes per element
   const float* inv_scales;  // M f32: what each row's sum is multiplied by
+  const void* x;          // the activations themselves, for CTAs that prepare their own (up to 8 rows)
+  int ld_x;
   const void* bias;
   int bias_dtype;
   void* y;
@@ -212,34 +214,13 @@ struct Ring {
 };
 
 // ---- activation preparation ----------------------------------------------------------------------------------------
-// Block (chunk, u): 128 threads, each 16 bytes of K of every plane of activation row u. The row's largest magnitude
-// is found by every block of the row again (the row is a few KB, from L2), which saves a second kernel. With kb the
-// byte offset of k inside its stage (k % 256 times the element size), plane j of row u is column c = j * Mp + u and
-// goes to
-//   stage * x_bytes + ((kb / 16) * (NC / 8) + c / 8) * 128 + (c % 8) * 16 + kb % 16,
-// the K-major core-matrix order of the B operand. k past K is written as zero up to the end of the last stage; columns
-// that no row owns are never written (their accumulator columns are never read).
-template <int ACT, bool XBF>
-__global__ void __launch_bounds__(128) tc_prep_kernel(const void* __restrict__ x, int ld_x, int rows, int K, int NC, int Mp, int planes,
-                                                      uint8_t* __restrict__ out, float* __restrict__ inv_scales, int n_stages) {
-  constexpr int kElem = act_elem(ACT), V = 16 / kElem;
-  constexpr int kXDtype = XBF ? LX_BF16 : LX_F32;
-  pdl_trigger();
-  pdl_wait();  // the kernel before this one may still be reading the workspace
-  __shared__ float part[4];
-  const int u = blockIdx.y, tid = threadIdx.x;
-  const int k0 = (blockIdx.x * 128 + tid) * V;
-  const bool in_range = k0 < n_stages * kKS;
-  const int kb = (k0 % kKS) * kElem;
-  const size_t x_bytes = static_cast<size_t>(NC) * kKS * kElem;
-  auto address = [&](int c) {
-    return out + static_cast<size_t>(k0 / kKS) * x_bytes + (static_cast<size_t>(kb / 16) * (NC / 8) + c / 8) * 128 + (c % 8) * 16;
-  };
-  const int64_t row = static_cast<int64_t>(u) * ld_x;
-  const bool aligned16 = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && ld_x % (XBF ? 8 : 4) == 0;
-  // this thread's values first (the loads are in flight while the row's largest magnitude is found)
-  float v[V];
-  if (in_range && aligned16 && k0 + V <= K) {
+// The same functions serve the preparation kernel (more than 8 activation rows) and the CTAs that prepare their own
+// activations (up to 8 rows), so a row's digits, and with them its sums, are the same bits on either way.
+
+// V consecutive activations of a row starting at k0, as f32; zero past K.
+template <bool XBF, int V>
+__device__ __forceinline__ void load_values(const void* __restrict__ x, int64_t row, int k0, int K, bool aligned16, float (&v)[V]) {
+  if (aligned16 && k0 + V <= K) {
     if constexpr (XBF) {
       const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + row + k0);
 #pragma unroll
@@ -262,49 +243,60 @@ __global__ void __launch_bounds__(128) tc_prep_kernel(const void* __restrict__ x
     }
   } else {
 #pragma unroll
-    for (int i = 0; i < V; ++i) v[i] = (in_range && k0 + i < K) ? load_f32(x, kXDtype, row + k0 + i) : 0.0f;
+    for (int i = 0; i < V; ++i) v[i] = k0 + i < K ? load_f32(x, XBF ? LX_BF16 : LX_F32, row + k0 + i) : 0.0f;
   }
-  float sc = 1.0f;
-  if constexpr (ACT != kActBf16) {
-    float a = 0.0f;
-    if (XBF && aligned16) {
-      const uint4* xr = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + row);
-      uint32_t m = 0;  // bf16 magnitudes compare as integers
-      for (int i = tid; i < K / 8; i += 128) {
-        const uint4 q = xr[i];
-        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+}
+
+// Thread t of n: the largest magnitude among its share of a row (the callers reduce over the n threads).
+template <bool XBF>
+__device__ __forceinline__ float row_max_share(const void* __restrict__ x, int64_t row, int K, bool aligned16, int t, int n) {
+  float a = 0.0f;
+  if (XBF && aligned16) {
+    const uint4* xr = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + row);
+    uint32_t m = 0;  // bf16 magnitudes compare as integers
+    for (int i = t; i < K / 8; i += n) {
+      const uint4 q = xr[i];
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          m = max(m, (w[t] & 0x7fffu) << 16);
-          m = max(m, w[t] & 0x7fff0000u);
-        }
+      for (int z = 0; z < 4; ++z) {
+        m = max(m, (w[z] & 0x7fffu) << 16);
+        m = max(m, w[z] & 0x7fff0000u);
       }
-      a = __uint_as_float(m);
-      for (int k = K / 8 * 8 + tid; k < K; k += 128) a = fmaxf(a, fabsf(load_f32(x, kXDtype, row + k)));
-    } else if (!XBF && aligned16) {
-      const float4* xr = reinterpret_cast<const float4*>(static_cast<const float*>(x) + row);
-      for (int i = tid; i < K / 4; i += 128) {
-        const float4 q = xr[i];
-        a = fmaxf(fmaxf(a, fabsf(q.x)), fmaxf(fabsf(q.y), fmaxf(fabsf(q.z), fabsf(q.w))));
-      }
-      for (int k = K / 4 * 4 + tid; k < K; k += 128) a = fmaxf(a, fabsf(load_f32(x, kXDtype, row + k)));
-    } else {
-      for (int k = tid; k < K; k += 128) a = fmaxf(a, fabsf(load_f32(x, kXDtype, row + k)));
     }
-    a = warp_max(a);
-    if ((tid & 31) == 0) part[tid >> 5] = a;
-    __syncthreads();
-    a = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
-    // The power of two that brings the largest magnitude into the math's top binade: 2^14 for f16 (below 65504),
-    // 2^7 for e4m3 (below 448), 2^5 for the first int8 digit (at most 64).
-    constexpr int kTop = ACT == kActF16 ? 14 : ACT == kActE4m3 ? 7 : 5;
-    int ex = static_cast<int>((__float_as_uint(a) >> 23) & 0xffu);
-    ex = a > 0.0f ? min(max(ex, 30), 230) : 127 + kTop;
-    sc = __uint_as_float(static_cast<uint32_t>(254 + kTop - ex) << 23);
+    a = __uint_as_float(m);
+    for (int k = K / 8 * 8 + t; k < K; k += n) a = fmaxf(a, fabsf(load_f32(x, LX_BF16, row + k)));
+  } else if (!XBF && aligned16) {
+    const float4* xr = reinterpret_cast<const float4*>(static_cast<const float*>(x) + row);
+    for (int i = t; i < K / 4; i += n) {
+      const float4 q = xr[i];
+      a = fmaxf(fmaxf(a, fabsf(q.x)), fmaxf(fabsf(q.y), fmaxf(fabsf(q.z), fabsf(q.w))));
+    }
+    for (int k = K / 4 * 4 + t; k < K; k += n) a = fmaxf(a, fabsf(load_f32(x, LX_F32, row + k)));
+  } else {
+    for (int k = t; k < K; k += n) a = fmaxf(a, fabsf(load_f32(x, XBF ? LX_BF16 : LX_F32, row + k)));
   }
-  if (blockIdx.x == 0 && tid == 0) inv_scales[u] = 1.0f / sc;
-  if (!in_range) return;
-  uint32_t w[3][4] = {};
+  return a;
+}
+
+// The power of two that brings a row's largest magnitude into the math's top binade: 2^14 for f16 (below 65504),
+// 2^7 for e4m3 (below 448), 2^5 for the first int8 digit (at most 64); 1 for bf16 (no scaling).
+template <int ACT>
+__device__ __forceinline__ float scale_of(float a) {
+  if constexpr (ACT == kActBf16) return 1.0f;
+  constexpr int kTop = ACT == kActF16 ? 14 : ACT == kActE4m3 ? 7 : 5;
+  int ex = static_cast<int>((__float_as_uint(a) >> 23) & 0xffu);
+  ex = a > 0.0f ? min(max(ex, 30), 230) : 127 + kTop;
+  return __uint_as_float(static_cast<uint32_t>(254 + kTop - ex) << 23);
+}
+
+// V = 16 / element size scaled values to the 16 bytes of each plane.
+template <int ACT, bool XBF, int V>
+__device__ __forceinline__ void make_planes(const float (&v)[V], float sc, uint32_t (&w)[3][4]) {
+  constexpr int kElem = act_elem(ACT);
+#pragma unroll
+  for (int j = 0; j < 3; ++j)
+#pragma unroll
+    for (int q = 0; q < 4; ++q) w[j][q] = 0;
 #pragma unroll
   for (int i = 0; i < V; ++i) {
     float r = v[i] * sc;
@@ -336,7 +328,45 @@ __global__ void __launch_bounds__(128) tc_prep_kernel(const void* __restrict__ x
 #pragma unroll
     for (int j = 0; j < 3; ++j) w[j][i * kElem / 4] |= (d[j] & kMask) << ((i * kElem % 4) * 8);
   }
-  for (int j = 0; j < planes; ++j) *reinterpret_cast<uint4*>(address(j * Mp + u)) = make_uint4(w[j][0], w[j][1], w[j][2], w[j][3]);
+}
+
+// Where the 16 bytes at byte offset kb (a multiple of 16) along K of column c sit inside a stage's block: the K-major
+// core-matrix order of the B operand (8 columns x 16 bytes per core matrix).
+__device__ __forceinline__ int block_offset(int NC, int kb, int c) { return ((kb >> 4) * (NC >> 3) + (c >> 3)) * 128 + (c & 7) * 16; }
+
+// Block (chunk, u): 128 threads, each 16 bytes of K of every plane of activation row u. The row's largest magnitude
+// is found by every block of the row again (the row is a few KB, from L2), which saves a second kernel. Plane j of
+// row u is column j * Mp + u. k past K is written as zero up to the end of the last stage; columns that no row owns
+// are never written (their accumulator columns are never read).
+template <int ACT, bool XBF>
+__global__ void __launch_bounds__(128) tc_prep_kernel(const void* __restrict__ x, int ld_x, int rows, int K, int NC, int Mp, int planes,
+                                                      uint8_t* __restrict__ out, float* __restrict__ inv_scales, int n_stages) {
+  constexpr int kElem = act_elem(ACT), V = 16 / kElem;
+  pdl_trigger();
+  pdl_wait();  // the kernel before this one may still be reading the workspace
+  __shared__ float part[4];
+  const int u = blockIdx.y, tid = threadIdx.x;
+  const int k0 = (blockIdx.x * 128 + tid) * V;
+  const bool in_range = k0 < n_stages * kKS;
+  const int64_t row = static_cast<int64_t>(u) * ld_x;
+  const bool aligned16 = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && ld_x % (XBF ? 8 : 4) == 0;
+  // this thread's values first (the loads are in flight while the row's largest magnitude is found)
+  float v[V];
+  if (in_range) load_values<XBF, V>(x, row, k0, K, aligned16, v);
+  float sc = 1.0f;
+  if constexpr (ACT != kActBf16) {
+    float a = warp_max(row_max_share<XBF>(x, row, K, aligned16, tid, 128));
+    if ((tid & 31) == 0) part[tid >> 5] = a;
+    __syncthreads();
+    sc = scale_of<ACT>(fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])));
+  }
+  if (blockIdx.x == 0 && tid == 0) inv_scales[u] = 1.0f / sc;
+  if (!in_range) return;
+  uint32_t w[3][4];
+  make_planes<ACT, XBF, V>(v, sc, w);
+  uint8_t* block = out + static_cast<size_t>(k0 / kKS) * (static_cast<size_t>(NC) * kKS * kElem);
+  const int kb = (k0 % kKS) * kElem;
+  for (int j = 0; j < planes; ++j) *reinterpret_cast<uint4*>(block + block_offset(NC, kb, j * Mp + u)) = make_uint4(w[j][0], w[j][1], w[j][2], w[j][3]);
 }
 
 // ---- expanding NVFP4 -------------------------------------------------------------------------------------------------
@@ -434,14 +464,23 @@ __device__ __forceinline__ void finish_tile(const TcParams& P, const RowTerms& T
   if (chunk0 >= chunks) release();
 }
 
+// Stages of raw activations a CTA that prepares its own keeps in flight (32 bytes per thread and stage for bf16, 64 for f32).
+constexpr int own_depth(bool x_bf16) { return x_bf16 ? 4 : 2; }  // per group of preparing warps; there are two groups
+constexpr int own_staging_bytes(bool x_bf16) { return 2 * own_depth(x_bf16) * 128 * 16 * (x_bf16 ? 2 : 4); }
+
 // ---- BF16 / FP8 / INT8: weights go from shared memory straight into the tensor core ------------------------------------
 constexpr int kDirectThreads = 192;   // warps 0-3 epilogue, warp 4 producers, warp 5 MMA issuer
+constexpr int kOwnThreads = 320;      // ... and warps 6-9, the second group that prepares activation blocks
 constexpr int kDBufColumns = 256;     // two accumulators, 256 TMEM columns apart
 
-template <int F>
-__global__ void __launch_bounds__(kDirectThreads, 1) tc_direct_kernel(const __grid_constant__ CUtensorMap wmap, const TcParams P) {
+// XMODE 0: activation blocks come prepared from the workspace (bulk copies). XMODE 1 / 2: up to 8 rows of bf16 / f32
+// activations, which the CTA's epilogue warps turn into blocks themselves, stage by stage, straight into the ring: no
+// preparation kernel, no workspace, one launch.
+template <int F, int XMODE>
+__global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_direct_kernel(const __grid_constant__ CUtensorMap wmap, const TcParams P) {
   using Fm = TcFmt<F>;
   constexpr int kAct = Fm::kAct;
+  constexpr bool kOwn = XMODE != 0, kXBF = XMODE == 1;
   constexpr int kBoxes = Fm::kRowBytes / 128;    // 128-byte-wide tile copies per stage
   extern __shared__ __align__(1024) uint8_t smem[];
   const int NC = P.NC, SW = P.SW, SX = P.SX;
@@ -450,7 +489,8 @@ __global__ void __launch_bounds__(kDirectThreads, 1) tc_direct_kernel(const __gr
   // The tensor core reads 128 rows from every box, whatever R is: behind the weight ring come at least 16 KB of this
   // CTA's own shared memory (the activation ring and padding).
   uint8_t* const xring = smem + static_cast<size_t>(SW) * w_stage;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(xring + static_cast<size_t>(SX) * x_bytes);
+  // (kOwn) behind the activation ring: the threads' private pieces for raw activations in flight
+  uint64_t* bars = reinterpret_cast<uint64_t*>(xring + static_cast<size_t>(SX) * x_bytes + (kOwn ? own_staging_bytes(kXBF) : 0));
   const uint32_t bar0 = smem_u32(bars);
   auto w_full = [&](int s) { return bar0 + 8u * s; };                     // weight stage landed
   auto w_empty = [&](int s) { return bar0 + 8u * (SW + s); };             // its products are done
@@ -458,7 +498,9 @@ __global__ void __launch_bounds__(kDirectThreads, 1) tc_direct_kernel(const __gr
   auto x_empty = [&](int s) { return bar0 + 8u * (2 * SW + SX + s); };    // its products are done
   auto d_full = [&](int b) { return bar0 + 8u * (2 * SW + 2 * SX + b); };       // accumulator b is complete
   auto d_empty = [&](int b) { return bar0 + 8u * (2 * SW + 2 * SX + 2 + b); };  // accumulator b has been read
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * SW + 2 * SX + 4);
+  const uint32_t group_bar = bar0 + 8u * (2 * SW + 2 * SX + 4);           // the epilogue warps meet here
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * SW + 2 * SX + 5);
+  float* row_scale = reinterpret_cast<float*>(tmem_slot + 2);             // (kOwn) at 16 + 8 w + m: warp w's share of row m's largest magnitude
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_stages = (P.K + kKS - 1) / kKS;
@@ -472,13 +514,14 @@ __global__ void __launch_bounds__(kDirectThreads, 1) tc_direct_kernel(const __gr
       mbar_init(w_empty(s), 1);
     }
     for (int s = 0; s < SX; ++s) {
-      mbar_init(x_full(s), 1);
+      mbar_init(x_full(s), kOwn ? 4 : 1);  // the four preparing warps, or the bulk copy's bytes
       mbar_init(x_empty(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(d_full(b), 1);
       mbar_init(d_empty(b), 4);
     }
+    mbar_init(group_bar, kOwn ? 8 : 4);
     mbar_init_fence();
   }
   if (warp == 5) {
@@ -515,7 +558,7 @@ __global__ void __launch_bounds__(kDirectThreads, 1) tc_direct_kernel(const __gr
           wrapped |= w.slot == 0;
         }
       }
-    } else if (lane == 1) {
+    } else if (lane == 1 && !kOwn) {
       pdl_wait();  // the prepared activations come from the kernel before this one
       Ring x;
       bool wrapped = false;
@@ -574,17 +617,206 @@ __global__ void __launch_bounds__(kDirectThreads, 1) tc_direct_kernel(const __gr
       }
     }
   } else {
-    // ================================ epilogue ================================
-    const int r = tid;  // weight row of the tile = TMEM lane
-    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    pdl_wait();  // y and the activation scales come from earlier kernels
-    const float inv_lo = lane < P.M ? P.inv_scales[lane] : 0.0f, inv_hi = 32 + lane < P.M ? P.inv_scales[32 + lane] : 0.0f;
-    for (int tile = tile_begin; tile < tile_end; ++tile) {
-      const int t = tile - tile_begin, buf = t & 1;
-      const RowTerms T = row_terms<F>(P, tile, r);
-      if (!tc_wait(d_full(buf), (t >> 1) & 1, P.status)) break;
-      tc_fence_after();
-      finish_tile<F>(P, T, lane_addr + buf * kDBufColumns, lane, 0, 1, inv_lo, inv_hi, d_empty(buf));
+    // ================================ epilogue (and, if kOwn, the activation blocks) ================================
+    // kOwn: two groups of four warps (0-3 and 6-9) prepare the activation blocks of alternate stages; the first group
+    // also runs the epilogue, its thread r owning accumulator lane r.
+    const int group = warp >= 6 ? 1 : 0;
+    const int gtid = group ? tid - 192 : tid, gwarp = gtid >> 5;
+    const int r = gtid;  // weight row of the tile = TMEM lane (group 0)
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(gwarp * 32) << 16);
+    pdl_wait();  // the activations (or their prepared form) and y come from earlier kernels
+    if constexpr (!kOwn) {
+      const float inv_lo = lane < P.M ? P.inv_scales[lane] : 0.0f, inv_hi = 32 + lane < P.M ? P.inv_scales[32 + lane] : 0.0f;
+      for (int tile = tile_begin; tile < tile_end; ++tile) {
+        const int t = tile - tile_begin, buf = t & 1;
+        const RowTerms T = row_terms<F>(P, tile, r);
+        if (!tc_wait(d_full(buf), (t >> 1) & 1, P.status)) break;
+        tc_fence_after();
+        finish_tile<F>(P, T, lane_addr + buf * kDBufColumns, lane, 0, 1, inv_lo, inv_hi, d_empty(buf));
+      }
+    } else {
+      static_assert(act_elem(kAct) == 1, "CTAs prepare their own activations for the 8-bit maths only");
+      constexpr int V = 16;
+      constexpr int kPiece = kXBF ? 8 : 4;  // activations per 16 bytes
+      constexpr int kUnitBytes = V * (kXBF ? 2 : 4);
+      constexpr int D = own_depth(kXBF);
+      const bool aligned16 = (reinterpret_cast<uintptr_t>(P.x) & 15) == 0 && P.ld_x % kPiece == 0;
+      bool ok = true;
+      // ---- first pass: the largest magnitude of every row, by all 256 preparing threads ----
+      {
+        const int t256 = group * 128 + gtid;
+        float a[8];
+#pragma unroll
+        for (int m = 0; m < 8; ++m) a[m] = 0.0f;
+        if (aligned16) {
+          const int pieces = P.K / kPiece;  // whole 16-byte pieces per row
+          for (int p0 = t256; p0 < pieces; p0 += 512) {
+            uint4 q[2][8];
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+              for (int m = 0; m < 8; ++m) {
+                q[h][m] = make_uint4(0, 0, 0, 0);
+                const int p = p0 + 256 * h;
+                if (m < P.M && p < pieces)
+                  q[h][m] = *reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(P.x) +
+                                                            (static_cast<int64_t>(m) * P.ld_x + static_cast<int64_t>(p) * kPiece) * (kXBF ? 2 : 4));
+              }
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+              for (int m = 0; m < 8; ++m) {
+                const uint32_t w[4] = {q[h][m].x, q[h][m].y, q[h][m].z, q[h][m].w};
+#pragma unroll
+                for (int z = 0; z < 4; ++z) {
+                  if constexpr (kXBF) a[m] = fmaxf(a[m], fmaxf(fabsf(__uint_as_float(w[z] << 16)), fabsf(__uint_as_float(w[z] & 0xffff0000u))));
+                  else a[m] = fmaxf(a[m], fabsf(__uint_as_float(w[z])));
+                }
+              }
+          }
+          for (int m = 0; m < P.M; ++m)
+            for (int k = pieces * kPiece + t256; k < P.K; k += 256)
+              a[m] = fmaxf(a[m], fabsf(load_f32(P.x, kXBF ? LX_BF16 : LX_F32, static_cast<int64_t>(m) * P.ld_x + k)));
+        } else {
+          for (int m = 0; m < P.M; ++m)
+            for (int k = t256; k < P.K; k += 256)
+              a[m] = fmaxf(a[m], fabsf(load_f32(P.x, kXBF ? LX_BF16 : LX_F32, static_cast<int64_t>(m) * P.ld_x + k)));
+        }
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {
+          const float v = warp_max(a[m]);
+          if (lane == 0) row_scale[(group * 4 + gwarp) * 8 + m] = v;  // this warp's share of row m
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(group_bar);
+        ok = tc_wait(group_bar, 0, P.status);
+      }
+      auto row_scale_of = [&](int row) {
+        float v = 0.0f;
+#pragma unroll
+        for (int w8 = 0; w8 < 8; ++w8) v = fmaxf(v, row_scale[w8 * 8 + row]);
+        return scale_of<kAct>(v);
+      };
+      // ---- second pass: the digits, stage by stage into the ring ----
+      // Thread (m = gtid % 8, kg = gtid / 8) owns, in each of its group's stages, the 16 values k = 16 kg .. 16 kg + 15
+      // of activation row m: 16 bytes of each plane. Its raw activations travel from global memory into a private piece
+      // of shared memory with cp.async, D of the group's stages ahead.
+      const int m = gtid & 7, kg = gtid >> 3;
+      const bool row_live = m < P.M;
+      const float sc = row_live ? row_scale_of(m) : 1.0f;
+      const float inv = lane < P.M ? 1.0f / row_scale_of(lane) : 0.0f;  // lane l: row l (finish_tile's layout)
+      const uint8_t* xrow = static_cast<const uint8_t*>(P.x) + static_cast<int64_t>(m) * P.ld_x * (kXBF ? 2 : 4);
+      uint8_t* const staging = xring + static_cast<size_t>(SX) * x_bytes + static_cast<size_t>(group) * D * 128 * kUnitBytes;
+      const int row_bytes = P.K * (kXBF ? 2 : 4);
+      // stage s of a tile (or nothing, s < 0) into staging slot d; always one cp.async group
+      auto issue = [&](int s, int d) {
+        if (row_live && s >= 0) {
+          uint8_t* dst = staging + (static_cast<size_t>(d) * 128 + gtid) * kUnitBytes;
+          const int at = (s * kKS + kg * V) * (kXBF ? 2 : 4);  // byte offset of the unit in its row
+          if (aligned16) {
+#pragma unroll
+            for (int q = 0; q < kUnitBytes / 16; ++q) {
+              const int left = min(16, max(0, row_bytes - (at + 16 * q)));  // bytes of the row in this piece; the rest reads as zero
+              asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst + 16 * q)), "l"(xrow + (left ? at + 16 * q : 0)),
+                           "r"(left)
+                           : "memory");
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < V; ++i) {
+              const int k = s * kKS + kg * V + i;
+              if constexpr (kXBF) reinterpret_cast<uint16_t*>(dst)[i] = k < P.K ? reinterpret_cast<const uint16_t*>(xrow)[k] : uint16_t(0);
+              else reinterpret_cast<float*>(dst)[i] = k < P.K ? reinterpret_cast<const float*>(xrow)[k] : 0.0f;
+            }
+          }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+      };
+      // the oldest group in flight has landed: its unit as f32
+      auto take = [&](int d, float (&v)[V]) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(D - 1) : "memory");
+        const uint8_t* src = staging + (static_cast<size_t>(d) * 128 + gtid) * kUnitBytes;
+        if constexpr (kXBF) {
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const uint4 t = *reinterpret_cast<const uint4*>(src + 16 * q);
+            const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int z = 0; z < 4; ++z) {
+              v[8 * q + 2 * z] = __uint_as_float(w[z] << 16);
+              v[8 * q + 2 * z + 1] = __uint_as_float(w[z] & 0xffff0000u);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float4 t = *reinterpret_cast<const float4*>(src + 16 * q);
+            v[4 * q] = t.x, v[4 * q + 1] = t.y, v[4 * q + 2] = t.z, v[4 * q + 3] = t.w;
+          }
+        }
+      };
+      int next_finish = tile_begin;  // (group 0) the first tile whose accumulator has not been read yet
+      auto finish = [&](int tile) {
+        const int t = tile - tile_begin, buf = t & 1;
+        const RowTerms T = row_terms<F>(P, tile, r);
+        if (!tc_wait(d_full(buf), (t >> 1) & 1, P.status)) return false;
+        tc_fence_after();
+        finish_tile<F>(P, T, lane_addr + buf * kDBufColumns, lane, 0, 1, inv, 0.0f, d_empty(buf));
+        return true;
+      };
+      const int total = (tile_end - tile_begin) * n_stages;
+      // This group's stages are i = group, group + 2, ...; stage i of the CTA is stage i % n_stages of tile i / n_stages.
+      auto step2 = [&](int& s_in_tile, int& tile_of) {  // two stages on
+        s_in_tile += 2;
+        while (s_in_tile >= n_stages) s_in_tile -= n_stages, ++tile_of;
+      };
+      int ahead_i = group, ahead_s = group, ahead_tile = 0;  // the next stage to fetch
+      while (ahead_s >= n_stages) ahead_s -= n_stages;
+      for (int d = 0; d < D; ++d) {
+        issue(ahead_i < total ? ahead_s : -1, d);
+        ahead_i += 2;
+        step2(ahead_s, ahead_tile);
+      }
+      Ring x;
+      if (group) x.advance(SX);
+      int d = 0, tile = tile_begin, s = group;
+      while (s >= n_stages) s -= n_stages, ++tile;
+      for (int i = group; i < total && ok; i += 2) {
+        if (group == 0) {
+          // The products of this stage's tile need the accumulator of the tile two before it: that one must have been
+          // read by now. The one before, as soon as it happens to be complete.
+          while (ok && next_finish <= tile - 2) ok = finish(next_finish++);
+          if (ok && next_finish < tile && mbar_try_wait(d_full((next_finish - tile_begin) & 1), ((next_finish - tile_begin) >> 1) & 1))
+            ok = finish(next_finish++);
+          if (!ok) break;
+        }
+        float v[V];
+        take(d, v);
+        uint32_t w[3][4];
+        make_planes<kAct, kXBF, V>(v, sc, w);
+        issue(ahead_i < total ? ahead_s : -1, d);
+        ahead_i += 2;
+        step2(ahead_s, ahead_tile);
+        if (++d == D) d = 0;
+        if (i >= SX && !tc_wait(x_empty(x.slot), x.lap ^ 1u, P.status)) {
+          ok = false;
+          break;
+        }
+        uint8_t* block = xring + static_cast<size_t>(x.slot) * x_bytes;
+        if (row_live) {
+          for (int j = 0; j < P.planes; ++j)
+            *reinterpret_cast<uint4*>(block + block_offset(NC, kg * 16, j * P.Mp + m)) = make_uint4(w[j][0], w[j][1], w[j][2], w[j][3]);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads what these threads wrote
+        __syncwarp();
+        if (lane == 0) mbar_arrive(x_full(x.slot));
+        x.advance(SX);
+        x.advance(SX);
+        step2(s, tile);
+      }
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      if (group == 0)
+        while (ok && next_finish < tile_end) ok = finish(next_finish++);
     }
   }
   __syncthreads();
@@ -818,7 +1050,7 @@ int tile_rows(int N, int sms) {
   return std::min(kBM, std::max(kMinTileRows, rows));
 }
 
-template <int F>
+template <int F, int XMODE>
 int tc_launch(const lx_weight& w, TcParams P, cudaStream_t stream) {
   using Fm = TcFmt<F>;
   constexpr int kBoxes = Fm::kRowBytes / 128;
@@ -829,12 +1061,14 @@ int tc_launch(const lx_weight& w, TcParams P, cudaStream_t stream) {
   // NVFP4 keeps a stage's box and its block scales in a slot of twice the box, so that every box starts 1024-aligned.
   const int w_stage = F == LX_W_NVFP4 ? 2 * P.box_bytes : kBoxes * P.box_bytes;
   constexpr int kBudget = 204 * 1024;  // leaves room for the 16 KB the tensor core may read past the last box
+  constexpr int kStaging = XMODE == 0 ? 0 : own_staging_bytes(XMODE == 1);
   P.SX = P.x_bytes > 24 * 1024 ? 2 : 3;
-  P.SW = std::min(12, (kBudget - P.SX * P.x_bytes) / w_stage);
+  P.SW = std::min(12, (kBudget - P.SX * P.x_bytes - kStaging) / w_stage);
   if (P.SW < 2) return kNotSupported;
   // Tensor memory is taken whole (512 columns), so exactly one CTA may live on an SM: ask for more than half of its
   // shared memory whatever the rings need.
-  const size_t smem = std::max<size_t>(static_cast<size_t>(P.SW) * w_stage + std::max(P.SX * P.x_bytes, 16 * 1024) + 1024, 120 * 1024);
+  const size_t smem =
+      std::max<size_t>(static_cast<size_t>(P.SW) * w_stage + std::max(P.SX * P.x_bytes + kStaging, 16 * 1024) + 1024, 120 * 1024);
   alignas(64) CUtensorMap wmap, smap;
   memset(&wmap, 0, sizeof(wmap));
   memset(&smap, 0, sizeof(smap));
@@ -843,12 +1077,13 @@ int tc_launch(const lx_weight& w, TcParams P, cudaStream_t stream) {
   const int tiles = (P.N + P.R - 1) / P.R;
   const int grid = std::min(tiles, sms);
   if constexpr (F == LX_W_NVFP4) {
+    static_assert(XMODE == 0, "NVFP4 takes prepared activations");
     if (int e = make_tile_map(&smap, w.scale, P.K / 16, P.N, 16, P.R, 1, false)) return e;
-    if (int e = allow_big_smem<F>(tc_nvfp4_kernel)) return e;
+    if (int e = allow_big_smem<F * 4>(tc_nvfp4_kernel)) return e;
     return launch_kernel(tc_nvfp4_kernel, dim3(grid), dim3(kConvThreads), smem, stream, wmap, smap, P);
   } else {
-    if (int e = allow_big_smem<F>(tc_direct_kernel<F>)) return e;
-    return launch_kernel(tc_direct_kernel<F>, dim3(grid), dim3(kDirectThreads), smem, stream, wmap, P);
+    if (int e = allow_big_smem<F * 4 + XMODE>(tc_direct_kernel<F, XMODE>)) return e;
+    return launch_kernel(tc_direct_kernel<F, XMODE>, dim3(grid), dim3(XMODE ? kOwnThreads : kDirectThreads), smem, stream, wmap, P);
   }
 }
 
@@ -858,7 +1093,58 @@ int act_of(int wtype) {
 // Activation rows one pass takes: the block of one stage stays within 48 KB.
 int rows_per_pass(int act, bool x_bf16) { return (act == kActBf16 && !x_bf16) ? 32 : kMaxRows; }
 
+// Fills what every pass shares.
+TcParams base_params(const lx_weight& w, const void* bias, int bias_dtype, int y_dtype, int ld_y, int N, int K, float alpha, float beta,
+                     int act, bool x_bf16, int rows) {
+  TcParams P{};
+  P.scale = static_cast<const uint8_t*>(w.scale);
+  P.global = w.global;
+  P.N = N, P.K = K, P.M = rows;
+  P.planes = act_planes(act, x_bf16);
+  P.digit = act == kActS8 ? 0.0078125f : act == kActE4m3 ? 0.0625f : 1.0f;
+  P.Mp = (rows + 7) / 8 * 8;
+  P.NC = (P.planes * P.Mp + 15) / 16 * 16;
+  P.x_bytes = P.NC * kKS * act_elem(act);
+  P.bias = bias, P.bias_dtype = bias_dtype;
+  P.y_dtype = y_dtype, P.ld_y = ld_y;
+  P.alpha = alpha, P.beta = beta;
+  P.status = status_word();
+  return P;
+}
+
 }  // namespace
+
+bool tc_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("LX_B200_TC");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+
+// Can up to 8 activation rows go through the tensor-core product without a workspace? INT8 and FP8 weights whose
+// tiles come out at 64 rows or more (smaller ones leave the tensor pipe's instruction rate, not HBM, as the bound),
+// rows of whole 16-byte pieces. The answer depends on the weight and its shape only, never on the row count, so that
+// a row's bits do not depend on its batch. (BF16 stays with the streaming kernel, whose bits the lossless BF16X
+// format must reproduce.)
+bool tc_rows_ok(const lx_weight& w, int N, int K) {
+  if (!tc_enabled() || (w.type != LX_W_INT8 && w.type != LX_W_FP8)) return false;
+  if (K % 16 != 0 || (reinterpret_cast<uintptr_t>(w.data) & 15) != 0) return false;
+  const int sms = sm_count();
+  return sms > 0 && tile_rows(N, sms) >= 64;
+}
+
+// Up to 8 activation rows, prepared by the product kernel itself: one launch, no workspace.
+int tc_product_rows(const void* x, int x_dtype, int ld_x, const lx_weight& w, const void* bias, int bias_dtype, void* y, int y_dtype,
+                    int ld_y, int M, int N, int K, float alpha, float beta, cudaStream_t stream) {
+  const bool x_bf16 = x_dtype == LX_BF16;
+  TcParams P = base_params(w, bias, bias_dtype, y_dtype, ld_y, N, K, alpha, beta, act_of(w.type), x_bf16, M);
+  P.x = x, P.ld_x = ld_x;
+  P.y = y;
+  if (w.type == LX_W_INT8) return x_bf16 ? tc_launch<LX_W_INT8, 1>(w, P, stream) : tc_launch<LX_W_INT8, 2>(w, P, stream);
+  if (w.type == LX_W_FP8) return x_bf16 ? tc_launch<LX_W_FP8, 1>(w, P, stream) : tc_launch<LX_W_FP8, 2>(w, P, stream);
+  return kNotSupported;
+}
 
 // The product, in passes of at most 64 activation rows. workspace: at least tc_workspace_bytes.
 int tc_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const void* bias, int bias_dtype, void* y, int y_dtype,
@@ -870,23 +1156,11 @@ int tc_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const v
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   for (int m0 = 0; m0 < M; m0 += per_pass) {
     const int rows = std::min(per_pass, M - m0);
-    TcParams P{};
-    P.scale = static_cast<const uint8_t*>(w.scale);
-    P.global = w.global;
-    P.N = N, P.K = K, P.M = rows;
-    P.planes = act_planes(act, x_bf16);
-    P.digit = act == kActS8 ? 0.0078125f : act == kActE4m3 ? 0.0625f : 1.0f;
-    P.Mp = (rows + 7) / 8 * 8;
-    P.NC = (P.planes * P.Mp + 15) / 16 * 16;
-    P.x_bytes = P.NC * kKS * elem;
+    TcParams P = base_params(w, bias, bias_dtype, y_dtype, ld_y, N, K, alpha, beta, act, x_bf16, rows);
     const TcLayout L(P.NC, elem, n_stages);
     P.xprep = ws;
     P.inv_scales = reinterpret_cast<const float*>(ws + L.scales);
-    P.bias = bias, P.bias_dtype = bias_dtype;
     P.y = static_cast<uint8_t*>(y) + static_cast<int64_t>(m0) * ld_y * (y_dtype == LX_BF16 ? 2 : 4);
-    P.y_dtype = y_dtype, P.ld_y = ld_y;
-    P.alpha = alpha, P.beta = beta;
-    P.status = status_word();
     const uint8_t* xrow = static_cast<const uint8_t*>(x) + static_cast<int64_t>(m0) * ld_x * (x_bf16 ? 2 : 4);
     const int per_block = 128 * 16 / elem;
     const dim3 prep_grid((n_stages * kKS + per_block - 1) / per_block, rows);
@@ -908,10 +1182,10 @@ int tc_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const v
     if (pe) return pe;
     int e;
     switch (w.type) {
-      case LX_W_BF16: e = tc_launch<LX_W_BF16>(w, P, stream); break;
-      case LX_W_INT8: e = tc_launch<LX_W_INT8>(w, P, stream); break;
-      case LX_W_FP8: e = tc_launch<LX_W_FP8>(w, P, stream); break;
-      case LX_W_NVFP4: e = tc_launch<LX_W_NVFP4>(w, P, stream); break;
+      case LX_W_BF16: e = tc_launch<LX_W_BF16, 0>(w, P, stream); break;
+      case LX_W_INT8: e = tc_launch<LX_W_INT8, 0>(w, P, stream); break;
+      case LX_W_FP8: e = tc_launch<LX_W_FP8, 0>(w, P, stream); break;
+      case LX_W_NVFP4: e = tc_launch<LX_W_NVFP4, 0>(w, P, stream); break;
       default: e = kNotSupported;
     }
     if (e) return e;

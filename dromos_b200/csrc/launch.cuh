@@ -159,6 +159,10 @@ int launch_stream(StreamParams P, cudaStream_t stream, int64_t stack_rows) {
 int tc_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const void* bias, int bias_dtype, void* y, int y_dtype,
                int ld_y, int M, int N, int K, float alpha, float beta, void* workspace, cudaStream_t stream);
 int64_t tc_workspace_bytes(int M, int K);
+bool tc_enabled();
+bool tc_rows_ok(const lx_weight& w, int N, int K);
+int tc_product_rows(const void* x, int x_dtype, int ld_x, const lx_weight& w, const void* bias, int bias_dtype, void* y, int y_dtype,
+                    int ld_y, int M, int N, int K, float alpha, float beta, cudaStream_t stream);
 
 struct ActLayout {
   int64_t ld_q, ld_bs;

@@ -141,6 +141,40 @@ def test_gemm_w_tiles_shared_between_ctas(lx, fmt, case):
     assert np.array_equal(outs[0], outs[1]), "two runs differ"
 
 
+WIDE = [O.W_INT8, O.W_FP8]  # formats whose small batches run on the tensor-core product when N gives every SM >= 64 rows
+
+
+@pytest.mark.parametrize("fmt", WIDE, ids=lambda f: NAMES[f])
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("x_f32", [False, True], ids=["xbf16", "xf32"])
+def test_gemv_wide_weight(lx, fmt, M, x_f32):
+    """N large enough that lx_gemv_w takes the tcgen05 path (tiles of 65 rows, a ragged last tile, K ending inside a
+    stage), with bias, alpha and beta."""
+    N, K = 9605, 1040
+    got, want, y0 = run(lx, fmt, M, N, K, seed=20 + M, x_f32=x_f32, bias_dtype=abi.BF16, alpha=1.5, beta=-0.5)
+    check(got, want, y0, N, True, f"{NAMES[fmt]} M={M}")
+
+
+@pytest.mark.parametrize("fmt", WIDE, ids=lambda f: NAMES[f])
+def test_wide_weight_rows_do_not_depend_on_batch(lx, fmt):
+    """On the tensor-core path too, a row's bits are the same alone, in any batch of up to 8 (which prepare their own
+    activations) and in an lx_gemm_w call of 16 rows (activations prepared by a kernel of their own)."""
+    N, K = 9605, 1040
+    w_bits = util.bf16_normal((N, K), 0.02, 31)
+    dw = util.DeviceWeight(util.make_weight(w_bits, fmt))
+    x = util.bf16_normal((16, K), 1.0, 32)
+    x_dev = util.dev(x)
+    big = torch.full((16, N), float("nan"), device="cuda")
+    ws = torch.empty(lx.lx_gemm_workspace_bytes(16, K, 0), dtype=torch.uint8, device="cuda")
+    assert util.gemv(lx, x_dev, abi.BF16, K, dw, big, abi.F32, N, 16, N, K, fn="lx_gemm_w", workspace=ws) == 0
+    want = util.host(big).view(np.uint32)
+    for M in (1, 2, 5, 8):
+        y = torch.full((M, N), float("nan"), device="cuda")
+        assert util.gemv(lx, x_dev, abi.BF16, K, dw, y, abi.F32, N, M, N, K) == 0
+        assert np.array_equal(util.host(y).view(np.uint32), want[:M]), f"rows at M={M} differ from the same rows at M=16"
+    util.check_status(lx)
+
+
 @pytest.mark.parametrize("fmt", FORMATS, ids=lambda f: NAMES[f])
 def test_rows_do_not_depend_on_batch_and_runs_repeat(lx, fmt):
     N, K = 256, 2048
