@@ -248,6 +248,35 @@ def main():
             if world > 1:
                 dist.all_gather_into_tensor(gathered[M].view(world * M, n1 - n0), ys[M])
 
+    # The decode loop is launch-bound from Python (a product is ~15 us of GPU time), so, like the reference engine's
+    # decode loop, the steps are captured once into CUDA graphs (one per rotation position, programmatic dependent
+    # launch edges included) and replayed; LX_BENCH_GRAPHS=0 launches every kernel from Python instead.
+    use_graphs = os.environ.get("LX_BENCH_GRAPHS", "1") != "0"
+
+    def capture(fn):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        return g
+
+    def replayer(fn, period):
+        """fn(i) for i in range(period) captured as graphs; returns run(i) that replays graph i % period, and how many
+        of this library's kernels one pass over the period launches."""
+        for i in range(period):  # every allocation (workspaces, the status word) happens before capture
+            fn(i)
+        torch.cuda.synchronize()
+        before = lib.lx_b200_kernel_launches()
+        if not use_graphs:
+            fn(0)
+            return fn, (lib.lx_b200_kernel_launches() - before) * period
+        try:
+            graphs = [capture(lambda i=i: fn(i)) for i in range(period)]
+        except Exception as e:  # e.g. a collective that cannot be captured: fall back to eager launches
+            print(f"[bench] graph capture failed ({type(e).__name__}: {e}); launching eagerly", file=sys.stderr)
+            torch.cuda.synchronize()
+            return fn, 0
+        return (lambda i: graphs[i % period].replay()), lib.lx_b200_kernel_launches() - before
+
     def timed(fn, n):
         if world > 1:
             dist.barrier()
@@ -263,30 +292,35 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
+    period = copies // len(Ms)  # steps until the rotation comes back to the first weight copy
+    run_step, launches_per_period = replayer(step, period)
     for i in range(args.warmup):
-        step(i)
-    launches0 = lib.lx_b200_kernel_launches()
+        run_step(i)
     with ClockSampler(local) as clocks:
-        ms = timed(lambda i: step(args.warmup + i), args.steps)
-    launches = lib.lx_b200_kernel_launches() - launches0
+        ms = timed(lambda i: run_step(args.warmup + i), args.steps)
+    launches = launches_per_period * args.steps // period
     value = total_step_bytes * args.steps / (ms * 1e-3) / 1e12
 
-    # ---- the streaming kernel alone, per M (events on the launching stream, no collective) ----
+    # ---- the product kernels alone, per M (events on the launching stream, no collective): one graph holds a pass
+    # over every weight copy ----
     per_m, k_bytes, k_ms = {}, 0.0, 0.0
-    reps = max(10, min(200, int(2e9 // shard_bytes)))
+    reps = max(2, min(20, int(4e9 // (shard_bytes * copies))))
     for M in Ms:
-        def one(i, M=M):
-            layers[i % copies](xs[M], ys[M])
-        for i in range(3):
-            one(i)
-        t = timed(one, reps) / reps
+        def sweep(_, M=M):
+            for c in range(copies):
+                layers[c](xs[M], ys[M])
+        run_sweep, _ = replayer(sweep, 1)
+        for i in range(2):
+            run_sweep(i)
+        t = timed(run_sweep, reps) / (reps * copies)
         per_m[str(M)] = {"us": t * 1e3, "GB/s": shard_bytes / (t * 1e-3) / 1e9}
         k_bytes += shard_bytes
         k_ms += t
     peak, peak_kind = measured_peak_gbs()
     achieved = k_bytes / (k_ms * 1e-3) / 1e9
+    dominant = "tc_direct_kernel" if wtype in (abi.W_INT8, abi.W_FP8) else "stream_kernel"
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
-                "peak_source": f"{peak_kind} copy bandwidth (burst)", "kernel": "stream_kernel", "per_m": per_m,
+                "peak_source": f"{peak_kind} copy bandwidth (burst)", "kernel": dominant, "per_m": per_m,
                 "algorithmic_bytes_per_launch": shard_bytes}
 
     # ---- end to end through the host-buffer API: pinned activations in, outputs out, every step ----
@@ -294,7 +328,7 @@ def main():
     yh = {M: torch.empty((M, (n1 - n0) * (world if world > 1 else 1)), dtype=torch.float32).pin_memory() for M in Ms}
     xd = {M: torch.empty_like(xs[M]) for M in Ms}
 
-    def e2e_step(i):
+    def e2e_work(i):
         for j, M in enumerate(Ms):
             xd[M].copy_(xh[M], non_blocking=True)
             layers[(i * len(Ms) + j) % copies](xd[M], ys[M])
@@ -303,6 +337,11 @@ def main():
                 yh[M].copy_(gathered[M].permute(1, 0, 2).reshape(M, -1), non_blocking=True)
             else:
                 yh[M].copy_(ys[M], non_blocking=True)
+
+    run_e2e, _ = replayer(e2e_work, period)
+
+    def e2e_step(i):
+        run_e2e(i)
         torch.cuda.current_stream().synchronize()  # the caller reads the result before the next step
 
     for i in range(3):
@@ -319,7 +358,7 @@ def main():
     out = {"metric": metric, "value": value, "unit": "TB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
            "vs_baseline": None, "dtype": DTYPE[wtype], "data": "synthetic", "config": config, "roofline": roofline, "e2e": e2e,
-           "gpu_launches": int(launches), "clocks": clocks.summary(), "pct_of_8TBs": value / 8.0 / max(world, 1),
+           "gpu_launches": int(launches), "launch": "CUDA graphs" if use_graphs else "eager", "clocks": clocks.summary(), "pct_of_8TBs": value / 8.0 / max(world, 1),
            "kernel_status": status}
     if world == 1:
         if cpu_library() is not None:

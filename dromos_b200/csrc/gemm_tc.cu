@@ -40,7 +40,6 @@ namespace b200 {
 namespace {
 
 constexpr int kBM = 128;          // rows the tensor core multiplies = TMEM lanes; a tile uses the first R of them
-constexpr int kKS = 256;          // values of K per stage
 constexpr int kTmemColumns = 512;
 constexpr int kMinTileRows = 32;  // below this the instruction rate of the tensor pipe, not HBM, would bound a stage
 constexpr int kMaxRows = 64;      // activation rows per pass
@@ -48,6 +47,10 @@ constexpr int kStatusTcWait = 5;  // a bounded wait of this kernel gave up
 
 // How activations become B-operand columns.
 enum ActMath { kActBf16 = 0, kActF16 = 1, kActE4m3 = 2, kActS8 = 3 };
+constexpr int act_elem(int act) { return act == kActBf16 || act == kActF16 ? 2 : 1; }
+// Values of K per stage. (512 for the 8-bit formats halves the per-stage bookkeeping but was no faster, and the
+// activation blocks of 32 rows and more no longer fit beside a useful weight ring.)
+constexpr int ks_of(int) { return 256; }
 
 struct TcParams {
   const uint8_t* scale;   // f32 [N] (INT8 / FP8); NVFP4 block scales come through the tensor map
@@ -73,11 +76,11 @@ struct TcParams {
   int SW, SX;             // depth of the weight ring and of the activation ring
 };
 
-// Where the parts of the workspace begin, for a pass of NC columns of `elem` bytes over n_stages stages.
+// Where the parts of the workspace begin, for a pass of NC columns of the activation math `act` over n_stages stages.
 struct TcLayout {
   int64_t scales, total;
-  TcLayout(int NC, int elem, int64_t n_stages) {
-    scales = n_stages * NC * kKS * elem;
+  TcLayout(int NC, int act, int64_t n_stages) {
+    scales = n_stages * NC * ks_of(act) * act_elem(act);
     total = scales + 256;
   }
 };
@@ -104,7 +107,6 @@ struct TcFmt<LX_W_NVFP4> {
   static constexpr int kRowBytes = 128;
   static constexpr int kAct = kActF16;
 };
-constexpr int act_elem(int act) { return act == kActBf16 || act == kActF16 ? 2 : 1; }
 inline int act_planes(int act, bool x_bf16) {
   return act == kActS8 ? 3 : act == kActE4m3 ? (x_bf16 ? 2 : 3) : (x_bf16 ? 1 : 2);
 }
@@ -292,41 +294,58 @@ __device__ __forceinline__ float scale_of(float a) {
 // V = 16 / element size scaled values to the 16 bytes of each plane.
 template <int ACT, bool XBF, int V>
 __device__ __forceinline__ void make_planes(const float (&v)[V], float sc, uint32_t (&w)[3][4]) {
-  constexpr int kElem = act_elem(ACT);
 #pragma unroll
   for (int j = 0; j < 3; ++j)
 #pragma unroll
     for (int q = 0; q < 4; ++q) w[j][q] = 0;
+  if constexpr (ACT == kActBf16 || ACT == kActF16) {
 #pragma unroll
-  for (int i = 0; i < V; ++i) {
-    float r = v[i] * sc;
-    uint32_t d[3] = {0, 0, 0};
-    if constexpr (ACT == kActBf16) {
-      d[0] = f32_to_bf16_bits(r);
-      if (!XBF) d[1] = f32_to_bf16_bits(r - bf16_bits_to_f32(d[0]));
-    } else if constexpr (ACT == kActF16) {
-      const __half h = __float2half_rn(r);
-      d[0] = __half_as_ushort(h);
-      if (!XBF) d[1] = __half_as_ushort(__float2half_rn(r - __half2float(h)));
-    } else if constexpr (ACT == kActE4m3) {
-      // digits in base 16 of the scaled value: each e4m3 takes the next four significant bits
+    for (int i = 0; i < V; ++i) {
+      const float r = v[i] * sc;
+      uint32_t hi, lo = 0;
+      if constexpr (ACT == kActBf16) {
+        hi = f32_to_bf16_bits(r);
+        if (!XBF) lo = f32_to_bf16_bits(r - bf16_bits_to_f32(hi));
+      } else {
+        const __half h = __float2half_rn(r);
+        hi = __half_as_ushort(h);
+        if (!XBF) lo = __half_as_ushort(__float2half_rn(r - __half2float(h)));
+      }
+      w[0][i / 2] |= (hi & 0xffffu) << ((i % 2) * 16);
+      w[1][i / 2] |= (lo & 0xffffu) << ((i % 2) * 16);
+    }
+  } else if constexpr (ACT == kActE4m3) {
+    // Digits in base 16 of the scaled value: each e4m3 takes the next four significant bits. Two values per
+    // conversion instruction (saturating, round to nearest even); the digit's value comes back through f16, exactly.
+#pragma unroll
+    for (int i = 0; i < V; i += 2) {
+      float r0 = v[i] * sc, r1 = v[i + 1] * sc;
 #pragma unroll
       for (int j = 0; j < (XBF ? 2 : 3); ++j) {
-        d[j] = __nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3);
-        r = (r - e4m3_to_f32(d[j])) * 16.0f;
-      }
-    } else {
-      // digits in base 128 of the scaled value, each in [-64, 64]
-#pragma unroll
-      for (int j = 0; j < 3; ++j) {
-        const float q = rintf(r);
-        d[j] = static_cast<uint32_t>(static_cast<int>(q)) & 0xffu;
-        r = (r - q) * 128.0f;
+        uint32_t pair;  // bits 0-7: the digit of r0, bits 8-15: of r1
+        asm("{ .reg .b16 p; cvt.rn.satfinite.e4m3x2.f32 p, %2, %1; cvt.u32.u16 %0, p; }" : "=r"(pair) : "f"(r0), "f"(r1));
+        uint32_t h2;
+        asm("{ .reg .b16 p; cvt.u16.u32 p, %1; cvt.rn.f16x2.e4m3x2 %0, p; }" : "=r"(h2) : "r"(pair));
+        const __half2 back = *reinterpret_cast<const __half2*>(&h2);
+        r0 = (r0 - __low2float(back)) * 16.0f;
+        r1 = (r1 - __high2float(back)) * 16.0f;
+        w[j][i / 4] |= pair << ((i % 4) * 8);
       }
     }
-    constexpr uint32_t kMask = kElem == 2 ? 0xffffu : 0xffu;
+  } else {
+    // Digits in base 128 of the scaled value (below 64 in magnitude), each in [-64, 64): the value is rounded once to
+    // 14 binary places and the integer split exactly.
 #pragma unroll
-    for (int j = 0; j < 3; ++j) w[j][i * kElem / 4] |= (d[j] & kMask) << ((i * kElem % 4) * 8);
+    for (int i = 0; i < V; ++i) {
+      const int q = __float2int_rn(v[i] * sc * 16384.0f);
+      const int d2 = ((q + 64) & 127) - 64;
+      const int q1 = (q - d2) >> 7;
+      const int d1 = ((q1 + 64) & 127) - 64;
+      const int d0 = (q1 - d1) >> 7;
+      w[0][i / 4] |= (static_cast<uint32_t>(d0) & 0xffu) << ((i % 4) * 8);
+      w[1][i / 4] |= (static_cast<uint32_t>(d1) & 0xffu) << ((i % 4) * 8);
+      w[2][i / 4] |= (static_cast<uint32_t>(d2) & 0xffu) << ((i % 4) * 8);
+    }
   }
 }
 
@@ -341,7 +360,7 @@ __device__ __forceinline__ int block_offset(int NC, int kb, int c) { return ((kb
 template <int ACT, bool XBF>
 __global__ void __launch_bounds__(128) tc_prep_kernel(const void* __restrict__ x, int ld_x, int rows, int K, int NC, int Mp, int planes,
                                                       uint8_t* __restrict__ out, float* __restrict__ inv_scales, int n_stages) {
-  constexpr int kElem = act_elem(ACT), V = 16 / kElem;
+  constexpr int kElem = act_elem(ACT), V = 16 / kElem, kKS = ks_of(ACT);
   pdl_trigger();
   pdl_wait();  // the kernel before this one may still be reading the workspace
   __shared__ float part[4];
@@ -466,7 +485,7 @@ __device__ __forceinline__ void finish_tile(const TcParams& P, const RowTerms& T
 
 // Stages of raw activations a CTA that prepares its own keeps in flight (32 bytes per thread and stage for bf16, 64 for f32).
 constexpr int own_depth(bool x_bf16) { return x_bf16 ? 4 : 2; }  // per group of preparing warps; there are two groups
-constexpr int own_staging_bytes(bool x_bf16) { return 2 * own_depth(x_bf16) * 128 * 16 * (x_bf16 ? 2 : 4); }
+constexpr int own_staging_bytes(bool x_bf16) { return 2 * own_depth(x_bf16) * 128 * (ks_of(kActS8) / 256) * 16 * (x_bf16 ? 2 : 4); }
 
 // ---- BF16 / FP8 / INT8: weights go from shared memory straight into the tensor core ------------------------------------
 constexpr int kDirectThreads = 192;   // warps 0-3 epilogue, warp 4 producers, warp 5 MMA issuer
@@ -479,7 +498,7 @@ constexpr int kDBufColumns = 256;     // two accumulators, 256 TMEM columns apar
 template <int F, int XMODE>
 __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_direct_kernel(const __grid_constant__ CUtensorMap wmap, const TcParams P) {
   using Fm = TcFmt<F>;
-  constexpr int kAct = Fm::kAct;
+  constexpr int kAct = Fm::kAct, kKS = ks_of(kAct);
   constexpr bool kOwn = XMODE != 0, kXBF = XMODE == 1;
   constexpr int kBoxes = Fm::kRowBytes / 128;    // 128-byte-wide tile copies per stage
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -638,6 +657,7 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_di
       static_assert(act_elem(kAct) == 1, "CTAs prepare their own activations for the 8-bit maths only");
       constexpr int V = 16;
       constexpr int kPiece = kXBF ? 8 : 4;  // activations per 16 bytes
+      constexpr int kQ = kKS / 256;  // 16-value units of a row per thread and stage (16 threads share a row's stage)
       constexpr int kUnitBytes = V * (kXBF ? 2 : 4);
       constexpr int D = own_depth(kXBF);
       const bool aligned16 = (reinterpret_cast<uintptr_t>(P.x) & 15) == 0 && P.ld_x % kPiece == 0;
@@ -706,36 +726,39 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_di
       const float sc = row_live ? row_scale_of(m) : 1.0f;
       const float inv = lane < P.M ? 1.0f / row_scale_of(lane) : 0.0f;  // lane l: row l (finish_tile's layout)
       const uint8_t* xrow = static_cast<const uint8_t*>(P.x) + static_cast<int64_t>(m) * P.ld_x * (kXBF ? 2 : 4);
-      uint8_t* const staging = xring + static_cast<size_t>(SX) * x_bytes + static_cast<size_t>(group) * D * 128 * kUnitBytes;
+      uint8_t* const staging = xring + static_cast<size_t>(SX) * x_bytes + static_cast<size_t>(group) * D * 128 * kQ * kUnitBytes;
       const int row_bytes = P.K * (kXBF ? 2 : 4);
       // stage s of a tile (or nothing, s < 0) into staging slot d; always one cp.async group
       auto issue = [&](int s, int d) {
         if (row_live && s >= 0) {
-          uint8_t* dst = staging + (static_cast<size_t>(d) * 128 + gtid) * kUnitBytes;
-          const int at = (s * kKS + kg * V) * (kXBF ? 2 : 4);  // byte offset of the unit in its row
-          if (aligned16) {
 #pragma unroll
-            for (int q = 0; q < kUnitBytes / 16; ++q) {
-              const int left = min(16, max(0, row_bytes - (at + 16 * q)));  // bytes of the row in this piece; the rest reads as zero
-              asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst + 16 * q)), "l"(xrow + (left ? at + 16 * q : 0)),
-                           "r"(left)
-                           : "memory");
-            }
-          } else {
+          for (int u = 0; u < kQ; ++u) {
+            uint8_t* dst = staging + ((static_cast<size_t>(d) * kQ + u) * 128 + gtid) * kUnitBytes;
+            const int k0 = s * kKS + (kg + 16 * u) * V;
+            const int at = k0 * (kXBF ? 2 : 4);  // byte offset of the unit in its row
+            if (aligned16) {
 #pragma unroll
-            for (int i = 0; i < V; ++i) {
-              const int k = s * kKS + kg * V + i;
-              if constexpr (kXBF) reinterpret_cast<uint16_t*>(dst)[i] = k < P.K ? reinterpret_cast<const uint16_t*>(xrow)[k] : uint16_t(0);
-              else reinterpret_cast<float*>(dst)[i] = k < P.K ? reinterpret_cast<const float*>(xrow)[k] : 0.0f;
+              for (int q = 0; q < kUnitBytes / 16; ++q) {
+                const int left = min(16, max(0, row_bytes - (at + 16 * q)));  // bytes of the row in this piece; the rest reads as zero
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst + 16 * q)), "l"(xrow + (left ? at + 16 * q : 0)),
+                             "r"(left)
+                             : "memory");
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < V; ++i) {
+                if constexpr (kXBF) reinterpret_cast<uint16_t*>(dst)[i] = k0 + i < P.K ? reinterpret_cast<const uint16_t*>(xrow)[k0 + i] : uint16_t(0);
+                else reinterpret_cast<float*>(dst)[i] = k0 + i < P.K ? reinterpret_cast<const float*>(xrow)[k0 + i] : 0.0f;
+              }
             }
           }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
       };
-      // the oldest group in flight has landed: its unit as f32
-      auto take = [&](int d, float (&v)[V]) {
-        asm volatile("cp.async.wait_group %0;" ::"n"(D - 1) : "memory");
-        const uint8_t* src = staging + (static_cast<size_t>(d) * 128 + gtid) * kUnitBytes;
+      // unit u of staging slot d as f32 (after wait_landed)
+      auto wait_landed = [&]() { asm volatile("cp.async.wait_group %0;" ::"n"(D - 1) : "memory"); };
+      auto take = [&](int d, int u, float (&v)[V]) {
+        const uint8_t* src = staging + ((static_cast<size_t>(d) * kQ + u) * 128 + gtid) * kUnitBytes;
         if constexpr (kXBF) {
 #pragma unroll
           for (int q = 0; q < 2; ++q) {
@@ -790,10 +813,14 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_di
             ok = finish(next_finish++);
           if (!ok) break;
         }
-        float v[V];
-        take(d, v);
-        uint32_t w[3][4];
-        make_planes<kAct, kXBF, V>(v, sc, w);
+        wait_landed();  // the oldest group in flight, this stage's
+        uint32_t w[kQ][3][4];
+#pragma unroll
+        for (int u = 0; u < kQ; ++u) {
+          float v[V];
+          take(d, u, v);
+          make_planes<kAct, kXBF, V>(v, sc, w[u]);
+        }
         issue(ahead_i < total ? ahead_s : -1, d);
         ahead_i += 2;
         step2(ahead_s, ahead_tile);
@@ -804,8 +831,11 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_di
         }
         uint8_t* block = xring + static_cast<size_t>(x.slot) * x_bytes;
         if (row_live) {
-          for (int j = 0; j < P.planes; ++j)
-            *reinterpret_cast<uint4*>(block + block_offset(NC, kg * 16, j * P.Mp + m)) = make_uint4(w[j][0], w[j][1], w[j][2], w[j][3]);
+#pragma unroll
+          for (int u = 0; u < kQ; ++u)
+            for (int j = 0; j < P.planes; ++j)
+              *reinterpret_cast<uint4*>(block + block_offset(NC, (kg + 16 * u) * 16, j * P.Mp + m)) =
+                  make_uint4(w[u][j][0], w[u][j][1], w[u][j][2], w[u][j][3]);
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads what these threads wrote
         __syncwarp();
@@ -824,9 +854,10 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_di
 }
 
 // ---- NVFP4: converter warps expand the stage into tensor memory ---------------------------------------------------------
-constexpr int kChunks = kKS / 16;  // tcgen05.mma instructions per stage (K = 16 each)
-constexpr int kASlots = 3;         // A-operand slots in TMEM, one stage each (kKS / 2 columns)
-constexpr int kAColumns = kKS / 2;
+constexpr int kKS4 = ks_of(kActF16);  // values of K per stage
+constexpr int kChunks = kKS4 / 16;   // tcgen05.mma instructions per stage (K = 16 each)
+constexpr int kASlots = 3;           // A-operand slots in TMEM, one stage each (kKS4 / 2 columns)
+constexpr int kAColumns = kKS4 / 2;
 constexpr int kDColumn = kASlots * kAColumns;  // the accumulator's first TMEM column (128 columns remain for it)
 constexpr int kConvWarps = 8, kConvThreads = 320;  // warps 0-7 convert, warp 8 produces, warp 9 issues
 
@@ -851,7 +882,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * SW + 2 * SX + 2 * kASlots + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n_stages = (P.K + kKS - 1) / kKS;
+  const int n_stages = (P.K + kKS4 - 1) / kKS4;
   const int n_tiles = (P.N + P.R - 1) / P.R;
   const int tile_begin = static_cast<int>(static_cast<int64_t>(n_tiles) * blockIdx.x / gridDim.x);
   const int tile_end = static_cast<int>(static_cast<int64_t>(n_tiles) * (blockIdx.x + 1) / gridDim.x);
@@ -1104,7 +1135,7 @@ TcParams base_params(const lx_weight& w, const void* bias, int bias_dtype, int y
   P.digit = act == kActS8 ? 0.0078125f : act == kActE4m3 ? 0.0625f : 1.0f;
   P.Mp = (rows + 7) / 8 * 8;
   P.NC = (P.planes * P.Mp + 15) / 16 * 16;
-  P.x_bytes = P.NC * kKS * act_elem(act);
+  P.x_bytes = P.NC * ks_of(act) * act_elem(act);
   P.bias = bias, P.bias_dtype = bias_dtype;
   P.y_dtype = y_dtype, P.ld_y = ld_y;
   P.alpha = alpha, P.beta = beta;
@@ -1150,14 +1181,14 @@ int tc_product_rows(const void* x, int x_dtype, int ld_x, const lx_weight& w, co
 int tc_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const void* bias, int bias_dtype, void* y, int y_dtype,
                int ld_y, int M, int N, int K, float alpha, float beta, void* workspace, cudaStream_t stream) {
   const bool x_bf16 = x_dtype == LX_BF16;
-  const int act = act_of(w.type), elem = act_elem(act);
+  const int act = act_of(w.type), elem = act_elem(act), kKS = ks_of(act);
   const int per_pass = rows_per_pass(act, x_bf16);
   const int n_stages = (K + kKS - 1) / kKS;
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   for (int m0 = 0; m0 < M; m0 += per_pass) {
     const int rows = std::min(per_pass, M - m0);
     TcParams P = base_params(w, bias, bias_dtype, y_dtype, ld_y, N, K, alpha, beta, act, x_bf16, rows);
-    const TcLayout L(P.NC, elem, n_stages);
+    const TcLayout L(P.NC, act, n_stages);
     P.xprep = ws;
     P.inv_scales = reinterpret_cast<const float*>(ws + L.scales);
     P.y = static_cast<uint8_t*>(y) + static_cast<int64_t>(m0) * ld_y * (y_dtype == LX_BF16 ? 2 : 4);
@@ -1196,13 +1227,12 @@ int tc_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const v
 // Bytes of workspace the product needs for M activation rows, whatever the weight format and activation dtype.
 int64_t tc_workspace_bytes(int M, int K) {
   const int rows = std::min(M, kMaxRows);
-  const int64_t n_stages = (K + kKS - 1) / kKS;
   int64_t need = 0;
   for (int act = 0; act < 4; ++act)
     for (int bf = 0; bf < 2; ++bf) {
       const int r = std::min(rows, rows_per_pass(act, bf != 0));
       const int NC = (act_planes(act, bf != 0) * ((r + 7) / 8 * 8) + 15) / 16 * 16;
-      need = std::max(need, TcLayout(NC, act_elem(act), n_stages).total);
+      need = std::max(need, TcLayout(NC, act, (K + ks_of(act) - 1) / ks_of(act)).total);
     }
   return need;
 }
