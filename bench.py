@@ -45,6 +45,11 @@ DTYPE = {abi.W_BF16: "bf16", abi.W_INT8: "int8xbf16->s32/f32", abi.W_FP8: "e4m3x
 ROTATE_BYTES = 1 << 30  # weights touched between two uses of the same copy (L2 is 126 MB)
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the workload's dominant kernel, from an ncu capture
+# (profiles/tc_direct_kernel_c2_int8_m1.md); workloads without a capture report null.
+NCU_TRAFFIC = {"c2_int8": 58.854e6 + 0.752e6}
+
+
 def measured_peak_gbs():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -319,7 +324,9 @@ def main():
     peak, peak_kind = measured_peak_gbs()
     achieved = k_bytes / (k_ms * 1e-3) / 1e9
     dominant = "tc_direct_kernel" if wtype in (abi.W_INT8, abi.W_FP8) else "stream_kernel"
-    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+    # DRAM bytes per launch of the dominant kernel from the ncu capture summarised under profiles/ (read + write)
+    traffic = NCU_TRAFFIC.get(args.workload) if world == 1 else None
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
                 "peak_source": f"{peak_kind} copy bandwidth (burst)", "kernel": dominant, "per_m": per_m,
                 "algorithmic_bytes_per_launch": shard_bytes}
 

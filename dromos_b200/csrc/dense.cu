@@ -10,7 +10,6 @@
 #include "variants.h"
 
 namespace b200 {
-unsigned long long* g_debug_trace = nullptr;
 namespace {
 
 // ---- scalar path: one warp per weight row, any K, any alignment ------------------------------------------------
@@ -135,8 +134,6 @@ int dense_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, cons
   P.y = y, P.y_dtype = y_dtype, P.ld_y = ld_y;
   P.alpha = alpha, P.beta = beta;
   P.status = status_word();
-  P.debug_skip = std::getenv("LX_B200_DEBUG_SKIP") ? std::atoi(std::getenv("LX_B200_DEBUG_SKIP")) : 0;
-  P.trace = g_debug_trace;
   const bool fast = stream_ok(w, K) && !force_scalar();
   switch (w.type) {
     case LX_W_BF16: return fast ? launch_dense_format<LX_W_BF16>(P, stream) : launch_scalar<LX_W_BF16>(P, stream);
@@ -274,4 +271,3 @@ extern "C" int lx_gemm_skinny(const void* x, lx_dtype x_dtype, int ld_x, const l
                        static_cast<cudaStream_t>(stream));
 }
 
-extern "C" LX_API void lx_b200_debug_trace(void* buf) { b200::g_debug_trace = static_cast<unsigned long long*>(buf); }

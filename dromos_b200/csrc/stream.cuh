@@ -64,14 +64,12 @@ struct StreamParams {
   void* moe_out;  // gate_up: bf16 [P, I] in grouped order; down: f32 [P, L] by pair index
   int* status;
   int tiled;  // the weight rows come as 2-D tile copies through the tensor maps (else row by row)
-  int debug_skip;  // experiments only: 1 = consumers release stages without reading them
   // Dense products may cut the work between CTAs at stage granularity instead of tile granularity (split_k): a tile
   // whose stages end up in several CTAs is finished by the last of them, which adds the others' partial sums (left in
   // `partials`, announced through `flags`) in CTA order.
   int split_k;
   float* partials;  // [grid][R * COLS]
   int* flags;       // [grid], zero between launches
-  unsigned long long* trace;  // experiments only: per-stage timestamps of CTA 0 (issue, full, done), or null
 };
 
 template <int F>
@@ -388,7 +386,6 @@ __global__ void __launch_bounds__(32 * NW + 32, 1)
           const int slot = gs % S;
           if (gs >= S) mbar_wait(empty_bar(slot), ((gs / S) - 1) & 1, P.status, kStatusEmptyWait);
           const uint32_t stage = smem_u32(ring) + static_cast<uint32_t>(slot) * C::STAGE_BYTES;
-          if (P.trace && blockIdx.x == 0 && lane == 0 && gs < 4096) P.trace[3 * gs] = global_timer_ns();
           if (P.tiled) {
             // One tile copy per stage: R rows x SEG bytes (rows and bytes past the matrix read as zero). gate_up
             // takes two half-height tiles, the gate rows and the up rows.
@@ -468,7 +465,6 @@ __global__ void __launch_bounds__(32 * NW + 32, 1)
 
   // Everything below reads activations, which the previous kernel in the stream may have written.
   pdl_wait();
-  if (P.trace && tid == 0) P.trace[3 * 4096 + 2 * blockIdx.x] = global_timer_ns();
 
   // Two accumulators per output fragment, fed alternately, so that consecutive products do not wait for each other;
   // they are added (in a fixed order) when the tile is done.
@@ -711,7 +707,6 @@ __global__ void __launch_bounds__(32 * NW + 32, 1)
         }
 
         mbar_wait(full_bar(slot), (gs / S) & 1, P.status, kStatusFullWait);
-        if (P.trace && blockIdx.x == 0 && tid == 0 && gs < 4096) P.trace[3 * gs + 1] = global_timer_ns();
         const uint8_t* stage = ring + static_cast<size_t>(slot) * C::STAGE_BYTES;
         const int k_stage0 = s * C::KSTAGE;
 
@@ -719,7 +714,7 @@ __global__ void __launch_bounds__(32 * NW + 32, 1)
         for (int u = 0; u < U; ++u) {
           const int st = wk * U + u;  // step inside the stage
           const int k_step0 = k_stage0 + st * C::kStepValues;
-          if (k_step0 >= K || P.debug_skip == 1) break;
+          if (k_step0 >= K) break;
           // weight operands
           uint32_t plo[RT][C::NREG], phi[RT][C::NREG];
 #pragma unroll
@@ -775,7 +770,6 @@ __global__ void __launch_bounds__(32 * NW + 32, 1)
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_bar(slot));
-        if (P.trace && blockIdx.x == 0 && tid == 0 && gs < 4096) P.trace[3 * gs + 2] = global_timer_ns();
       }
 
       // ---- the K-split partial sums meet in shared memory, added in warp order ---------------------------
@@ -880,7 +874,6 @@ __global__ void __launch_bounds__(32 * NW + 32, 1)
       }
     }
   }
-  if (P.trace && tid == 0) P.trace[3 * 4096 + 2 * blockIdx.x + 1] = global_timer_ns();
 }
 
 }  // namespace b200
