@@ -160,6 +160,11 @@ int tc_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const v
                int ld_y, int M, int N, int K, float alpha, float beta, void* workspace, cudaStream_t stream);
 int64_t tc_workspace_bytes(int M, int K);
 bool tc_enabled();
+bool experts_tc_ok(const lx_weight& gate_up, const lx_weight& down, int L, int I);
+int64_t experts_tc_workspace(int64_t base, int P, int E, int L, int I);
+int experts_tc(const void* latent, const float* weights, const lx_weight& gate_up, const lx_weight& down, const int32_t* offsets,
+               const int32_t* pairs, uint16_t* mid, float* rows, uint8_t* ws, int64_t base, int T, int L, int I, int E, int top_k,
+               int* status, cudaStream_t stream);
 bool tc_rows_ok(const lx_weight& w, int N, int K);
 int tc_product_rows(const void* x, int x_dtype, int ld_x, const lx_weight& w, const void* bias, int bias_dtype, void* y, int y_dtype,
                     int ld_y, int M, int N, int K, float alpha, float beta, cudaStream_t stream);

@@ -316,6 +316,17 @@ int run_experts(const void* latent, const int32_t* ids, const float* weights, co
   g.top_k = top_k, g.I = I;
   g.moe_out = ws + l.mid;
   g.status = status ? status : status_word();
+  // Both stacks in a format the tensor core reads as stored: the tcgen05 kernels (their tables and activation blocks
+  // sit behind this layout in the workspace), then the same ordered sum.
+  if (!indirect && experts_tc_ok(gate_up, down, L, I)) {
+    if (int e = experts_tc(latent, weights, gate_up, down, reinterpret_cast<const int32_t*>(ws + l.offsets),
+                           reinterpret_cast<const int32_t*>(ws + l.pairs), reinterpret_cast<uint16_t*>(ws + l.mid),
+                           reinterpret_cast<float*>(ws + l.rows), ws, l.total, T, L, I, experts, top_k, g.status, s))
+      return e;
+    const int64_t n = static_cast<int64_t>(T) * L;
+    return launch_kernel(ordered_sum_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, s,
+                         reinterpret_cast<const float*>(ws + l.rows), out, T, L, top_k);
+  }
   // weights the streaming kernel cannot take run both stages on the scalar kernels (intermediate rows by pair index)
   const bool fast_gu = stack_streams(gate_up, L) && stack_streams(down, I), fast_dn = fast_gu;
   if (int e = fast_gu ? launch_expert_stage<kGateUp>(g, gate_up.type, s, static_cast<int64_t>(experts) * 2 * I)
@@ -357,7 +368,8 @@ extern "C" int lx_moe_route(const float* logits, const float* selection_bias, in
 extern "C" int64_t lx_moe_grouped_workspace_bytes(int T, int L, int I, int E, int top_k, lx_math math) {
   (void)math;
   if (T <= 0 || L <= 0 || I <= 0 || E <= 0 || top_k <= 0) return 0;
-  return layout(T * top_k, E, L, I).total;
+  // the grouping tables and buffers, then what the tensor-core path adds (chunk tables, activation blocks)
+  return experts_tc_workspace(layout(T * top_k, E, L, I).total, T * top_k, E, L, I);
 }
 
 extern "C" int lx_moe_experts_grouped(const void* latent, const int32_t* ids, const float* weights,
@@ -436,7 +448,7 @@ extern "C" int lx_b200_moe_experts_grouped_static(const void* latent, const int3
   if (gate_up->type == LX_W_NVFP4 && (L % 16 != 0 || I % 16 != 0)) return kInvalid;
   const int P = T * top_k;
   const Layout l = layout(P, E, L, I);
-  if (l.total > kStaticScratchBytes - kStaticHeaderBytes) return LX_B200_ERR_SCRATCH;  // larger than the fixed array
+  if (experts_tc_workspace(l.total, P, E, L, I) > kStaticScratchBytes - kStaticHeaderBytes) return LX_B200_ERR_SCRATCH;  // larger than the fixed array
   uint8_t* base = nullptr;
   if (int e = static_scratch(&base)) return e;
   auto s = static_cast<cudaStream_t>(stream);
