@@ -40,6 +40,10 @@ WORKLOADS = {
     "c3_nvfp4": (abi.W_NVFP4, 28672, 8192, (1, 16, 64), "NVFP4 gemm_w M in {1,16,64} K=8192 N=28672"),
     "c4_bf16x": (abi.W_BF16X, 14336, 4096, (1,), "BF16X lossless GEMV M=1 K=4096 N=14336"),
 }
+MOE_WORKLOADS = {
+    # name: (weight format, E, top_k, L, I, T, description)
+    "c5_moe_fp8": (abi.W_FP8, 64, 8, 4096, 1536, 32, "MoE routed experts E=64 top-8 L=4096 I=1536 FP8 (per-row scale), T=32"),
+}
 DTYPE = {abi.W_BF16: "bf16", abi.W_INT8: "int8xbf16->s32/f32", abi.W_FP8: "e4m3xbf16->f32", abi.W_NVFP4: "e2m1xbf16->f32",
          abi.W_BF16X: "bf16"}
 ROTATE_BYTES = 1 << 30  # weights touched between two uses of the same copy (L2 is 126 MB)
@@ -187,9 +191,11 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2_int8", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2_int8", choices=sorted(WORKLOADS) + sorted(MOE_WORKLOADS))
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.workload in MOE_WORKLOADS:
+        return main_moe(args)
     wtype, N, K, Ms, desc = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -376,6 +382,150 @@ def main():
             out["cpu_baseline"] = {"value": None, "unit": "TB/s", "cores": os.cpu_count(), "kind": "reference",
                                    "sample": "oracle/_ref/libdromos_cpu.so not built"}
     print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main_moe(args):
+    """The routed-experts workload (C5): a step is lx_moe_route + lx_moe_experts_grouped on T tokens with fresh logits
+    and the next copy of the expert stacks (>= 1 GiB of other weights between two uses of a copy). Bytes of a step =
+    the weights and scales of the experts the step's routing touches (the reference's accounting, model/traffic.cpp:23-58).
+    With N > 1 ranks the experts are split over the ranks (expert parallel: two all-to-all exchanges per step)."""
+    wtype, E, top_k, L, I, T, desc = MOE_WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    metric = "decode matmul effective HBM TB/s"
+    config = {"workload": desc, "rotation": "expert stack copies >= 1 GiB between reuses (inputs larger than L2)",
+              "parallelism": f"experts split over {world} GPU(s), all-to-all of routed rows" if world > 1 else "single GPU"}
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the CPU reference arm of bench.py times the dense workloads only"}))
+        return
+    import torch
+    import torch.distributed as dist
+
+    from dromos_b200 import host
+
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib = abi.Library()
+    dev = torch.device("cuda", local)
+    e0, e1 = host.expert_range(E, rank, world)
+    gen = torch.Generator(device=dev).manual_seed(0)
+    per_expert = (2 * I * L + L * I) + 4 * (2 * I + L)  # bytes of one expert: both stacks and their row scales
+    local_bytes = per_expert * (e1 - e0)
+    copies = max(2, -(-ROTATE_BYTES // local_bytes) + 1)
+    stacks = []
+    for c in range(copies):
+        if c == 0:
+            gu = host.store_weight(lib, (torch.randn((e1 - e0, 2 * I, L), generator=gen, device=dev) * 0.02).to(torch.bfloat16), wtype)
+            dn = host.store_weight(lib, (torch.randn((e1 - e0, L, I), generator=gen, device=dev) * 0.02).to(torch.bfloat16), wtype)
+        else:
+            gu = host.StoredWeight(wtype, stacks[0][0].data.clone(), stacks[0][0].scale.clone(), stacks[0][0].glob, rows=stacks[0][0].rows, cols=L)
+            dn = host.StoredWeight(wtype, stacks[0][1].data.clone(), stacks[0][1].scale.clone(), stacks[0][1].glob, rows=stacks[0][1].rows, cols=I)
+        stacks.append((gu, dn))
+    t0, t1 = T * rank // world, T * (rank + 1) // world  # this rank's tokens
+    periods = 8  # distinct routings
+    logits = [torch.randn((T, E), generator=torch.Generator(device=dev).manual_seed(100 + i), device=dev)[t0:t1].contiguous()
+              for i in range(periods)]
+    latent = torch.randn((T, L), generator=gen, device=dev).to(torch.bfloat16)[t0:t1].contiguous()
+    if world == 1:
+        engines = [host.Experts(lib, gu, dn, E, L, I, top_k) for gu, dn in stacks]
+    else:
+        engines = [host.ExpertParallel(lib, gu, dn, E, L, I, top_k) for gu, dn in stacks]
+    router = host.Experts(lib, stacks[0][0], stacks[0][1], E, L, I, top_k)
+    out = torch.empty((t1 - t0, L), dtype=torch.float32, device=dev)
+    touched = []
+    for i in range(periods):  # the experts each routing touches, whole job (the same seeds on every rank give the same T x E logits)
+        full = torch.randn((T, E), generator=torch.Generator(device=dev).manual_seed(100 + i), device=dev)
+        touched.append(int(torch.unique(torch.topk(full, top_k, dim=1).indices).numel()))
+
+    def step(i):
+        ids, w = router.route(logits[i % periods])
+        if world == 1:
+            engines[i % copies](latent, ids, w, out)
+        else:
+            out.copy_(engines[i % copies](latent, ids, w))
+
+    use_graphs = world == 1 and os.environ.get("LX_BENCH_GRAPHS", "1") != "0"
+    period = periods * copies
+    for i in range(min(period, 4)):
+        step(i)
+    torch.cuda.synchronize()
+    before = lib.lx_b200_kernel_launches()
+    step(0)
+    launches_per_step = lib.lx_b200_kernel_launches() - before
+    if use_graphs:
+        graphs = []
+        for i in range(period):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                step(i)
+            graphs.append(g)
+        run = lambda i: graphs[i % period].replay()
+    else:
+        run = step
+
+    def timed(fn, n):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(n):
+            fn(i)
+        b.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([a.elapsed_time(b)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for i in range(args.warmup):
+        run(i)
+    with ClockSampler(local) as clocks:
+        ms = timed(lambda i: run(args.warmup + i), args.steps)
+    step_bytes = [per_expert * touched[(args.warmup + i) % periods] for i in range(args.steps)]
+    value = sum(step_bytes) / (ms * 1e-3) / 1e12
+    peak, peak_kind = measured_peak_gbs()
+    achieved = sum(step_bytes) / (ms * 1e-3) / 1e9 / world
+    # end to end: logits and latent from pinned host memory in, the tokens' outputs out, every step
+    lh = [x.cpu().pin_memory() for x in logits]
+    xh = latent.cpu().pin_memory()
+    oh = torch.empty(out.shape, dtype=torch.float32).pin_memory()
+    ld, xd = torch.empty_like(logits[0]), torch.empty_like(latent)
+
+    def e2e_step(i):
+        ld.copy_(lh[i % periods], non_blocking=True)
+        xd.copy_(xh, non_blocking=True)
+        ids, w = router.route(ld)
+        if world == 1:
+            engines[i % copies](xd, ids, w, out)
+        else:
+            out.copy_(engines[i % copies](xd, ids, w))
+        oh.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(3):
+        e2e_step(i)
+    e2e_ms = timed(e2e_step, args.steps)
+    status = lib.lx_b200_last_error()
+    if rank == 0:
+        print(json.dumps({
+            "metric": metric, "value": value, "unit": "TB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+            "dtype": DTYPE[wtype], "data": "synthetic", "config": config,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "peak_source": f"{peak_kind} copy bandwidth (burst)", "kernel": "tc_expert_kernel (whole call: 7 kernels)",
+                         "algorithmic_bytes_per_launch": sum(step_bytes) / len(step_bytes)},
+            "e2e": {"value": sum(step_bytes) / (e2e_ms * 1e-3) / 1e12, "unit": "TB/s",
+                    "h2d_bytes_per_step": T * E * 4 + T * L * 2, "d2h_bytes_per_step": T * L * 4},
+            "gpu_launches": int(launches_per_step * args.steps), "launch": "CUDA graphs" if use_graphs else "eager",
+            "clocks": clocks.summary(), "pct_of_8TBs": value / 8.0 / max(world, 1), "kernel_status": status,
+            "cpu_baseline": {"value": None, "unit": "TB/s", "cores": os.cpu_count(), "kind": "reference",
+                             "sample": "not timed for this workload (the dense workloads time the reference CPU backend)"}}))
     if world > 1:
         dist.destroy_process_group()
 

@@ -89,6 +89,21 @@ def test_grouped_experts_match_oracle(lx, wtype, T, L, I, E, top_k):
     util.assert_close(got, want, what=NAMES[wtype])
 
 
+@pytest.mark.parametrize("wtype", [O.W_BF16, O.W_INT8, O.W_FP8], ids=lambda w: NAMES[w])
+def test_grouped_experts_many_tiles_and_chunks(lx, wtype):
+    """Shapes that give the tensor-core path several row tiles per expert with a ragged last one (I = 400, L = 1024:
+    tiles of fewer than 128 rows), K ending inside a stage (400 = 256 + 144), and an expert with more than 16 rows
+    (two chunks)."""
+    def crowd(ids):
+        ids = ids.copy()
+        ids[:20, 0] = 2  # 20 rows for expert 2: two chunks
+        return ids
+
+    got, want, _ = experts_case(lx, wtype, 24, 1024, 400, 12, 3, seed=17, ids_override=crowd)
+    assert np.abs(got - want).max() <= 2e-3 * np.abs(want).max()
+    util.assert_close(got, want, what=NAMES[wtype])
+
+
 def test_grouping_tables_are_exact(lx):
     T, L, I, E, top_k = 32, 256, 64, 64, 8
     _, _, (ws, ids, E) = experts_case(lx, O.W_FP8, T, L, I, E, top_k, seed=5)
