@@ -88,16 +88,25 @@ __global__ void __launch_bounds__(256) route_kernel(const float* __restrict__ lo
 
 // ---- grouping --------------------------------------------------------------------------------------------------
 // offsets[e] = pairs of experts below e; pairs[offsets[e] + j] = the j-th pair (ascending) that chose expert e.
-// One CTA of 1024 threads, thread e walks the ids; E <= 1024.
+// One CTA of 1024 threads, thread e walks the ids (staged in shared memory when there are at most 8192 of them: the
+// walk is then ~P shared-memory reads, not P dependent global loads); E <= 1024.
+constexpr int kGroupStaged = 8192;
 __global__ void __launch_bounds__(1024) group_kernel(const int32_t* __restrict__ ids, int P, int E,
                                                      int32_t* __restrict__ offsets, int32_t* __restrict__ pairs) {
   pdl_trigger();
   pdl_wait();
   __shared__ int32_t start[kMaxExperts + 1];
+  __shared__ int32_t staged[kGroupStaged];
   const int e = threadIdx.x;
+  const bool in_smem = P <= kGroupStaged;
+  if (in_smem) {
+    for (int p = e; p < P; p += 1024) staged[p] = ids[p];
+    __syncthreads();
+  }
+  const int32_t* src = in_smem ? staged : ids;
   int count = 0;
   if (e < E)
-    for (int p = 0; p < P; ++p) count += ids[p] == e;
+    for (int p = 0; p < P; ++p) count += src[p] == e;
   start[e] = e < E ? count : 0;
   __syncthreads();
   if (e == 0) {
@@ -114,7 +123,7 @@ __global__ void __launch_bounds__(1024) group_kernel(const int32_t* __restrict__
   if (e < E) {
     int at = start[e];
     for (int p = 0; p < P && count > 0; ++p)
-      if (ids[p] == e) pairs[at++] = p, --count;
+      if (src[p] == e) pairs[at++] = p, --count;
   }
 }
 
