@@ -80,9 +80,21 @@ int launch_dense_format(const StreamParams& P, cudaStream_t stream) {
   if (cols <= 8) {
     // Bytes of activation units for the whole of K; up to 32 KB stays resident in the small buffer.
     const int64_t unit_bytes = static_cast<int64_t>(P.K) / (k8 ? 16 : 8) * 16 * cols;
-    if (unit_bytes > 32 * 1024) return launch_stream<F, 8, 1, 2, 1, 2, 4, 64, kDense>(P, stream, P.N);
+    const bool big_x = unit_bytes > 32 * 1024;
+    const int tuned = lx_tune_get(gemv_kernel_name(F), P.M, P.N, P.K);
+    if (tuned < 0) {
+      // Defaults. A format keeps ONE warp layout (consumer warps, warp rows, steps per stage: what fixes the order a
+      // row's products are added in) for every M = 1..8, with the large activation buffer when the rows need it, so a
+      // row's bits do not depend on its batch; BF16 and BF16X share theirs, so the lossless format reproduces bf16's
+      // bits. Picked from sweeps of the variants at M = 1 on the decode shapes.
+      if constexpr (F == LX_W_BF16 || F == LX_W_BF16X)
+        return big_x ? launch_stream<F, 16, 1, 2, 1, 2, 2, 64, kDense>(P, stream, P.N) : launch_stream<F, 16, 1, 2, 1, 2, 5, 16, kDense>(P, stream, P.N);
+      if constexpr (F == LX_W_NVFP4)
+        return big_x ? launch_stream<F, 16, 1, 4, 1, 2, 2, 64, kDense>(P, stream, P.N) : launch_stream<F, 16, 1, 4, 1, 2, 4, 16, kDense>(P, stream, P.N);
+    }
+    if (big_x) return launch_stream<F, 8, 1, 2, 1, 2, 4, 64, kDense>(P, stream, P.N);
     // decode GEMV: the variant the table holds for this shape (keyed on M's power-of-two bucket), else variant 0
-    switch (lx_tune_get(gemv_kernel_name(F), P.M, P.N, P.K)) {
+    switch (tuned) {
       case 1: return launch_stream<F, 8, 1, 2, 1, 2, 8, 16, kDense>(P, stream, P.N);
       case 2: return launch_stream<F, 8, 1, 2, 1, 2 * UW, 4, 16, kDense>(P, stream, P.N);
       case 3: return launch_stream<F, 16, 1, 4, 1, 2, 4, 16, kDense>(P, stream, P.N);

@@ -127,9 +127,10 @@ def test_gemm_w_small_m(lx, fmt, M):
 @pytest.mark.parametrize("fmt", FORMATS, ids=lambda f: NAMES[f])
 @pytest.mark.parametrize("case", [(16, 264, 4096, False), (24, 1000, 2304, False), (20, 1000, 2304, True), (64, 520, 8192, False)],
                          ids=lambda c: f"M{c[0]}N{c[1]}K{c[2]}{'f32' if c[3] else ''}")
-def test_gemm_w_tiles_shared_between_ctas(lx, fmt, case):
-    """Shapes whose 128-row tiles are summed from the partial results of several CTAs (stage ranges that start and end
-    inside tiles), with bias, alpha and beta, twice in a row on the same workspace: the two results are bitwise equal."""
+def test_gemm_w_odd_tiles_and_long_k(lx, fmt, case):
+    """Shapes with few, ragged tiles (N not a multiple of the tile rows, fewer tiles than SMs), K ending inside a stage,
+    f32 activations and 64 rows, with bias, alpha and beta, twice in a row on the same workspace: the two results are
+    bitwise equal."""
     if fmt == O.W_BF16X:
         pytest.skip("lx_gemm_w takes BF16X through lx_bf16x_decode in the engine")
     M, N, K, x_f32 = case
@@ -176,8 +177,9 @@ def test_wide_weight_rows_do_not_depend_on_batch(lx, fmt):
 
 
 @pytest.mark.parametrize("fmt", FORMATS, ids=lambda f: NAMES[f])
-def test_rows_do_not_depend_on_batch_and_runs_repeat(lx, fmt):
-    N, K = 256, 2048
+@pytest.mark.parametrize("K", [2048, 4096], ids=["K2048", "K4096"])  # 8 rows of K = 4096 need the large activation buffer
+def test_rows_do_not_depend_on_batch_and_runs_repeat(lx, fmt, K):
+    N = 256
     w_bits = util.bf16_normal((N, K), 0.02, 11)
     wt = util.make_weight(w_bits, fmt)
     dw = util.DeviceWeight(wt)
