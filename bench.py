@@ -62,6 +62,18 @@ def measured_peak_gbs():
         return 6650.0, "fallback"
 
 
+def hold_load(fn, seconds=0.6):
+    """The K timed steps last a few milliseconds, less than one nvidia-smi sample: the same work is repeated (untimed)
+    for a moment while the clock sampler still runs, so that the clocks it reports are clocks under this load."""
+    import torch
+
+    end = time.time() + seconds
+    while time.time() < end:
+        for _ in range(20):
+            fn()
+        torch.cuda.synchronize()
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
 
@@ -108,7 +120,8 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm),
+                "window": "the timed steps and 0.6 s of the same steps repeated right after them"}
 
 
 # ---------------------------------------------------------------------------------------------------------------------
@@ -307,8 +320,24 @@ def main():
     run_step, launches_per_period = replayer(step, period)
     for i in range(args.warmup):
         run_step(i)
+    # The K timed steps are ONE graph (the reference's method, bench/bench_gemv.py:74-119: every launch of the timed
+    # region in one graph), so that no host round trip sits between two steps; eager when graphs are off or the capture
+    # fails (then every step is a host launch).
+    whole = None
+    if use_graphs:
+        try:
+            whole = capture(lambda: [step(args.warmup + i) for i in range(args.steps)])
+            whole.replay()  # once untimed: the graph's own first-launch cost
+        except Exception as e:
+            print(f"[bench] capture of the timed region failed ({type(e).__name__}: {e}); replaying per step", file=sys.stderr)
+            torch.cuda.synchronize()
+            whole = None
     with ClockSampler(local) as clocks:
-        ms = timed(lambda i: run_step(args.warmup + i), args.steps)
+        if whole is not None:
+            ms = timed(lambda i: whole.replay(), 1)
+        else:
+            ms = timed(lambda i: run_step(args.warmup + i), args.steps)
+        hold_load(whole.replay if whole is not None else (lambda: run_step(0)))
     launches = launches_per_period * args.steps // period
     value = total_step_bytes * args.steps / (ms * 1e-3) / 1e12
 
@@ -485,8 +514,16 @@ def main_moe(args):
 
     for i in range(args.warmup):
         run(i)
+    whole = None
+    if use_graphs:  # the timed steps as one graph, no host round trip between steps
+        whole = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(whole):
+            for i in range(args.steps):
+                step(args.warmup + i)
+        whole.replay()
     with ClockSampler(local) as clocks:
-        ms = timed(lambda i: run(args.warmup + i), args.steps)
+        ms = timed((lambda i: whole.replay()), 1) if whole is not None else timed(lambda i: run(args.warmup + i), args.steps)
+        hold_load(whole.replay if whole is not None else (lambda: run(0)))
     step_bytes = [per_expert * touched[(args.warmup + i) % periods] for i in range(args.steps)]
     value = sum(step_bytes) / (ms * 1e-3) / 1e12
     peak, peak_kind = measured_peak_gbs()
@@ -518,7 +555,7 @@ def main_moe(args):
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
             "dtype": DTYPE[wtype], "data": "synthetic", "config": config,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
-                         "peak_source": f"{peak_kind} copy bandwidth (burst)", "kernel": "tc_expert_kernel (whole call: 7 kernels)",
+                         "peak_source": f"{peak_kind} copy bandwidth (burst)", "kernel": "tc_expert_kernel (whole step: route + 6 kernels)",
                          "algorithmic_bytes_per_launch": sum(step_bytes) / len(step_bytes)},
             "e2e": {"value": sum(step_bytes) / (e2e_ms * 1e-3) / 1e12, "unit": "TB/s",
                     "h2d_bytes_per_step": T * E * 4 + T * L * 2, "d2h_bytes_per_step": T * L * 4},

@@ -160,6 +160,18 @@ int tc_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const v
                int ld_y, int M, int N, int K, float alpha, float beta, void* workspace, cudaStream_t stream);
 int64_t tc_workspace_bytes(int M, int K);
 bool tc_enabled();
+// Rows of one expert that a tile of the tensor-core expert kernels multiplies at once, and the tables that cut the sorted
+// pairs into such chunks (written by group_kernel, read by the kernels of moe_tc.cu; they live in the workspace).
+constexpr int kExpertChunkRows = 16;
+struct ExpertChunkTables {
+  int32_t* n_chunks;      // one word: how many chunks
+  int32_t* chunk_expert;  // per chunk: its expert,
+  int32_t* chunk_row0;    //   the sorted position of its first row,
+  int32_t* chunk_rows;    //   its rows (1..16)
+  int32_t* pos_chunk;     // per sorted position: its chunk
+  int32_t* pos_col;       //   and its row inside the chunk
+};
+ExpertChunkTables expert_chunk_tables(uint8_t* ws, int64_t base, int P, int E, int L, int I);
 bool experts_tc_ok(const lx_weight& gate_up, const lx_weight& down, int L, int I);
 int64_t experts_tc_workspace(int64_t base, int P, int E, int L, int I);
 int experts_tc(const void* latent, const float* weights, const lx_weight& gate_up, const lx_weight& down, const int32_t* offsets,

@@ -92,7 +92,8 @@ __global__ void __launch_bounds__(256) route_kernel(const float* __restrict__ lo
 // walk is then ~P shared-memory reads, not P dependent global loads); E <= 1024.
 constexpr int kGroupStaged = 8192;
 __global__ void __launch_bounds__(1024) group_kernel(const int32_t* __restrict__ ids, int P, int E,
-                                                     int32_t* __restrict__ offsets, int32_t* __restrict__ pairs) {
+                                                     int32_t* __restrict__ offsets, int32_t* __restrict__ pairs,
+                                                     const ExpertChunkTables chunks) {
   pdl_trigger();
   pdl_wait();
   __shared__ int32_t start[kMaxExperts + 1];
@@ -120,10 +121,26 @@ __global__ void __launch_bounds__(1024) group_kernel(const int32_t* __restrict__
   }
   __syncthreads();
   if (e <= E) offsets[e] = start[e];
+  const int row0 = e < E ? start[e] : 0, rows = count;
   if (e < E) {
-    int at = start[e];
+    int at = row0;
     for (int p = 0; p < P && count > 0; ++p)
       if (src[p] == e) pairs[at++] = p, --count;
+  }
+  // The chunk tables of the tensor-core expert kernels: expert e's rows cut into chunks of up to 16.
+  if (chunks.n_chunks) {
+    __syncthreads();  // everyone has read start[]; it now holds each expert's chunk count
+    const int mine = (rows + kExpertChunkRows - 1) / kExpertChunkRows;
+    start[e] = e < E ? mine : 0;
+    __syncthreads();
+    int base = 0;
+    for (int q = 0; q < e && q < E; ++q) base += start[q];
+    if (e == E - 1) *chunks.n_chunks = base + mine;
+    for (int j = 0; j < mine; ++j) {
+      const int c = base + j, first = row0 + j * kExpertChunkRows, n = min(kExpertChunkRows, rows - j * kExpertChunkRows);
+      chunks.chunk_expert[c] = e, chunks.chunk_row0[c] = first, chunks.chunk_rows[c] = n;
+      for (int m = 0; m < n; ++m) chunks.pos_chunk[first + m] = c, chunks.pos_col[first + m] = m;
+    }
   }
 }
 
@@ -399,8 +416,9 @@ extern "C" int lx_moe_experts_grouped(const void* latent, const int32_t* ids, co
   const int P = T * top_k;
   const Layout l = layout(P, E, L, I);
   auto* ws = static_cast<uint8_t*>(workspace);
+  const ExpertChunkTables chunks = experts_tc_ok(*gate_up, *down, L, I) ? expert_chunk_tables(ws, l.total, P, E, L, I) : ExpertChunkTables{};
   if (int e = launch_kernel(group_kernel, dim3(1), dim3(1024), 0, s, ids, P, E, reinterpret_cast<int32_t*>(ws + l.offsets),
-                            reinterpret_cast<int32_t*>(ws + l.pairs)))
+                            reinterpret_cast<int32_t*>(ws + l.pairs), chunks))
     return e;
   return run_experts(latent, ids, weights, *gate_up, *down, out, ws, l, false, E, E, T, L, I, top_k, s);
 }
@@ -462,8 +480,9 @@ extern "C" int lx_b200_moe_experts_grouped_static(const void* latent, const int3
   if (int e = static_scratch(&base)) return e;
   auto s = static_cast<cudaStream_t>(stream);
   uint8_t* ws = base + kStaticHeaderBytes;
+  const ExpertChunkTables chunks = experts_tc_ok(*gate_up, *down, L, I) ? expert_chunk_tables(ws, l.total, P, E, L, I) : ExpertChunkTables{};
   if (int e = launch_kernel(group_kernel, dim3(1), dim3(1024), 0, s, ids, P, E, reinterpret_cast<int32_t*>(ws + l.offsets),
-                            reinterpret_cast<int32_t*>(ws + l.pairs)))
+                            reinterpret_cast<int32_t*>(ws + l.pairs), chunks))
     return e;
   return run_experts(latent, ids, weights, *gate_up, *down, out, ws, l, false, E, E, T, L, I, top_k, s,
                      reinterpret_cast<int*>(base));

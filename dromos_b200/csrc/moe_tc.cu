@@ -1,6 +1,7 @@
 // The two grouped products of the routed experts on the 5th-generation tensor cores: gate/up with SwiGLU, then down.
 //
-// After the pairs (token, pick) have been sorted by expert, an expert's rows are cut into CHUNKS of up to 16 rows. A
+// After the pairs (token, pick) have been sorted by expert, an expert's rows are cut into CHUNKS of up to 16 rows (the
+// grouping kernel writes the chunk tables with its own). A
 // tile is one chunk x R weight rows of its expert x all of K: the weight tile is the A operand of tcgen05.mma exactly
 // as it lands in shared memory (128-byte-swizzled 2-D TMA boxes addressed in the stack [E, N, K]), the chunk's rows are
 // the B operand as digit columns (BF16: bf16; FP8: two e4m3 digits; INT8: three int8 digits), prepared once per stage
@@ -22,7 +23,7 @@
 namespace b200 {
 namespace {
 
-constexpr int kChunkRows = 16;  // rows of one expert a tile multiplies at once
+constexpr int kChunkRows = kExpertChunkRows;  // rows of one expert a tile multiplies at once
 constexpr int kExpertThreads = 192;  // warps 0-3 epilogue, warp 4 producers, warp 5 MMA issuer
 constexpr int kDBuf = 256;           // two accumulator sets, 256 TMEM columns apart
 
@@ -53,30 +54,6 @@ struct ExpertParams {
   int* status;
   int SW, SX;
 };
-
-// ---- chunk table -------------------------------------------------------------------------------------------------------
-// One CTA of 1024 threads; thread e cuts expert e's rows into chunks. offsets: E + 1 exclusive prefix counts.
-__global__ void __launch_bounds__(1024) chunk_kernel(const int32_t* __restrict__ offsets, int E, int32_t* __restrict__ n_chunks,
-                                                     int32_t* __restrict__ chunk_expert, int32_t* __restrict__ chunk_row0,
-                                                     int32_t* __restrict__ chunk_rows, int32_t* __restrict__ pos_chunk,
-                                                     int32_t* __restrict__ pos_col) {
-  pdl_trigger();
-  pdl_wait();
-  __shared__ int32_t count[1024];
-  const int e = threadIdx.x;
-  const int row0 = e < E ? offsets[e] : 0, rows = e < E ? offsets[e + 1] - row0 : 0;
-  const int mine = (rows + kChunkRows - 1) / kChunkRows;
-  count[e] = mine;
-  __syncthreads();
-  int base = 0;
-  for (int q = 0; q < e && q < E; ++q) base += count[q];
-  if (e == E - 1) *n_chunks = base + mine;
-  for (int j = 0; j < mine; ++j) {
-    const int c = base + j, first = row0 + j * kChunkRows, n = min(kChunkRows, rows - j * kChunkRows);
-    chunk_expert[c] = e, chunk_row0[c] = first, chunk_rows[c] = n;
-    for (int m = 0; m < n; ++m) pos_chunk[first + m] = c, pos_col[first + m] = m;
-  }
-}
 
 // ---- activation blocks of the chunks -----------------------------------------------------------------------------------
 // Block (k piece, sorted position u): as tc_prep_kernel, but the row is gathered (src row = pairs[u] / top_k for the
@@ -397,6 +374,13 @@ struct ExpertTcLayout {
 
 int64_t experts_tc_workspace(int64_t base, int P, int E, int L, int I) { return ExpertTcLayout(base, P, E, L, I).total; }
 
+ExpertChunkTables expert_chunk_tables(uint8_t* ws, int64_t base, int P, int E, int L, int I) {
+  const ExpertTcLayout lay(base, P, E, L, I);
+  return ExpertChunkTables{reinterpret_cast<int32_t*>(ws + lay.n_chunks),  reinterpret_cast<int32_t*>(ws + lay.chunk_expert),
+                           reinterpret_cast<int32_t*>(ws + lay.chunk_row0), reinterpret_cast<int32_t*>(ws + lay.chunk_rows),
+                           reinterpret_cast<int32_t*>(ws + lay.pos_chunk), reinterpret_cast<int32_t*>(ws + lay.pos_col)};
+}
+
 // Can the routed experts run on the tensor-core kernels? Both stacks of the same directly readable format, rows of
 // whole 16-byte pieces.
 bool experts_tc_ok(const lx_weight& gate_up, const lx_weight& down, int L, int I) {
@@ -422,9 +406,7 @@ int experts_tc(const void* latent, const float* weights, const lx_weight& gate_u
   int32_t* pos_col = reinterpret_cast<int32_t*>(ws + lay.pos_col);
   float* inv = reinterpret_cast<float*>(ws + lay.inv);
   uint8_t* xprep = ws + lay.xprep;
-  if (int e = launch_kernel(chunk_kernel, dim3(1), dim3(1024), 0, stream, offsets, E, n_chunks, chunk_expert, chunk_row0, chunk_rows, pos_chunk,
-                            pos_col))
-    return e;
+  (void)offsets;  // the chunk tables were written together with the grouping tables (group_kernel)
   const int act = act_of(gate_up.type), elem = act_elem(act), KS = ks_of(act);
   const int planes = act_planes(act, true);
   ExpertParams Pm{};
