@@ -62,16 +62,15 @@ def measured_peak_gbs():
         return 6650.0, "fallback"
 
 
-def hold_load(fn, seconds=0.6):
+def hold_load(fn, once_ms, seconds=0.6):
     """The K timed steps last a few milliseconds, less than one nvidia-smi sample: the same work is repeated (untimed)
-    for a moment while the clock sampler still runs, so that the clocks it reports are clocks under this load."""
+    for a moment while the clock sampler still runs, so that the clocks it reports are clocks under this load. The
+    number of repetitions comes from the measured time (the same on every rank, so collectives inside fn stay matched)."""
     import torch
 
-    end = time.time() + seconds
-    while time.time() < end:
-        for _ in range(20):
-            fn()
-        torch.cuda.synchronize()
+    for _ in range(max(1, min(2000, int(seconds * 1e3 / max(once_ms, 1e-3))))):
+        fn()
+    torch.cuda.synchronize()
 
 
 class ClockSampler:
@@ -277,10 +276,13 @@ def main():
     # launch edges included) and replayed; LX_BENCH_GRAPHS=0 launches every kernel from Python instead.
     use_graphs = os.environ.get("LX_BENCH_GRAPHS", "1") != "0"
 
+    all_graphs = []
+
     def capture(fn):
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             fn()
+        all_graphs.append(g)
         return g
 
     def replayer(fn, period):
@@ -337,7 +339,7 @@ def main():
             ms = timed(lambda i: whole.replay(), 1)
         else:
             ms = timed(lambda i: run_step(args.warmup + i), args.steps)
-        hold_load(whole.replay if whole is not None else (lambda: run_step(0)))
+        hold_load(whole.replay if whole is not None else (lambda: run_step(0)), ms if whole is not None else ms / args.steps)
     launches = launches_per_period * args.steps // period
     value = total_step_bytes * args.steps / (ms * 1e-3) / 1e12
 
@@ -393,9 +395,23 @@ def main():
            "h2d_bytes_per_step": sum(M * K * 2 for M in Ms), "d2h_bytes_per_step": sum(M * N * 4 for M in Ms)}
 
     status = lib.lx_b200_last_error()
-    if rank != 0:
+
+    def leave():
+        """Graphs that hold NCCL kernels must be gone before the communicator is: release them, meet, then leave the
+        process without running NCCL's destructors (which can wait for ever on a communicator a graph once captured)."""
+        torch.cuda.synchronize()
+        for g in all_graphs:
+            g.reset()
+        all_graphs.clear()
         if world > 1:
-            dist.destroy_process_group()
+            dist.barrier()
+            torch.cuda.synchronize()
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)
+
+    if rank != 0:
+        leave()
         return
     out = {"metric": metric, "value": value, "unit": "TB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
@@ -410,9 +426,8 @@ def main():
         else:
             out["cpu_baseline"] = {"value": None, "unit": "TB/s", "cores": os.cpu_count(), "kind": "reference",
                                    "sample": "oracle/_ref/libdromos_cpu.so not built"}
-    print(json.dumps(out))
-    if world > 1:
-        dist.destroy_process_group()
+    print(json.dumps(out), flush=True)
+    leave()
 
 
 def main_moe(args):
@@ -523,7 +538,7 @@ def main_moe(args):
         whole.replay()
     with ClockSampler(local) as clocks:
         ms = timed((lambda i: whole.replay()), 1) if whole is not None else timed(lambda i: run(args.warmup + i), args.steps)
-        hold_load(whole.replay if whole is not None else (lambda: run(0)))
+        hold_load(whole.replay if whole is not None else (lambda: run(0)), ms if whole is not None else ms / args.steps)
     step_bytes = [per_expert * touched[(args.warmup + i) % periods] for i in range(args.steps)]
     value = sum(step_bytes) / (ms * 1e-3) / 1e12
     peak, peak_kind = measured_peak_gbs()
@@ -564,7 +579,10 @@ def main_moe(args):
             "cpu_baseline": {"value": None, "unit": "TB/s", "cores": os.cpu_count(), "kind": "reference",
                              "sample": "not timed for this workload (the dense workloads time the reference CPU backend)"}}))
     if world > 1:
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":
