@@ -55,6 +55,13 @@ struct TcParams {
   int bias_dtype;
   void* y;
   int y_dtype, ld_y;
+  // All-gather epilogue (peers > 0): the tile's outputs go to column col0 + n of every rank's copy of the whole y
+  // (peer-mapped pointers, this rank's own among them) instead of P.y, and when the CTA is done each of its epilogue
+  // warps adds one to every rank's arrival counter.
+  void* y_peer[8];
+  int* flag_peer[8];
+  int peers;
+  int64_t col0;
   float alpha, beta;
   int* status;
   int SW, SX;             // depth of the weight ring and of the activation ring
@@ -145,6 +152,10 @@ __device__ __forceinline__ void combine_and_store(const TcParams& P, const uint3
     sum *= inv[j];
     float out = P.alpha * (rf * sum + bias);
     const int64_t at = static_cast<int64_t>(m) * P.ld_y + n;
+    if (P.peers > 0) {
+      for (int g = 0; g < P.peers; ++g) store_from_f32(P.y_peer[g], P.y_dtype, at + P.col0, out);
+      continue;
+    }
     if (P.beta != 0.0f) out = fmaf(P.beta, load_f32(P.y, P.y_dtype, at), out);
     store_from_f32(P.y, P.y_dtype, at, out);
   }
@@ -197,6 +208,16 @@ __device__ __forceinline__ void finish_tile(const TcParams& P, const RowTerms& T
     if (T.live) combine_and_store<kAct>(P, raw, inv, c * 8, T.n, T.rf, T.bias);
   }
   if (chunk0 >= chunks) release();
+}
+
+// The all-gather epilogue's hand-off: everything this warp stored to the peers' buffers is visible system-wide before
+// the warp counts itself on every rank's arrival counter.
+__device__ __forceinline__ void signal_peers(const TcParams& P, int lane) {
+  if (P.peers <= 0) return;
+  __threadfence_system();
+  __syncwarp();
+  if (lane == 0)
+    for (int g = 0; g < P.peers; ++g) asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(P.flag_peer[g]) : "memory");
 }
 
 // Stages of raw activations a CTA that prepares its own keeps in flight (32 bytes per thread and stage for bf16, 64 for f32).
@@ -369,6 +390,7 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_di
         tc_fence_after();
         finish_tile<F>(P, T, lane_addr + buf * kDBufColumns, lane, 0, 1, inv_lo, inv_hi, d_empty(buf));
       }
+      signal_peers(P, lane);  // (a CTA whose wait gave up still counts itself: nobody hangs, the status word tells)
     } else {
       static_assert(act_elem(kAct) == 1, "CTAs prepare their own activations for the 8-bit maths only");
       constexpr int V = 16;
@@ -561,8 +583,10 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_di
         step2(s, tile);
       }
       asm volatile("cp.async.wait_group 0;" ::: "memory");
-      if (group == 0)
+      if (group == 0) {
         while (ok && next_finish < tile_end) ok = finish(next_finish++);
+        signal_peers(P, lane);
+      }
     }
   }
   __syncthreads();
@@ -764,7 +788,7 @@ int tile_rows(int N, int sms) {
 }
 
 template <int F, int XMODE>
-int tc_launch(const lx_weight& w, TcParams P, cudaStream_t stream) {
+int tc_launch(const lx_weight& w, TcParams P, cudaStream_t stream, int* grid_out = nullptr) {
   using Fm = TcFmt<F>;
   constexpr int kBoxes = Fm::kRowBytes / 128;
   const int sms = sm_count();
@@ -789,6 +813,7 @@ int tc_launch(const lx_weight& w, TcParams P, cudaStream_t stream) {
   if (int e = make_tile_map(&wmap, w.data, row_bytes, P.N, 128, P.R, 4, true)) return e;
   const int tiles = (P.N + P.R - 1) / P.R;
   const int grid = std::min(tiles, sms);
+  if (grid_out) *grid_out = grid;
   if constexpr (F == LX_W_NVFP4) {
     static_assert(XMODE == 0, "NVFP4 takes prepared activations");
     if (int e = make_tile_map(&smap, w.scale, P.K / 16, P.N, 16, P.R, 1, false)) return e;
@@ -833,7 +858,7 @@ bool tc_enabled() {
 }
 
 // Can up to 8 activation rows go through the tensor-core product without a workspace? INT8 and FP8 weights whose
-// tiles come out at 64 rows or more (smaller ones leave the tensor pipe's instruction rate, not HBM, as the bound),
+// tiles come out at 40 rows or more (smaller ones leave the tensor pipe's instruction rate, not HBM, as the bound),
 // rows of whole 16-byte pieces. The answer depends on the weight and its shape only, never on the row count, so that
 // a row's bits do not depend on its batch. (BF16 stays with the streaming kernel, whose bits the lossless BF16X
 // format must reproduce.)
@@ -841,7 +866,7 @@ bool tc_rows_ok(const lx_weight& w, int N, int K) {
   if (!tc_enabled() || (w.type != LX_W_INT8 && w.type != LX_W_FP8)) return false;
   if (K % 16 != 0 || (reinterpret_cast<uintptr_t>(w.data) & 15) != 0) return false;
   const int sms = sm_count();
-  return sms > 0 && tile_rows(N, sms) >= 64;
+  return sms > 0 && tile_rows(N, sms) >= 40;
 }
 
 // Up to 8 activation rows, prepared by the product kernel itself: one launch, no workspace.
@@ -900,6 +925,81 @@ int tc_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const v
     }
     if (e) return e;
   }
+  return kOk;
+}
+
+// ---- the product with an all-gather epilogue ---------------------------------------------------------------------------
+// A counting semaphore: waits (bounded) until the counter holds at least `total` arrivals, then takes them. Arrivals of
+// a later round that come early stay in the counter, and nothing here depends on how often the call has run before, so
+// a captured graph can be replayed.
+__global__ void wait_arrivals_kernel(int* counter, int total, int* status) {
+  pdl_trigger();
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+    if (v >= total) break;
+    if (global_timer_ns() - t0 > 1000000000ull) {  // a peer that never arrives: give up after a second and say so
+      if (status) atomicExch(status, kStatusTcWait);
+      return;
+    }
+  }
+  asm volatile("red.relaxed.sys.global.add.s32 [%0], %1;" ::"l"(counter), "r"(-total) : "memory");
+}
+
+int tc_wait_arrivals(int* counter, int total, cudaStream_t stream) {
+  return launch_kernel(wait_arrivals_kernel, dim3(1), dim3(1), 0, stream, counter, total, status_word());
+}
+
+// One pass (M <= 64 rows for bf16 activations) of BF16 / INT8 / FP8 weights whose outputs go straight into every rank's
+// y. *arrivals_added: what this launch adds to each rank's counter when it is done.
+int tc_product_allgather(const void* x, int x_dtype, int ld_x, const lx_weight& w, const void* bias, int bias_dtype,
+                         const PeerTargets& T, int y_dtype, int ld_y, int M, int N, int K, float alpha, void* workspace,
+                         int* arrivals_added, cudaStream_t stream) {
+  if (!tc_enabled() || T.ranks < 1 || T.ranks > 8) return kNotSupported;
+  if (w.type != LX_W_BF16 && w.type != LX_W_INT8 && w.type != LX_W_FP8) return kNotSupported;
+  const bool x_bf16 = x_dtype == LX_BF16;
+  const int act = act_of(w.type);
+  const bool own = M <= 8 && tc_rows_ok(w, N, K);
+  if (!own && (!workspace || M > rows_per_pass(act, x_bf16))) return kNotSupported;
+  TcParams P = base_params(w, bias, bias_dtype, y_dtype, ld_y, N, K, alpha, 0.0f, act, x_bf16, M);
+  P.peers = T.ranks, P.col0 = T.col0;
+  for (int g = 0; g < T.ranks; ++g) P.y_peer[g] = T.y_all[g], P.flag_peer[g] = T.arrivals[g];
+  int grid = 0, e;
+  if (own) {
+    P.x = x, P.ld_x = ld_x;
+    if (w.type == LX_W_INT8) e = x_bf16 ? tc_launch<LX_W_INT8, 1>(w, P, stream, &grid) : tc_launch<LX_W_INT8, 2>(w, P, stream, &grid);
+    else e = x_bf16 ? tc_launch<LX_W_FP8, 1>(w, P, stream, &grid) : tc_launch<LX_W_FP8, 2>(w, P, stream, &grid);
+  } else {
+    const int elem = act_elem(act), kKS = ks_of(act), n_stages = (K + kKS - 1) / kKS;
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    const TcLayout L(P.NC, act, n_stages);
+    P.xprep = ws;
+    P.inv_scales = reinterpret_cast<const float*>(ws + L.scales);
+    const int per_block = 128 * 16 / elem;
+    const dim3 prep_grid((n_stages * kKS + per_block - 1) / per_block, M);
+    auto prep = [&](auto kernel) {
+      return launch_kernel(kernel, prep_grid, dim3(128), 0, stream, x, ld_x, M, K, P.NC, P.Mp, P.planes, ws, reinterpret_cast<float*>(ws + L.scales),
+                           n_stages);
+    };
+    int pe;
+    switch (act * 2 + (x_bf16 ? 1 : 0)) {
+      case kActBf16 * 2: pe = prep(tc_prep_kernel<kActBf16, false>); break;
+      case kActBf16 * 2 + 1: pe = prep(tc_prep_kernel<kActBf16, true>); break;
+      case kActE4m3 * 2: pe = prep(tc_prep_kernel<kActE4m3, false>); break;
+      case kActE4m3 * 2 + 1: pe = prep(tc_prep_kernel<kActE4m3, true>); break;
+      case kActS8 * 2: pe = prep(tc_prep_kernel<kActS8, false>); break;
+      default: pe = prep(tc_prep_kernel<kActS8, true>); break;
+    }
+    if (pe) return pe;
+    switch (w.type) {
+      case LX_W_BF16: e = tc_launch<LX_W_BF16, 0>(w, P, stream, &grid); break;
+      case LX_W_INT8: e = tc_launch<LX_W_INT8, 0>(w, P, stream, &grid); break;
+      default: e = tc_launch<LX_W_FP8, 0>(w, P, stream, &grid); break;
+    }
+  }
+  if (e) return e;
+  if (arrivals_added) *arrivals_added = grid * 4;  // one per epilogue warp of every CTA
   return kOk;
 }
 

@@ -160,6 +160,17 @@ int tc_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const v
                int ld_y, int M, int N, int K, float alpha, float beta, void* workspace, cudaStream_t stream);
 int64_t tc_workspace_bytes(int M, int K);
 bool tc_enabled();
+// Where the all-gather epilogue of a sharded product stores: every rank's copy of the whole y and arrival counter.
+struct PeerTargets {
+  void* const* y_all;      // host array: every rank's whole-y buffer (peer-mapped device pointers), this rank's too
+  int* const* arrivals;    // host array: every rank's arrival counter
+  int ranks;
+  int64_t col0;            // first column of this rank's slice in the whole y
+};
+int tc_product_allgather(const void* x, int x_dtype, int ld_x, const lx_weight& w, const void* bias, int bias_dtype,
+                         const PeerTargets& T, int y_dtype, int ld_y, int M, int N, int K, float alpha, void* workspace,
+                         int* arrivals_added, cudaStream_t stream);
+int tc_wait_arrivals(int* counter, int total, cudaStream_t stream);
 // Rows of one expert that a tile of the tensor-core expert kernels multiplies at once, and the tables that cut the sorted
 // pairs into such chunks (written by group_kernel, read by the kernels of moe_tc.cu; they live in the workspace).
 constexpr int kExpertChunkRows = 16;

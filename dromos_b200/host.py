@@ -15,6 +15,7 @@ torch is used for device memory, streams and the process group only. Nothing her
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -267,3 +268,65 @@ class ExpertParallel:
         for j in range(1, k):
             out += per_pair[:, j]
         return out
+
+
+class FusedShardedLinear:
+    """ShardedLinear without the collective: every rank's product stores its slice of y straight into every rank's copy
+    of the whole y (lx_b200_linear_allgather: NVLink stores from the kernel's epilogue through peer-mapped pointers) and
+    counts itself on every rank's arrival counter; lx_b200_wait_arrivals then holds the stream until all slices are in.
+    The buffers and counters are torch symmetric memory (one allocation per layer, exchanged once at construction).
+
+    Each layer owns two whole-y buffers used in turn, so that a rank one call ahead never overwrites the y a slower rank
+    is still reading. Raises if symmetric memory or the tensor-core product is not available for this weight; callers
+    then use ShardedLinear (NCCL all-gather)."""
+
+    def __init__(self, lib, w_bf16_shard: torch.Tensor, wtype: int, N: int, K: int, max_rows: int, group=None):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer mappings only
+        self.lib, self.dist, self.group = lib, dist, group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if self.world > 8:
+            raise RuntimeError("the all-gather epilogue addresses at most 8 ranks")
+        self.N, self.K, self.max_rows = N, K, max_rows
+        self.n0, self.n1 = shard_rows(N, self.rank, self.world)
+        self.weight = store_weight(lib, w_bf16_shard.contiguous(), wtype)
+        dev = w_bf16_shard.device
+        self.y = symm.empty((2, max_rows, N), dtype=torch.float32, device=dev)
+        self.counter = symm.empty((64,), dtype=torch.int32, device=dev)
+        self.counter.zero_()
+        hy, hc = symm.rendezvous(self.y, self.group), symm.rendezvous(self.counter, self.group)
+        self._y_ptrs, self._c_ptrs = [int(p) for p in hy.buffer_ptrs], [int(p) for p in hc.buffer_ptrs]
+        self._c_array = (ctypes.c_void_p * self.world)(*self._c_ptrs)
+        self._calls, self._total = 0, {}
+        self._ws = None
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        """x: bf16 or f32 [M, K], the same on every rank. Returns this rank's whole y, f32 [M, N] (valid on the stream)."""
+        M = x.shape[0]
+        assert M <= self.max_rows
+        half = self._calls & 1
+        self._calls += 1
+        stride = self.max_rows * self.N * 4
+        y_array = (ctypes.c_void_p * self.world)(*[p + half * stride for p in self._y_ptrs])
+        need = self.lib.lx_gemm_workspace_bytes(M, self.K, abi.MATH_BF16)
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = torch.empty(max(need, 256), dtype=torch.uint8, device=x.device)
+        added = ctypes.c_int(0)
+        x_dt = abi.BF16 if x.dtype == torch.bfloat16 else abi.F32
+        st = self.lib.lx_b200_linear_allgather(abi.ptr(x), x_dt, x.stride(0), self.weight.ref(), None, abi.BF16, y_array, self._c_array,
+                                               self.world, self.n0, abi.F32, self.N, M, self.n1 - self.n0, self.K, 1.0, abi.ptr(self._ws),
+                                               ctypes.byref(added), _stream())
+        if st:
+            raise RuntimeError(f"lx_b200_linear_allgather failed: {st}")
+        if M not in self._total:  # what one round adds to a counter: every rank's share, exchanged once per row count
+            shares = [None] * self.world
+            self.dist.all_gather_object(shares, int(added.value), group=self.group)
+            self._total[M] = int(sum(shares))
+        st = self.lib.lx_b200_wait_arrivals(self._c_ptrs[self.rank], self._total[M], _stream())
+        if st:
+            raise RuntimeError(f"lx_b200_wait_arrivals failed: {st}")
+        return self.y[half, :M]

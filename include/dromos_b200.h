@@ -150,6 +150,24 @@ LX_API int64_t lx_b200_kernel_launches(void);
  * Synchronizes the device. */
 LX_API int lx_b200_last_error(void);
 
+/* A row-sharded product whose epilogue is the all-gather (no counterpart in the reference, which is single-GPU). Every
+ * rank calls it with its rows of W (N rows, the columns col0 .. col0 + N - 1 of the whole y): the outputs are stored
+ * straight into every rank's copy of the whole y, y_all[r] (host array of `ranks` peer-mapped device pointers to
+ * [M, ld_y] buffers, this rank's own among them), and when the product is done each rank's arrival counter,
+ * *arrivals[r] (int32, peer-mapped, zero before the first call), has been increased by *arrivals_added. A consumer of
+ * the whole y calls lx_b200_wait_arrivals(counter, total) on its own counter with total = the sum of every rank's
+ * *arrivals_added: a counting semaphore, it waits until the counter holds `total` and takes them (arrivals of the next
+ * round that come early stay), so the pair of calls can sit in a replayed graph. The wait is bounded (1 s); a timeout
+ * shows in lx_b200_last_error.
+ * BF16 / INT8 / FP8 weights, M within one pass (64 rows of bf16 activations); up to 8 rows of INT8 / FP8 need no
+ * workspace, otherwise lx_gemm_workspace_bytes(M, K, LX_MATH_BF16). Other cases answer LX_ERR_NOT_SUPPORTED: use
+ * lx_gemv_w / lx_gemm_w and a collective. y = alpha * (x W^T + bias); nothing is read from y. */
+LX_API int lx_b200_linear_allgather(const void* x, lx_dtype x_dtype, int ld_x, const lx_weight* w, const void* bias,
+                                    lx_dtype bias_dtype, void* const* y_all, int* const* arrivals, int ranks, int64_t col0,
+                                    lx_dtype y_dtype, int ld_y, int M, int N, int K, float alpha, void* workspace,
+                                    int* arrivals_added, void* stream);
+LX_API int lx_b200_wait_arrivals(int* counter, int total, void* stream);
+
 /* Routed experts for callers that must not allocate. No counterpart in the reference: its lx_moe_experts_grouped always
  * takes a caller workspace. Same arguments, result and error codes as lx_moe_experts_grouped above minus the workspace:
  * the scratch is a fixed 8 MiB array inside the library image, of which lx_b200_moe_static_scratch_bytes() are usable

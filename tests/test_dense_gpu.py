@@ -245,3 +245,42 @@ def test_argument_errors(lx):
     ws = torch.empty(1 << 20, dtype=torch.uint8, device="cuda")
     assert util.gemv(lx, x, abi.BF16, K, dw, y, abi.F32, N, 8, N, K, fn="lx_gemm_w", math=abi.MATH_FP4,
                      workspace=ws) == abi.ERR_NOT_SUPPORTED
+
+
+@pytest.mark.parametrize("fmt", [O.W_BF16, O.W_INT8, O.W_FP8], ids=lambda f: NAMES[f])
+@pytest.mark.parametrize("M", [3, 20])
+def test_allgather_epilogue_on_one_gpu(lx, fmt, M):
+    """lx_b200_linear_allgather with the two "ranks" played one after the other on one GPU: each stores its row shard's
+    outputs into its columns of the one whole y and counts itself; lx_b200_wait_arrivals takes both rounds' arrivals.
+    The slices equal the same products through lx_gemm_w bit for bit (the same kernels, another epilogue)."""
+    import ctypes
+
+    N, K = 19210, 1024  # two shards of 9605 rows: wide enough for up to 8 rows to take the tensor-core GEMV
+    half = N // 2
+    w_bits = util.bf16_normal((N, K), 0.02, 41)
+    x = util.bf16_normal((M, K), 1.0, 42)
+    x_dev = util.dev(x)
+    y = torch.full((M, N), float("nan"), device="cuda")
+    counter = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ws = torch.empty(lx.lx_gemm_workspace_bytes(M, K, 0), dtype=torch.uint8, device="cuda")
+    y_all = (ctypes.c_void_p * 1)(y.data_ptr())
+    c_all = (ctypes.c_void_p * 1)(counter.data_ptr())
+    total, shards = 0, []
+    for r in range(2):
+        dw = util.DeviceWeight(util.make_weight(w_bits[r * half:(r + 1) * half], fmt))
+        shards.append(dw)
+        added = ctypes.c_int(0)
+        st = lx.lx_b200_linear_allgather(abi.ptr(x_dev), abi.BF16, K, dw.ref(), None, abi.BF16, y_all, c_all, 1, r * half, abi.F32, N, M,
+                                         half, K, 1.0, abi.ptr(ws), ctypes.byref(added), util.stream_ptr())
+        assert st == 0 and added.value > 0
+        total += added.value
+    assert lx.lx_b200_wait_arrivals(counter.data_ptr(), total, util.stream_ptr()) == 0
+    util.check_status(lx)
+    assert int(counter[0].item()) == 0  # the wait took exactly what the two products added
+    got = util.host(y)
+    for r in range(2):
+        ref = torch.full((M, half), float("nan"), device="cuda")
+        assert util.gemv(lx, x_dev, abi.BF16, K, shards[r], ref, abi.F32, half, M, half, K, fn="lx_gemm_w", workspace=ws) == 0
+        assert np.array_equal(got[:, r * half:(r + 1) * half].view(np.uint32), util.host(ref).view(np.uint32)), f"shard {r}"
+    want = O.gemv_reference(O.bf16_bits_to_f32(x).astype(np.float64), util.reference_weight(w_bits, util.make_weight(w_bits, fmt)))
+    util.assert_close(got, want, what=NAMES[fmt])
