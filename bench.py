@@ -265,9 +265,32 @@ def main():
         dist.all_reduce(total_step_bytes)
     total_step_bytes = float(total_step_bytes.item())
 
+    # More than one GPU: the products store their slices straight into every rank's y (the all-gather is the kernel's
+    # epilogue, NVLink peer stores, no collective kernel). Where that is not available (format, symmetric memory) the
+    # slices meet in an NCCL all-gather instead. LX_BENCH_FUSED=0 forces the latter.
+    fused = None
+    if world > 1 and os.environ.get("LX_BENCH_FUSED", "1") != "0":
+        try:
+            fused = [host.FusedShardedLinear(lib, None, wtype, N, K, max(Ms), stored=sw) for sw in stored]
+            for M in Ms:
+                fused[0](xs[M])
+            torch.cuda.synchronize()
+        except Exception as e:
+            print(f"[bench] all-gather epilogue unavailable ({type(e).__name__}: {e}); using NCCL all-gather", file=sys.stderr)
+            fused = None
+        ok = torch.tensor([1 if fused is not None else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)  # every rank takes the same path
+        if int(ok.item()) == 0:
+            fused = None
+    config["exchange"] = "all-gather epilogue (peer stores over NVLink)" if fused is not None else ("NCCL all-gather" if world > 1 else "none")
+
     def step(i):
         for j, M in enumerate(Ms):
-            layers[(i * len(Ms) + j) % copies](xs[M], ys[M])
+            c = (i * len(Ms) + j) % copies
+            if fused is not None:
+                fused[c](xs[M])
+                continue
+            layers[c](xs[M], ys[M])
             if world > 1:
                 dist.all_gather_into_tensor(gathered[M].view(world * M, n1 - n0), ys[M])
 
@@ -375,6 +398,9 @@ def main():
     def e2e_work(i):
         for j, M in enumerate(Ms):
             xd[M].copy_(xh[M], non_blocking=True)
+            if fused is not None:
+                yh[M].copy_(fused[(i * len(Ms) + j) % copies](xd[M]), non_blocking=True)
+                continue
             layers[(i * len(Ms) + j) % copies](xd[M], ys[M])
             if world > 1:
                 dist.all_gather_into_tensor(gathered[M].view(world * M, n1 - n0), ys[M])

@@ -273,20 +273,21 @@ extern "C" int lx_gemm_w(const void* x, lx_dtype x_dtype, int ld_x, const lx_wei
 
 // ---- additions: a row-sharded product whose epilogue is the all-gather ---------------------------------------------
 // Every rank multiplies its rows of W and stores its slice of y straight into every rank's copy of the whole y through
-// peer-mapped pointers (NVLink stores from the epilogue threads), then counts itself on every rank's arrival counter; a
+// peer-mapped pointers (NVLink stores from the epilogue threads); the grid's last warp then adds one arrival to every
+// rank's semaphore; a
 // consumer waits (lx_b200_wait_arrivals, bounded) until its counter holds what all ranks add, and takes it. No collective
 // kernel runs: the transfer overlaps the tiles. BF16 / INT8 / FP8 weights on the tcgen05 product; beta = 0.
 extern "C" int lx_b200_linear_allgather(const void* x, lx_dtype x_dtype, int ld_x, const lx_weight* w, const void* bias,
-                                        lx_dtype bias_dtype, void* const* y_all, int* const* arrivals, int ranks, int64_t col0,
+                                        lx_dtype bias_dtype, void* const* y_all, int* const* arrivals, int ranks, int rank, int64_t col0,
                                         lx_dtype y_dtype, int ld_y, int M, int N, int K, float alpha, void* workspace,
                                         int* arrivals_added, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0 || ld_x < K || ld_y < N || !w || !w->data || !x || !y_all || !arrivals) return kInvalid;
   if (!valid_dtype(x_dtype) || !valid_dtype(y_dtype) || (bias && !valid_dtype(bias_dtype))) return kInvalid;
-  if (ranks < 1 || ranks > 8 || col0 < 0 || col0 + N > ld_y) return kInvalid;
+  if (ranks < 1 || ranks > 8 || rank < 0 || rank >= ranks || col0 < 0 || col0 + N > ld_y) return kInvalid;
   if (w->type != LX_W_BF16 && !w->scale) return kInvalid;
   const int64_t rowb = row_bytes_of(w->type, K);
   if (rowb % 16 != 0 || !aligned(w->data, 16)) return kNotSupported;
-  const PeerTargets T{y_all, arrivals, ranks, col0};
+  const PeerTargets T{y_all, arrivals, ranks, rank, col0};
   return tc_product_allgather(x, x_dtype, ld_x, *w, bias, bias_dtype, T, y_dtype, ld_y, M, N, K, alpha, workspace, arrivals_added,
                               static_cast<cudaStream_t>(stream));
 }

@@ -56,10 +56,11 @@ struct TcParams {
   void* y;
   int y_dtype, ld_y;
   // All-gather epilogue (peers > 0): the tile's outputs go to column col0 + n of every rank's copy of the whole y
-  // (peer-mapped pointers, this rank's own among them) instead of P.y, and when the CTA is done each of its epilogue
-  // warps adds one to every rank's arrival counter.
+  // (peer-mapped pointers, this rank's own among them) instead of P.y; the last epilogue warp of the whole grid to
+  // finish then adds one to every rank's arrival counter.
   void* y_peer[8];
   int* flag_peer[8];
+  int* done_local;  // this rank's count of finished epilogue warps (word 1 of its own counter pair)
   int peers;
   int64_t col0;
   float alpha, beta;
@@ -210,14 +211,24 @@ __device__ __forceinline__ void finish_tile(const TcParams& P, const RowTerms& T
   if (chunk0 >= chunks) release();
 }
 
-// The all-gather epilogue's hand-off: everything this warp stored to the peers' buffers is visible system-wide before
-// the warp counts itself on every rank's arrival counter.
+// The all-gather epilogue's hand-off. Every epilogue warp, once what it stored to the peers' buffers is visible
+// system-wide, counts itself on this GPU's own counter; the warp that finds it is the last of the grid puts the counter
+// back to zero and adds ONE arrival to every rank's semaphore (a remote atomic per rank and launch, not per CTA: a
+// thousand remote atomics on one word cost more than the product itself).
 __device__ __forceinline__ void signal_peers(const TcParams& P, int lane) {
   if (P.peers <= 0) return;
   __threadfence_system();
   __syncwarp();
-  if (lane == 0)
-    for (int g = 0; g < P.peers; ++g) asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(P.flag_peer[g]) : "memory");
+  if (lane == 0) {
+    const int expected = static_cast<int>(gridDim.x) * 4;
+    int before;
+    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(before) : "l"(P.done_local) : "memory");
+    if (before == expected - 1) {
+      asm volatile("st.relaxed.gpu.global.s32 [%0], %1;" ::"l"(P.done_local), "r"(0) : "memory");
+      __threadfence_system();
+      for (int g = 0; g < P.peers; ++g) asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(P.flag_peer[g]) : "memory");
+    }
+  }
 }
 
 // Stages of raw activations a CTA that prepares its own keeps in flight (32 bytes per thread and stage for bf16, 64 for f32).
@@ -952,11 +963,11 @@ int tc_wait_arrivals(int* counter, int total, cudaStream_t stream) {
 }
 
 // One pass (M <= 64 rows for bf16 activations) of BF16 / INT8 / FP8 weights whose outputs go straight into every rank's
-// y. *arrivals_added: what this launch adds to each rank's counter when it is done.
+// y. *arrivals_added: what this launch adds to each rank's semaphore when it is done.
 int tc_product_allgather(const void* x, int x_dtype, int ld_x, const lx_weight& w, const void* bias, int bias_dtype,
                          const PeerTargets& T, int y_dtype, int ld_y, int M, int N, int K, float alpha, void* workspace,
                          int* arrivals_added, cudaStream_t stream) {
-  if (!tc_enabled() || T.ranks < 1 || T.ranks > 8) return kNotSupported;
+  if (!tc_enabled() || T.ranks < 1 || T.ranks > 8 || T.self < 0 || T.self >= T.ranks) return kNotSupported;
   if (w.type != LX_W_BF16 && w.type != LX_W_INT8 && w.type != LX_W_FP8) return kNotSupported;
   const bool x_bf16 = x_dtype == LX_BF16;
   const int act = act_of(w.type);
@@ -965,6 +976,7 @@ int tc_product_allgather(const void* x, int x_dtype, int ld_x, const lx_weight& 
   TcParams P = base_params(w, bias, bias_dtype, y_dtype, ld_y, N, K, alpha, 0.0f, act, x_bf16, M);
   P.peers = T.ranks, P.col0 = T.col0;
   for (int g = 0; g < T.ranks; ++g) P.y_peer[g] = T.y_all[g], P.flag_peer[g] = T.arrivals[g];
+  P.done_local = T.arrivals[T.self] + 1;
   int grid = 0, e;
   if (own) {
     P.x = x, P.ld_x = ld_x;
@@ -999,7 +1011,8 @@ int tc_product_allgather(const void* x, int x_dtype, int ld_x, const lx_weight& 
     }
   }
   if (e) return e;
-  if (arrivals_added) *arrivals_added = grid * 4;  // one per epilogue warp of every CTA
+  (void)grid;
+  if (arrivals_added) *arrivals_added = 1;  // the grid's last epilogue warp signals once
   return kOk;
 }
 

@@ -163,8 +163,8 @@ bool tc_enabled();
 // Where the all-gather epilogue of a sharded product stores: every rank's copy of the whole y and arrival counter.
 struct PeerTargets {
   void* const* y_all;      // host array: every rank's whole-y buffer (peer-mapped device pointers), this rank's too
-  int* const* arrivals;    // host array: every rank's arrival counter
-  int ranks;
+  int* const* arrivals;    // host array: every rank's counter pair {arrivals semaphore, finished warps of its own grid}
+  int ranks, self;         // how many ranks, and which of them this one is
   int64_t col0;            // first column of this rank's slice in the whole y
 };
 int tc_product_allgather(const void* x, int x_dtype, int ld_x, const lx_weight& w, const void* bias, int bias_dtype,

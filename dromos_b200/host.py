@@ -280,7 +280,8 @@ class FusedShardedLinear:
     is still reading. Raises if symmetric memory or the tensor-core product is not available for this weight; callers
     then use ShardedLinear (NCCL all-gather)."""
 
-    def __init__(self, lib, w_bf16_shard: torch.Tensor, wtype: int, N: int, K: int, max_rows: int, group=None):
+    def __init__(self, lib, w_bf16_shard: torch.Tensor | None, wtype: int, N: int, K: int, max_rows: int, group=None,
+                 stored: StoredWeight | None = None):
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm
 
@@ -291,8 +292,8 @@ class FusedShardedLinear:
             raise RuntimeError("the all-gather epilogue addresses at most 8 ranks")
         self.N, self.K, self.max_rows = N, K, max_rows
         self.n0, self.n1 = shard_rows(N, self.rank, self.world)
-        self.weight = store_weight(lib, w_bf16_shard.contiguous(), wtype)
-        dev = w_bf16_shard.device
+        self.weight = stored if stored is not None else store_weight(lib, w_bf16_shard.contiguous(), wtype)
+        dev = self.weight.data.device
         self.y = symm.empty((2, max_rows, N), dtype=torch.float32, device=dev)
         self.counter = symm.empty((64,), dtype=torch.int32, device=dev)
         self.counter.zero_()
@@ -318,7 +319,8 @@ class FusedShardedLinear:
         added = ctypes.c_int(0)
         x_dt = abi.BF16 if x.dtype == torch.bfloat16 else abi.F32
         st = self.lib.lx_b200_linear_allgather(abi.ptr(x), x_dt, x.stride(0), self.weight.ref(), None, abi.BF16, y_array, self._c_array,
-                                               self.world, self.n0, abi.F32, self.N, M, self.n1 - self.n0, self.K, 1.0, abi.ptr(self._ws),
+                                               self.world, self.rank, self.n0, abi.F32, self.N, M, self.n1 - self.n0, self.K, 1.0,
+                                               abi.ptr(self._ws),
                                                ctypes.byref(added), _stream())
         if st:
             raise RuntimeError(f"lx_b200_linear_allgather failed: {st}")

@@ -153,8 +153,9 @@ LX_API int lx_b200_last_error(void);
 /* A row-sharded product whose epilogue is the all-gather (no counterpart in the reference, which is single-GPU). Every
  * rank calls it with its rows of W (N rows, the columns col0 .. col0 + N - 1 of the whole y): the outputs are stored
  * straight into every rank's copy of the whole y, y_all[r] (host array of `ranks` peer-mapped device pointers to
- * [M, ld_y] buffers, this rank's own among them), and when the product is done each rank's arrival counter,
- * *arrivals[r] (int32, peer-mapped, zero before the first call), has been increased by *arrivals_added. A consumer of
+ * [M, ld_y] buffers, this rank's own, y_all[rank], among them), and when the product is done each rank's arrival
+ * semaphore, arrivals[r][0] (arrivals[r]: two int32 words, peer-mapped, zero before the first call; word 1 is used by
+ * rank r's own kernels), has been increased by *arrivals_added. A consumer of
  * the whole y calls lx_b200_wait_arrivals(counter, total) on its own counter with total = the sum of every rank's
  * *arrivals_added: a counting semaphore, it waits until the counter holds `total` and takes them (arrivals of the next
  * round that come early stay), so the pair of calls can sit in a replayed graph. The wait is bounded (1 s); a timeout
@@ -163,7 +164,8 @@ LX_API int lx_b200_last_error(void);
  * workspace, otherwise lx_gemm_workspace_bytes(M, K, LX_MATH_BF16). Other cases answer LX_ERR_NOT_SUPPORTED: use
  * lx_gemv_w / lx_gemm_w and a collective. y = alpha * (x W^T + bias); nothing is read from y. */
 LX_API int lx_b200_linear_allgather(const void* x, lx_dtype x_dtype, int ld_x, const lx_weight* w, const void* bias,
-                                    lx_dtype bias_dtype, void* const* y_all, int* const* arrivals, int ranks, int64_t col0,
+                                    lx_dtype bias_dtype, void* const* y_all, int* const* arrivals, int ranks, int rank,
+                                    int64_t col0,
                                     lx_dtype y_dtype, int ld_y, int M, int N, int K, float alpha, void* workspace,
                                     int* arrivals_added, void* stream);
 LX_API int lx_b200_wait_arrivals(int* counter, int total, void* stream);

@@ -270,13 +270,13 @@ def test_allgather_epilogue_on_one_gpu(lx, fmt, M):
         dw = util.DeviceWeight(util.make_weight(w_bits[r * half:(r + 1) * half], fmt))
         shards.append(dw)
         added = ctypes.c_int(0)
-        st = lx.lx_b200_linear_allgather(abi.ptr(x_dev), abi.BF16, K, dw.ref(), None, abi.BF16, y_all, c_all, 1, r * half, abi.F32, N, M,
+        st = lx.lx_b200_linear_allgather(abi.ptr(x_dev), abi.BF16, K, dw.ref(), None, abi.BF16, y_all, c_all, 1, 0, r * half, abi.F32, N, M,
                                          half, K, 1.0, abi.ptr(ws), ctypes.byref(added), util.stream_ptr())
         assert st == 0 and added.value > 0
         total += added.value
     assert lx.lx_b200_wait_arrivals(counter.data_ptr(), total, util.stream_ptr()) == 0
     util.check_status(lx)
-    assert int(counter[0].item()) == 0  # the wait took exactly what the two products added
+    assert int(counter[0].item()) == 0 and int(counter[1].item()) == 0  # the wait took what the products added; the warp count is back to zero
     got = util.host(y)
     for r in range(2):
         ref = torch.full((M, half), float("nan"), device="cuda")
