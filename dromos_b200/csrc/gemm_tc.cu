@@ -135,7 +135,7 @@ __device__ __forceinline__ void expand_nvfp4(uint32_t w0, uint32_t w1, uint32_t 
 }
 
 // ---- the epilogue of a tile ---------------------------------------------------------------------------------------------
-template <int kAct>
+template <int kAct, bool kPeers>
 __device__ __forceinline__ void combine_and_store(const TcParams& P, const uint32_t (&raw)[3][8], const float (&inv)[8], int m0, int n, float rf,
                                                   float bias) {
 #pragma unroll
@@ -153,7 +153,7 @@ __device__ __forceinline__ void combine_and_store(const TcParams& P, const uint3
     sum *= inv[j];
     float out = P.alpha * (rf * sum + bias);
     const int64_t at = static_cast<int64_t>(m) * P.ld_y + n;
-    if (P.peers > 0) {
+    if constexpr (kPeers) {
       for (int g = 0; g < P.peers; ++g) store_from_f32(P.y_peer[g], P.y_dtype, at + P.col0, out);
       continue;
     }
@@ -186,7 +186,8 @@ __device__ __forceinline__ RowTerms row_terms(const TcParams& P, int tile, int r
 // 8-row chunks of activations chunk0, chunk0 + chunk_step, ... inv_lo / inv_hi: lane l holds the inverse activation
 // scale of rows l and 32 + l. release_bar (0 = none) gets one arrival per warp as soon as the warp has read the
 // accumulator.
-template <int F>
+// kPeers: the all-gather epilogue (stores into every rank's y) instead of the usual one (into P.y).
+template <int F, bool kPeers>
 __device__ __forceinline__ void finish_tile(const TcParams& P, const RowTerms& T, uint32_t d_addr, int lane, int chunk0, int chunk_step,
                                             float inv_lo, float inv_hi, uint32_t release_bar) {
   constexpr int kAct = TcFmt<F>::kAct;
@@ -206,7 +207,7 @@ __device__ __forceinline__ void finish_tile(const TcParams& P, const RowTerms& T
     for (int j = 0; j < 8; ++j) inv[j] = __shfl_sync(0xffffffffu, c < 4 ? inv_lo : inv_hi, (c * 8 + j) & 31);
     tmem_wait_ld();
     if (c + chunk_step >= chunks) release();
-    if (T.live) combine_and_store<kAct>(P, raw, inv, c * 8, T.n, T.rf, T.bias);
+    if (T.live) combine_and_store<kAct, kPeers>(P, raw, inv, c * 8, T.n, T.rf, T.bias);
   }
   if (chunk0 >= chunks) release();
 }
@@ -243,7 +244,9 @@ constexpr int kDBufColumns = 256;     // two accumulators, 256 TMEM columns apar
 // XMODE 0: activation blocks come prepared from the workspace (bulk copies). XMODE 1 / 2: up to 8 rows of bf16 / f32
 // activations, which the CTA's epilogue warps turn into blocks themselves, stage by stage, straight into the ring: no
 // preparation kernel, no workspace, one launch.
-template <int F, int XMODE>
+// PEERS: the epilogue stores into every rank's y and signals (the all-gather epilogue) instead of storing into P.y; its
+// own instantiations, so that the usual kernels carry none of it (their code size shows when kernels alternate).
+template <int F, int XMODE, bool PEERS>
 __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_direct_kernel(const __grid_constant__ CUtensorMap wmap, const TcParams P) {
   using Fm = TcFmt<F>;
   constexpr int kAct = Fm::kAct, kKS = ks_of(kAct);
@@ -399,9 +402,9 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_di
         const RowTerms T = row_terms<F>(P, tile, r);
         if (!tc_wait(d_full(buf), (t >> 1) & 1, P.status)) break;
         tc_fence_after();
-        finish_tile<F>(P, T, lane_addr + buf * kDBufColumns, lane, 0, 1, inv_lo, inv_hi, d_empty(buf));
+        finish_tile<F, PEERS>(P, T, lane_addr + buf * kDBufColumns, lane, 0, 1, inv_lo, inv_hi, d_empty(buf));
       }
-      signal_peers(P, lane);  // (a CTA whose wait gave up still counts itself: nobody hangs, the status word tells)
+      if constexpr (PEERS) signal_peers(P, lane);  // (a CTA whose wait gave up still counts itself: nobody hangs, the status word tells)
     } else {
       static_assert(act_elem(kAct) == 1, "CTAs prepare their own activations for the 8-bit maths only");
       constexpr int V = 16;
@@ -533,7 +536,7 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_di
         const RowTerms T = row_terms<F>(P, tile, r);
         if (!tc_wait(d_full(buf), (t >> 1) & 1, P.status)) return false;
         tc_fence_after();
-        finish_tile<F>(P, T, lane_addr + buf * kDBufColumns, lane, 0, 1, inv, 0.0f, d_empty(buf));
+        finish_tile<F, PEERS>(P, T, lane_addr + buf * kDBufColumns, lane, 0, 1, inv, 0.0f, d_empty(buf));
         return true;
       };
       const int total = (tile_end - tile_begin) * n_stages;
@@ -596,7 +599,7 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_di
       asm volatile("cp.async.wait_group 0;" ::: "memory");
       if (group == 0) {
         while (ok && next_finish < tile_end) ok = finish(next_finish++);
-        signal_peers(P, lane);
+        if constexpr (PEERS) signal_peers(P, lane);
       }
     }
   }
@@ -781,7 +784,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
       tc_fence_after();
       pdl_wait();  // y and the activation scales come from earlier kernels
       const float inv_lo = lane < P.M ? P.inv_scales[lane] : 0.0f, inv_hi = 32 + lane < P.M ? P.inv_scales[32 + lane] : 0.0f;
-      finish_tile<F>(P, T, lane_addr + kDColumn, lane, half, 2, inv_lo, inv_hi, 0u);
+      finish_tile<F, false>(P, T, lane_addr + kDColumn, lane, half, 2, inv_lo, inv_hi, 0u);
       ++t;
     }
   }
@@ -831,8 +834,12 @@ int tc_launch(const lx_weight& w, TcParams P, cudaStream_t stream, int* grid_out
     if (int e = allow_big_smem<F * 4>(tc_nvfp4_kernel)) return e;
     return launch_kernel(tc_nvfp4_kernel, dim3(grid), dim3(kConvThreads), smem, stream, wmap, smap, P);
   } else {
-    if (int e = allow_big_smem<F * 4 + XMODE>(tc_direct_kernel<F, XMODE>)) return e;
-    return launch_kernel(tc_direct_kernel<F, XMODE>, dim3(grid), dim3(XMODE ? kOwnThreads : kDirectThreads), smem, stream, wmap, P);
+    if (P.peers > 0) {
+      if (int e = allow_big_smem<64 + F * 4 + XMODE>(tc_direct_kernel<F, XMODE, true>)) return e;
+      return launch_kernel(tc_direct_kernel<F, XMODE, true>, dim3(grid), dim3(XMODE ? kOwnThreads : kDirectThreads), smem, stream, wmap, P);
+    }
+    if (int e = allow_big_smem<F * 4 + XMODE>(tc_direct_kernel<F, XMODE, false>)) return e;
+    return launch_kernel(tc_direct_kernel<F, XMODE, false>, dim3(grid), dim3(XMODE ? kOwnThreads : kDirectThreads), smem, stream, wmap, P);
   }
 }
 
