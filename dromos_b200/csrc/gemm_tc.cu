@@ -213,18 +213,20 @@ __device__ __forceinline__ void finish_tile(const TcParams& P, const RowTerms& T
 }
 
 // The all-gather epilogue's hand-off. Every epilogue warp, once what it stored to the peers' buffers is visible
-// system-wide, counts itself on this GPU's own counter; the warp that finds it is the last of the grid puts the counter
-// back to zero and adds ONE arrival to every rank's semaphore (a remote atomic per rank and launch, not per CTA: a
-// thousand remote atomics on one word cost more than the product itself).
-__device__ __forceinline__ void signal_peers(const TcParams& P, int lane) {
+// system-wide, counts itself in shared memory; the CTA's last warp counts the CTA on this GPU's own counter; the CTA
+// that finds it is the last of the grid puts that counter back to zero and adds ONE arrival to every rank's semaphore.
+// (Atomics on one word serialise: a remote atomic per warp, 1184 per product at two ranks, cost more than the product,
+// and even 592 local ones showed; now it is 148 local and one remote per rank.) cta_count: a zeroed word of shared memory.
+__device__ __forceinline__ void signal_peers(const TcParams& P, int lane, int* cta_count) {
   if (P.peers <= 0) return;
   __threadfence_system();
   __syncwarp();
   if (lane == 0) {
-    const int expected = static_cast<int>(gridDim.x) * 4;
+    if (atomicAdd(cta_count, 1) != 3) return;  // not the CTA's last epilogue warp
+    __threadfence();
     int before;
     asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(before) : "l"(P.done_local) : "memory");
-    if (before == expected - 1) {
+    if (before == static_cast<int>(gridDim.x) - 1) {
       asm volatile("st.relaxed.gpu.global.s32 [%0], %1;" ::"l"(P.done_local), "r"(0) : "memory");
       __threadfence_system();
       for (int g = 0; g < P.peers; ++g) asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(P.flag_peer[g]) : "memory");
@@ -270,6 +272,7 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_di
   auto d_empty = [&](int b) { return bar0 + 8u * (2 * SW + 2 * SX + 2 + b); };  // accumulator b has been read
   const uint32_t group_bar = bar0 + 8u * (2 * SW + 2 * SX + 4);           // the epilogue warps meet here
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * SW + 2 * SX + 5);
+  int* cta_count = reinterpret_cast<int*>(tmem_slot + 1);                  // (PEERS) epilogue warps of this CTA that are done
   float* row_scale = reinterpret_cast<float*>(tmem_slot + 2);             // (kOwn) at 16 + 8 w + m: warp w's share of row m's largest magnitude
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -292,6 +295,7 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_di
       mbar_init(d_empty(b), 4);
     }
     mbar_init(group_bar, kOwn ? 8 : 4);
+    *cta_count = 0;
     mbar_init_fence();
   }
   if (warp == 5) {
@@ -404,7 +408,7 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_di
         tc_fence_after();
         finish_tile<F, PEERS>(P, T, lane_addr + buf * kDBufColumns, lane, 0, 1, inv_lo, inv_hi, d_empty(buf));
       }
-      if constexpr (PEERS) signal_peers(P, lane);  // (a CTA whose wait gave up still counts itself: nobody hangs, the status word tells)
+      if constexpr (PEERS) signal_peers(P, lane, cta_count);  // (a CTA whose wait gave up still counts itself: nobody hangs, the status word tells)
     } else {
       static_assert(act_elem(kAct) == 1, "CTAs prepare their own activations for the 8-bit maths only");
       constexpr int V = 16;
@@ -599,7 +603,7 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_di
       asm volatile("cp.async.wait_group 0;" ::: "memory");
       if (group == 0) {
         while (ok && next_finish < tile_end) ok = finish(next_finish++);
-        if constexpr (PEERS) signal_peers(P, lane);
+        if constexpr (PEERS) signal_peers(P, lane, cta_count);
       }
     }
   }
