@@ -284,6 +284,11 @@ def main():
         if int(ok.item()) == 0:
             fused = None
     config["exchange"] = "all-gather epilogue (peer stores over NVLink)" if fused is not None else ("NCCL all-gather" if world > 1 else "none")
+    if world > 1 and fused is None and os.environ.get("LX_BENCH_OVERLAP", "0") == "1":
+        config["exchange"] += ", overlapped with the next (independent) product of the step"
+
+    overlap = world > 1 and os.environ.get("LX_BENCH_OVERLAP", "0") == "1"
+    pending = []
 
     def step(i):
         for j, M in enumerate(Ms):
@@ -293,7 +298,13 @@ def main():
                 continue
             layers[c](xs[M], ys[M])
             if world > 1:
-                dist.all_gather_into_tensor(gathered[M].view(world * M, n1 - n0), ys[M])
+                # The three products of a step are independent, so a product's all-gather runs (on NCCL's own stream)
+                # under the next product when LX_BENCH_OVERLAP=1 (measured at 2 GPUs: no gain, the products fill every SM).
+                work = dist.all_gather_into_tensor(gathered[M].view(world * M, n1 - n0), ys[M], async_op=overlap)
+                if overlap:
+                    pending.append(work)
+        while pending:
+            pending.pop(0).wait()
 
     # The decode loop is launch-bound from Python (a product is ~15 us of GPU time), so, like the reference engine's
     # decode loop, the steps are captured once into CUDA graphs (one per rotation position, programmatic dependent
