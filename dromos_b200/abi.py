@@ -52,6 +52,12 @@ SIGNATURES = {
     "lx_moe_route": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_int, c_int, c_ptr]),
     "lx_moe_experts_grouped": (c_int, [c_ptr, c_ptr, c_ptr, _W, _W, c_int, c_ptr, c_ptr, c_int, c_int, c_int, c_int, c_int, c_ptr]),
     "lx_moe_grouped_workspace_bytes": (c_i64, [c_int, c_int, c_int, c_int, c_int, c_int]),
+    "lx_moe_experts_decode": (c_int, [c_ptr, c_ptr, c_ptr, _W, _W, c_ptr, c_ptr, c_int, c_int, c_int, c_int, c_ptr]),
+    "lx_moe_decode_workspace_bytes": (c_i64, [c_int, c_int, c_int]),
+    "lx_moe_experts_bf16x": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_int, c_int, c_int, c_ptr]),
+    "lx_moe_experts_decode_bf16": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_int, c_int, c_int, c_ptr]),
+    "lx_moe_bf16x_workspace_bytes": (c_i64, [c_int, c_int, c_int]),
+    "lx_moe_experts": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_int, c_int, c_int, c_ptr]),
     "lx_arch": (c_int, []),
     "lx_set_arch_override": (c_int, [c_int]),
     "lx_tune_get": (c_int, [ctypes.c_char_p, c_int, c_int, c_int]),

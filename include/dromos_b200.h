@@ -112,9 +112,27 @@ LX_API int lx_moe_experts_grouped(const void* latent, const int32_t* ids, const 
                                   const lx_weight* gate_up, const lx_weight* down, lx_math math, float* out,
                                   void* workspace, int T, int L, int I, int E, int top_k, void* stream);
 LX_API int64_t lx_moe_grouped_workspace_bytes(int T, int L, int I, int E, int top_k, lx_math math);
-/* Not exported yet (the engine then gets LX_ERR_NOT_SUPPORTED from its dispatcher for them): lx_moe_experts_decode,
- * lx_moe_decode_workspace_bytes (kernels.h:504-507), lx_moe_experts_bf16x, lx_moe_experts_decode_bf16,
- * lx_moe_bf16x_workspace_bytes (kernels.h:603-611), lx_moe_experts (kernels.h:224), lx_router_route (kernels.h:218). */
+/* Few tokens (T <= 8, top_k <= 8), any stored format per stack, weight-only f32 sums, batch-invariant rows.
+ * kernels.h:504-507 (engine/cuda/moe_decode.cu:397-436). BF16X stacks: both or neither (else LX_ERR_NOT_SUPPORTED). */
+LX_API int lx_moe_experts_decode(const void* latent, const int32_t* ids, const float* weights,
+                                 const lx_weight* gate_up, const lx_weight* down, float* out, void* workspace, int T,
+                                 int L, int I, int top_k, void* stream);
+LX_API int64_t lx_moe_decode_workspace_bytes(int T, int I, int top_k);
+/* The same on BF16X encodings and on plain bf16 stacks, bit-identical to each other and to lx_moe_experts.
+ * kernels.h:603-611 (engine/cuda/bf16x.cu:1336-1369). */
+LX_API int lx_moe_experts_bf16x(const void* latent, const int32_t* ids, const float* weights, const void* gate_up,
+                                const void* down, float* out, void* workspace, int T, int L, int I, int top_k,
+                                void* stream);
+LX_API int lx_moe_experts_decode_bf16(const void* latent, const int32_t* ids, const float* weights,
+                                      const void* gate_up, const void* down, float* out, void* workspace, int T,
+                                      int L, int I, int top_k, void* stream);
+LX_API int64_t lx_moe_bf16x_workspace_bytes(int T, int I, int top_k);
+/* bf16 stacks, any T; the intermediates live in a stream-ordered allocation for the length of the call, as in the
+ * reference. kernels.h:224 (engine/cuda/moe.cu:288-310). */
+LX_API int lx_moe_experts(const void* latent, const int32_t* ids, const float* weights, const void* gate_up,
+                          const void* down, float* out, int T, int L, int I, int top_k, void* stream);
+/* Not exported yet (the engine's dispatcher then falls back to lx_moe_route on logits it computes itself, as
+ * kernels.h:211-215 says hosts do): lx_router_route (kernels.h:216). */
 
 /* ---- architecture and variant table (tunable.h:37-75, engine/cuda/tunable.cu) ---------------------------- */
 typedef struct {

@@ -88,3 +88,26 @@ def test_gemv_product(ref, wt):
     assert ref.lx_gemv_w(abi.ptr(x), abi.BF16, K, ctypes.byref(lw), None, abi.BF16, abi.ptr(y), abi.F32, N, M, N, K, 1.0, 0.0, None) == 0
     want = O.gemv_reference(O.bf16_bits_to_f32(x).astype(np.float64), o)
     assert O.rel_l2(y, want) <= 1e-5
+
+
+@pytest.mark.parametrize("wt", [O.W_BF16, O.W_INT8, O.W_FP8, O.W_NVFP4])
+def test_routed_experts(ref, wt):
+    """The oracle's routed experts against the reference's few-token and grouped entry points on its CPU backend."""
+    rng = np.random.default_rng(13)
+    T, E, L, I, k = 5, 6, 128, 64, 3
+    gu = O.quantize_weight(bf16_normal(rng, (E, 2 * I, L), 0.02), wt)
+    dn = O.quantize_weight(bf16_normal(rng, (E, L, I), 0.02), wt)
+    latent = bf16_normal(rng, (T, L), 1.0)
+    ids, weights, _, _ = O.moe_route(rng.standard_normal((T, E)).astype(np.float32), None, k)
+    want = O.moe_experts_reference(latent, ids, weights, gu, dn, I)
+    lgu, ldn = abi.make_weight(wt, gu.data, gu.scale, gu.glob), abi.make_weight(wt, dn.data, dn.scale, dn.glob)
+    out = np.zeros((T, L), dtype=np.float32)
+    ws = np.zeros(max(int(ref.lx_moe_decode_workspace_bytes(T, I, k)), 16), dtype=np.uint8)
+    assert ref.lx_moe_experts_decode(abi.ptr(latent), abi.ptr(ids), abi.ptr(weights), ctypes.byref(lgu), ctypes.byref(ldn),
+                                     abi.ptr(out), abi.ptr(ws), T, L, I, k, None) == 0
+    assert O.rel_l2(out, want) <= 1e-5
+    out2 = np.zeros((T, L), dtype=np.float32)
+    ws2 = np.zeros(max(int(ref.lx_moe_grouped_workspace_bytes(T, L, I, E, k, abi.MATH_BF16)), 16), dtype=np.uint8)
+    assert ref.lx_moe_experts_grouped(abi.ptr(latent), abi.ptr(ids), abi.ptr(weights), ctypes.byref(lgu), ctypes.byref(ldn),
+                                      abi.MATH_BF16, abi.ptr(out2), abi.ptr(ws2), T, L, I, E, k, None) == 0
+    assert O.rel_l2(out2, want) <= 1e-5
