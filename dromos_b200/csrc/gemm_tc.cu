@@ -66,6 +66,7 @@ struct TcParams {
   float alpha, beta;
   int* status;
   int SW, SX;             // depth of the weight ring and of the activation ring
+  int tmem_cols, dstride; // TMEM columns the CTA takes (a power of two >= 32) and the distance between its two accumulators
 };
 
 // Where the parts of the workspace begin, for a pass of NC columns of the activation math `act` over n_stages stages.
@@ -235,13 +236,12 @@ __device__ __forceinline__ void signal_peers(const TcParams& P, int lane, int* c
 }
 
 // Stages of raw activations a CTA that prepares its own keeps in flight (32 bytes per thread and stage for bf16, 64 for f32).
-constexpr int own_depth(bool x_bf16) { return x_bf16 ? 4 : 2; }  // per group of preparing warps; there are two groups
+constexpr int own_depth(bool x_bf16) { return x_bf16 ? 2 : 1; }  // per group of preparing warps; there are two groups
 constexpr int own_staging_bytes(bool x_bf16) { return 2 * own_depth(x_bf16) * 128 * (ks_of(kActS8) / 256) * 16 * (x_bf16 ? 2 : 4); }
 
 // ---- BF16 / FP8 / INT8: weights go from shared memory straight into the tensor core ------------------------------------
 constexpr int kDirectThreads = 192;   // warps 0-3 epilogue, warp 4 producers, warp 5 MMA issuer
 constexpr int kOwnThreads = 320;      // ... and warps 6-9, the second group that prepares activation blocks
-constexpr int kDBufColumns = 256;     // two accumulators, 256 TMEM columns apart
 
 // XMODE 0: activation blocks come prepared from the workspace (bulk copies). XMODE 1 / 2: up to 8 rows of bf16 / f32
 // activations, which the CTA's epilogue warps turn into blocks themselves, stage by stage, straight into the ring: no
@@ -249,7 +249,7 @@ constexpr int kDBufColumns = 256;     // two accumulators, 256 TMEM columns apar
 // PEERS: the epilogue stores into every rank's y and signals (the all-gather epilogue) instead of storing into P.y; its
 // own instantiations, so that the usual kernels carry none of it (their code size shows when kernels alternate).
 template <int F, int XMODE, bool PEERS>
-__global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_direct_kernel(const __grid_constant__ CUtensorMap wmap, const TcParams P) {
+__global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 2) tc_direct_kernel(const __grid_constant__ CUtensorMap wmap, const TcParams P) {
   using Fm = TcFmt<F>;
   constexpr int kAct = Fm::kAct, kKS = ks_of(kAct);
   constexpr bool kOwn = XMODE != 0, kXBF = XMODE == 1;
@@ -299,7 +299,7 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_di
     mbar_init_fence();
   }
   if (warp == 5) {
-    tmem_alloc(smem_u32(tmem_slot), kTmemColumns);
+    tmem_alloc(smem_u32(tmem_slot), P.tmem_cols);
     tmem_relinquish();
     tc_fence_before();
   }
@@ -359,7 +359,7 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_di
       bool ok = true;
       for (int tile = tile_begin; tile < tile_end && ok; ++tile) {
         const int t = tile - tile_begin, buf = t & 1;
-        const uint32_t d_tmem = tmem_base + buf * kDBufColumns;
+        const uint32_t d_tmem = tmem_base + buf * P.dstride;
         if (t >= 2) {  // the epilogue of the tile before last has read this accumulator
           if (!tc_wait(d_empty(buf), ((t >> 1) - 1) & 1, P.status)) break;
           tc_fence_after();
@@ -406,7 +406,7 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_di
         const RowTerms T = row_terms<F>(P, tile, r);
         if (!tc_wait(d_full(buf), (t >> 1) & 1, P.status)) break;
         tc_fence_after();
-        finish_tile<F, PEERS>(P, T, lane_addr + buf * kDBufColumns, lane, 0, 1, inv_lo, inv_hi, d_empty(buf));
+        finish_tile<F, PEERS>(P, T, lane_addr + buf * P.dstride, lane, 0, 1, inv_lo, inv_hi, d_empty(buf));
       }
       if constexpr (PEERS) signal_peers(P, lane, cta_count);  // (a CTA whose wait gave up still counts itself: nobody hangs, the status word tells)
     } else {
@@ -540,7 +540,7 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_di
         const RowTerms T = row_terms<F>(P, tile, r);
         if (!tc_wait(d_full(buf), (t >> 1) & 1, P.status)) return false;
         tc_fence_after();
-        finish_tile<F, PEERS>(P, T, lane_addr + buf * kDBufColumns, lane, 0, 1, inv, 0.0f, d_empty(buf));
+        finish_tile<F, PEERS>(P, T, lane_addr + buf * P.dstride, lane, 0, 1, inv, 0.0f, d_empty(buf));
         return true;
       };
       const int total = (tile_end - tile_begin) * n_stages;
@@ -608,7 +608,7 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 1) tc_di
     }
   }
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem_base, kTmemColumns);
+  if (warp == 5) tmem_dealloc(tmem_base, P.tmem_cols);
 }
 
 // ---- NVFP4: converter warps expand the stage into tensor memory ---------------------------------------------------------
@@ -797,6 +797,26 @@ __global__ void __launch_bounds__(kConvThreads, 1)
 }
 
 // ---- launching -------------------------------------------------------------------------------------------------------
+// LX_B200_TC_SMALL=1 lets products whose rings fit take small CTAs (two per SM); LX_B200_TC_SMALL_STAGES sets the fewest
+// weight stages a small CTA must keep (default 3). Off by default: measured on C2, a product between small neighbours
+// gains 5 % (the next product's first stages arrive while this one drains; it cannot start multiplying before this one
+// has finished, whose output its activations may be), but a stream that alternates small and large CTAs loses more
+// than that.
+bool small_ctas() {
+  static const bool on = [] {
+    const char* v = std::getenv("LX_B200_TC_SMALL");
+    return v && v[0] == '1';
+  }();
+  return on;
+}
+int small_min_stages() {
+  static const int n = [] {
+    const char* v = std::getenv("LX_B200_TC_SMALL_STAGES");
+    return v ? std::max(2, atoi(v)) : 3;
+  }();
+  return n;
+}
+
 // Rows per tile: the fewest whole tiles per SM that keep a tile within 128 rows, then the rows that spread N evenly
 // over that many tiles.
 int tile_rows(int N, int sms) {
@@ -815,15 +835,33 @@ int tc_launch(const lx_weight& w, TcParams P, cudaStream_t stream, int* grid_out
   P.box_bytes = (P.R + 7) / 8 * 1024;
   // NVFP4 keeps a stage's box and its block scales in a slot of twice the box, so that every box starts 1024-aligned.
   const int w_stage = F == LX_W_NVFP4 ? 2 * P.box_bytes : kBoxes * P.box_bytes;
-  constexpr int kBudget = 204 * 1024;  // leaves room for the 16 KB the tensor core may read past the last box
   constexpr int kStaging = XMODE == 0 ? 0 : own_staging_bytes(XMODE == 1);
-  P.SX = P.x_bytes > 24 * 1024 ? 2 : 3;
-  P.SW = std::min(12, (kBudget - P.SX * P.x_bytes - kStaging) / w_stage);
-  if (P.SW < 2) return kNotSupported;
-  // Tensor memory is taken whole (512 columns), so exactly one CTA may live on an SM: ask for more than half of its
-  // shared memory whatever the rings need.
-  const size_t smem =
-      std::max<size_t>(static_cast<size_t>(P.SW) * w_stage + std::max(P.SX * P.x_bytes + kStaging, 16 * 1024) + 1024, 120 * 1024);
+  // Two sizes of CTA. Small: at most half of an SM's shared memory and tensor memory, so that the CTAs of the NEXT kernel
+  // in the stream (launched programmatically, their weights static) move in beside this kernel's and fill their rings
+  // while these drain: the weight stream never stops between products. Measured on plain tile copies of a 58 MB weight,
+  // back to back: 12.7 us per pass with one CTA per SM and no overlap, 8.2 us with the next kernel's CTAs resident.
+  // Large (one CTA per SM, deeper rings): for activation blocks that leave a small CTA fewer than two weight stages,
+  // or more than 256 accumulator columns.
+  constexpr int kSmall = 113 * 1024 - 512, kLarge = 204 * 1024;  // large: room for the 16 KB the tensor core may read past the last box
+  constexpr int kBars = 1024;
+  P.dstride = P.NC;
+  P.tmem_cols = 32;
+  while (P.tmem_cols < 2 * P.NC) P.tmem_cols *= 2;
+  const int small_sw = small_ctas() && F != LX_W_NVFP4 && P.tmem_cols <= 256 ? (kSmall - kBars - std::max(2 * P.x_bytes + kStaging, 16 * 1024)) / w_stage : 0;
+  const bool small = small_sw >= small_min_stages();
+  size_t smem;
+  if (small) {
+    P.SX = 2;
+    P.SW = std::min(12, small_sw);
+    smem = static_cast<size_t>(P.SW) * w_stage + std::max(P.SX * P.x_bytes + kStaging, 16 * 1024) + kBars;
+  } else {
+    P.SX = P.x_bytes > 24 * 1024 ? 2 : 3;
+    P.SW = std::min(12, (kLarge - P.SX * P.x_bytes - kStaging) / w_stage);
+    if (P.SW < 2) return kNotSupported;
+    P.tmem_cols = kTmemColumns, P.dstride = 256;
+    // all of tensor memory: exactly one CTA may live on an SM, so ask for more than half of its shared memory
+    smem = std::max<size_t>(static_cast<size_t>(P.SW) * w_stage + std::max(P.SX * P.x_bytes + kStaging, 16 * 1024) + kBars, 120 * 1024);
+  }
   alignas(64) CUtensorMap wmap, smap;
   memset(&wmap, 0, sizeof(wmap));
   memset(&smap, 0, sizeof(smap));

@@ -322,6 +322,8 @@ int allow_big_smem(Kernel kernel) {
   std::lock_guard<std::mutex> lock(mu);
   if (!done[dev]) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) != cudaSuccess) return static_cast<int>(cudaGetLastError());
+    // all of the SM's L1 as shared memory, so that two CTAs of half an SM each fit side by side
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess) return static_cast<int>(cudaGetLastError());
     done[dev] = true;
   }
   return kOk;
