@@ -213,7 +213,12 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     metric = "decode matmul effective HBM TB/s"
     config = {"workload": desc, "rotation": "weight copies >= 1 GiB between reuses (inputs larger than L2)",
-              "parallelism": f"rows of W split over {world} GPU(s), all-gather of y" if world > 1 else "single GPU"}
+              "parallelism": "single GPU"}
+    if world > 1:
+        if os.environ.get("LX_BENCH_SCALING", "weak") == "strong":
+            config["parallelism"] = f"the configuration's {N} rows of W split over {world} GPUs, all-gather of y"
+        else:
+            config["parallelism"] = f"{world} x {N} rows of W, {N} per GPU (the configuration's size on every GPU), all-gather of y"
 
     if args.impl == "reference":
         if rank != 0:
@@ -242,12 +247,16 @@ def main():
     lib = abi.Library()  # raises when the CUDA library is missing: there is no other path
     dev = torch.device("cuda", local)
 
-    # ---- synthetic weights: the same seeded matrix on every rank, each rank keeps its rows ----
-    n0, n1 = host.shard_rows(N, rank, world)
-    gen = torch.Generator(device=dev).manual_seed(0)
-    w_full = (torch.randn((N, K), generator=gen, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
-    w_shard = w_full[n0:n1].contiguous()
-    del w_full
+    # ---- synthetic weights: each rank draws the rows it keeps ----
+    # Weak scaling (default): the matrix grows with the job, world x N rows, so every GPU streams a shard of the
+    # configuration's own size (a model world times wider on world GPUs); LX_BENCH_SCALING=strong splits the
+    # configuration's N rows instead (29 MB per GPU at two GPUs: fixed costs, not bytes).
+    strong = world > 1 and os.environ.get("LX_BENCH_SCALING", "weak") == "strong"
+    N_job = N if strong or world == 1 else N * world
+    n0, n1 = host.shard_rows(N_job, rank, world)
+    gen = torch.Generator(device=dev).manual_seed(rank)
+    w_shard = (torch.randn((n1 - n0, K), generator=gen, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    gen.manual_seed(0)  # the activations are the same on every rank
     first = host.store_weight(lib, w_shard, wtype)
     shard_bytes = first.nbytes()
     copies = max(3, -(-ROTATE_BYTES // (shard_bytes * len(Ms))) * len(Ms))
@@ -272,7 +281,7 @@ def main():
     fused = None
     if world > 1 and os.environ.get("LX_BENCH_FUSED", "0") == "1":
         try:
-            fused = [host.FusedShardedLinear(lib, None, wtype, N, K, max(Ms), stored=sw) for sw in stored]
+            fused = [host.FusedShardedLinear(lib, None, wtype, N_job, K, max(Ms), stored=sw) for sw in stored]
             for M in Ms:
                 fused[0](xs[M])
             torch.cuda.synchronize()
@@ -452,7 +461,7 @@ def main():
         leave()
         return
     out = {"metric": metric, "value": value, "unit": "TB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-           "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+           "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if strong else "weak",
            "vs_baseline": None, "dtype": DTYPE[wtype], "data": "synthetic", "config": config, "roofline": roofline, "e2e": e2e,
            "gpu_launches": int(launches), "launch": "CUDA graphs" if use_graphs else "eager", "clocks": clocks.summary(), "pct_of_8TBs": value / 8.0 / max(world, 1),
            "kernel_status": status}

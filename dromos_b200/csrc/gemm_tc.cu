@@ -236,8 +236,8 @@ __device__ __forceinline__ void signal_peers(const TcParams& P, int lane, int* c
 }
 
 // Stages of raw activations a CTA that prepares its own keeps in flight (32 bytes per thread and stage for bf16, 64 for f32).
-constexpr int own_depth(bool x_bf16) { return x_bf16 ? 2 : 1; }  // per group of preparing warps; there are two groups
-constexpr int own_staging_bytes(bool x_bf16) { return 2 * own_depth(x_bf16) * 128 * (ks_of(kActS8) / 256) * 16 * (x_bf16 ? 2 : 4); }
+constexpr int own_depth(bool x_bf16) { return x_bf16 ? 1 : 1; }  // iterations (of two stages) per group of preparing warps; there are two groups
+constexpr int own_staging_bytes(bool x_bf16) { return 2 * own_depth(x_bf16) * 2 * 128 * 16 * (x_bf16 ? 2 : 4); }  // groups x depth x stages per iteration x threads x unit
 
 // ---- BF16 / FP8 / INT8: weights go from shared memory straight into the tensor core ------------------------------------
 constexpr int kDirectThreads = 192;   // warps 0-3 epilogue, warp 4 producers, warp 5 MMA issuer
@@ -249,7 +249,7 @@ constexpr int kOwnThreads = 320;      // ... and warps 6-9, the second group tha
 // PEERS: the epilogue stores into every rank's y and signals (the all-gather epilogue) instead of storing into P.y; its
 // own instantiations, so that the usual kernels carry none of it (their code size shows when kernels alternate).
 template <int F, int XMODE, bool PEERS>
-__global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 2) tc_direct_kernel(const __grid_constant__ CUtensorMap wmap, const TcParams P) {
+__global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, XMODE ? 1 : 2) tc_direct_kernel(const __grid_constant__ CUtensorMap wmap, const TcParams P) {
   using Fm = TcFmt<F>;
   constexpr int kAct = Fm::kAct, kKS = ks_of(kAct);
   constexpr bool kOwn = XMODE != 0, kXBF = XMODE == 1;
@@ -267,7 +267,7 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 2) tc_di
   auto w_full = [&](int s) { return bar0 + 8u * s; };                     // weight stage landed
   auto w_empty = [&](int s) { return bar0 + 8u * (SW + s); };             // its products are done
   auto x_full = [&](int s) { return bar0 + 8u * (2 * SW + s); };          // activation block landed
-  auto x_empty = [&](int s) { return bar0 + 8u * (2 * SW + SX + s); };    // its products are done
+  auto x_empty = [&](int s) { return SW == SX ? w_empty(s) : bar0 + 8u * (2 * SW + SX + s); };  // its products are done (rings of one depth share the weights' barrier)
   auto d_full = [&](int b) { return bar0 + 8u * (2 * SW + 2 * SX + b); };       // accumulator b is complete
   auto d_empty = [&](int b) { return bar0 + 8u * (2 * SW + 2 * SX + 2 + b); };  // accumulator b has been read
   const uint32_t group_bar = bar0 + 8u * (2 * SW + 2 * SX + 4);           // the epilogue warps meet here
@@ -355,6 +355,13 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 2) tc_di
       const uint32_t idesc = (cfmt << 4) | (abfmt << 7) | (abfmt << 10) | (static_cast<uint32_t>(NC >> 3) << 17) |
                              (static_cast<uint32_t>(kBM >> 4) << 24);
       const uint32_t lbo = static_cast<uint32_t>(NC / 8) * 128, sbo = 128;
+      // the descriptors' halves (smem_desc_sw128 / smem_desc): the high words never change, the low words carry the address
+      const uint32_t a_hi = (1024u >> 4) | (1u << 14) | (2u << 29), b_hi = (sbo >> 4) | (1u << 14);
+      const uint32_t a_lo0 = ((smem_u32(smem) & 0x3ffffu) >> 4) | (1u << 16);
+      const uint32_t b_lo0 = ((smem_u32(xring) & 0x3ffffu) >> 4) | ((lbo >> 4) << 16);
+      const uint32_t w_stage16 = static_cast<uint32_t>(w_stage) >> 4, x_bytes16 = static_cast<uint32_t>(x_bytes) >> 4;
+      const uint32_t box16 = static_cast<uint32_t>(box_bytes) >> 4, b_step = (2u * lbo) >> 4;
+      const bool one_ring = SW == SX;  // one barrier per stage frees both the weights and the activation block
       Ring w, x;
       bool ok = true;
       for (int tile = tile_begin; tile < tile_end && ok; ++tile) {
@@ -370,20 +377,18 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 2) tc_di
             break;
           }
           tc_fence_after();
-          const uint32_t wb = smem_u32(smem) + static_cast<uint32_t>(w.slot) * w_stage;
-          const uint32_t xb = smem_u32(xring) + static_cast<uint32_t>(x.slot) * x_bytes;
+          const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(w.slot) * w_stage16;
+          const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(x.slot) * x_bytes16;
 #pragma unroll
           for (int b = 0; b < kBoxes; ++b) {
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
               const int c = b * 4 + ks;  // 32 bytes of K per instruction
-              const uint64_t adesc = smem_desc_sw128(wb + b * box_bytes + ks * 32);
-              const uint64_t bdesc = smem_desc(xb + static_cast<uint32_t>(2 * c) * lbo, lbo, sbo);
-              umma_ss<kAct>(d_tmem, adesc, bdesc, idesc, (s | c) ? 1u : 0u);
+              umma_ss_halves<kAct>(d_tmem, a_lo + b * box16 + ks * 2, a_hi, b_lo + c * b_step, b_hi, idesc, c ? 1u : (s ? 1u : 0u));
             }
           }
           umma_commit(w_empty(w.slot));
-          umma_commit(x_empty(x.slot));
+          if (!one_ring) umma_commit(x_empty(x.slot));
           w.advance(SW);
           x.advance(SX);
         }
@@ -413,11 +418,60 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 2) tc_di
       static_assert(act_elem(kAct) == 1, "CTAs prepare their own activations for the 8-bit maths only");
       constexpr int V = 16;
       constexpr int kPiece = kXBF ? 8 : 4;  // activations per 16 bytes
-      constexpr int kQ = kKS / 256;  // 16-value units of a row per thread and stage (16 threads share a row's stage)
       constexpr int kUnitBytes = V * (kXBF ? 2 : 4);
       constexpr int D = own_depth(kXBF);
       const bool aligned16 = (reinterpret_cast<uintptr_t>(P.x) & 15) == 0 && P.ld_x % kPiece == 0;
       bool ok = true;
+      // Thread (m = gtid % 8, kg = gtid / 8) owns, in each of its group's stages, the 16 values k = 16 kg .. 16 kg + 15
+      // of activation row m: 16 bytes of each plane. Its raw activations travel from global memory into a private piece
+      // of shared memory with cp.async, D iterations ahead. A group takes two consecutive stages per iteration (group 0:
+      // stages 0, 1, 4, 5, ...; group 1: 2, 3, 6, 7, ...): the fixed cost of an iteration (about a microsecond of waits,
+      // proxy fence and arrivals, measured) is paid once for both.
+      constexpr int B = 2;
+      const int m = gtid & 7, kg = gtid >> 3;
+      const bool row_live = m < P.M;
+      const uint8_t* xrow = static_cast<const uint8_t*>(P.x) + static_cast<int64_t>(m) * P.ld_x * (kXBF ? 2 : 4);
+      uint8_t* const staging = xring + static_cast<size_t>(SX) * x_bytes + static_cast<size_t>(group) * D * B * 128 * kUnitBytes;
+      const int row_bytes = P.K * (kXBF ? 2 : 4);
+      // stage s of a tile (or nothing, s < 0) into piece b of staging slot d
+      auto fetch = [&](int s, int d, int b) {
+        if (!row_live || s < 0) return;
+        uint8_t* dst = staging + ((static_cast<size_t>(d) * B + b) * 128 + gtid) * kUnitBytes;
+        const int k0 = s * kKS + kg * V;
+        const int at = k0 * (kXBF ? 2 : 4);  // byte offset of the unit in its row
+        if (aligned16) {
+#pragma unroll
+          for (int q = 0; q < kUnitBytes / 16; ++q) {
+            const int left = min(16, max(0, row_bytes - (at + 16 * q)));  // bytes of the row in this piece; the rest reads as zero
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst + 16 * q)), "l"(xrow + (left ? at + 16 * q : 0)),
+                         "r"(left)
+                         : "memory");
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            if constexpr (kXBF) reinterpret_cast<uint16_t*>(dst)[i] = k0 + i < P.K ? reinterpret_cast<const uint16_t*>(xrow)[k0 + i] : uint16_t(0);
+            else reinterpret_cast<float*>(dst)[i] = k0 + i < P.K ? reinterpret_cast<const float*>(xrow)[k0 + i] : 0.0f;
+          }
+        }
+      };
+      const int total = (tile_end - tile_begin) * n_stages;
+      // The next stages to fetch: CTA stage ahead_i (and ahead_i + 1), which is stage ahead_s of its tile.
+      int ahead_i = B * group, ahead_s = (B * group) % n_stages;
+      auto issue = [&](int d) {  // always one cp.async group
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+          int sb = ahead_s + b;
+          if (sb >= n_stages) sb -= n_stages;
+          fetch(ahead_i + b < total ? sb : -1, d, b);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        ahead_i += 2 * B;
+        ahead_s += 2 * B;
+        while (ahead_s >= n_stages) ahead_s -= n_stages;
+      };
+      // the first fetches go out before the row maxima are known: they do not depend on them
+      for (int d = 0; d < D; ++d) issue(d);
       // ---- first pass: the largest magnitude of every row, by all 256 preparing threads ----
       {
         const int t256 = group * 128 + gtid;
@@ -473,48 +527,13 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 2) tc_di
         for (int w8 = 0; w8 < 8; ++w8) v = fmaxf(v, row_scale[w8 * 8 + row]);
         return scale_of<kAct>(v);
       };
-      // ---- second pass: the digits, stage by stage into the ring ----
-      // Thread (m = gtid % 8, kg = gtid / 8) owns, in each of its group's stages, the 16 values k = 16 kg .. 16 kg + 15
-      // of activation row m: 16 bytes of each plane. Its raw activations travel from global memory into a private piece
-      // of shared memory with cp.async, D of the group's stages ahead.
-      const int m = gtid & 7, kg = gtid >> 3;
-      const bool row_live = m < P.M;
+      // ---- second pass: the digits, two stages per iteration into the ring ----
       const float sc = row_live ? row_scale_of(m) : 1.0f;
       const float inv = lane < P.M ? 1.0f / row_scale_of(lane) : 0.0f;  // lane l: row l (finish_tile's layout)
-      const uint8_t* xrow = static_cast<const uint8_t*>(P.x) + static_cast<int64_t>(m) * P.ld_x * (kXBF ? 2 : 4);
-      uint8_t* const staging = xring + static_cast<size_t>(SX) * x_bytes + static_cast<size_t>(group) * D * 128 * kQ * kUnitBytes;
-      const int row_bytes = P.K * (kXBF ? 2 : 4);
-      // stage s of a tile (or nothing, s < 0) into staging slot d; always one cp.async group
-      auto issue = [&](int s, int d) {
-        if (row_live && s >= 0) {
-#pragma unroll
-          for (int u = 0; u < kQ; ++u) {
-            uint8_t* dst = staging + ((static_cast<size_t>(d) * kQ + u) * 128 + gtid) * kUnitBytes;
-            const int k0 = s * kKS + (kg + 16 * u) * V;
-            const int at = k0 * (kXBF ? 2 : 4);  // byte offset of the unit in its row
-            if (aligned16) {
-#pragma unroll
-              for (int q = 0; q < kUnitBytes / 16; ++q) {
-                const int left = min(16, max(0, row_bytes - (at + 16 * q)));  // bytes of the row in this piece; the rest reads as zero
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst + 16 * q)), "l"(xrow + (left ? at + 16 * q : 0)),
-                             "r"(left)
-                             : "memory");
-              }
-            } else {
-#pragma unroll
-              for (int i = 0; i < V; ++i) {
-                if constexpr (kXBF) reinterpret_cast<uint16_t*>(dst)[i] = k0 + i < P.K ? reinterpret_cast<const uint16_t*>(xrow)[k0 + i] : uint16_t(0);
-                else reinterpret_cast<float*>(dst)[i] = k0 + i < P.K ? reinterpret_cast<const float*>(xrow)[k0 + i] : 0.0f;
-              }
-            }
-          }
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-      };
-      // unit u of staging slot d as f32 (after wait_landed)
       auto wait_landed = [&]() { asm volatile("cp.async.wait_group %0;" ::"n"(D - 1) : "memory"); };
-      auto take = [&](int d, int u, float (&v)[V]) {
-        const uint8_t* src = staging + ((static_cast<size_t>(d) * kQ + u) * 128 + gtid) * kUnitBytes;
+      // piece b of staging slot d as f32 (after wait_landed)
+      auto take = [&](int d, int b, float (&v)[V]) {
+        const uint8_t* src = staging + ((static_cast<size_t>(d) * B + b) * 128 + gtid) * kUnitBytes;
         if constexpr (kXBF) {
 #pragma unroll
           for (int q = 0; q < 2; ++q) {
@@ -543,62 +562,59 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, 2) tc_di
         finish_tile<F, PEERS>(P, T, lane_addr + buf * P.dstride, lane, 0, 1, inv, 0.0f, d_empty(buf));
         return true;
       };
-      const int total = (tile_end - tile_begin) * n_stages;
-      // This group's stages are i = group, group + 2, ...; stage i of the CTA is stage i % n_stages of tile i / n_stages.
-      auto step2 = [&](int& s_in_tile, int& tile_of) {  // two stages on
-        s_in_tile += 2;
-        while (s_in_tile >= n_stages) s_in_tile -= n_stages, ++tile_of;
-      };
-      int ahead_i = group, ahead_s = group, ahead_tile = 0;  // the next stage to fetch
-      while (ahead_s >= n_stages) ahead_s -= n_stages;
-      for (int d = 0; d < D; ++d) {
-        issue(ahead_i < total ? ahead_s : -1, d);
-        ahead_i += 2;
-        step2(ahead_s, ahead_tile);
-      }
-      Ring x;
-      if (group) x.advance(SX);
-      int d = 0, tile = tile_begin, s = group;
+      Ring x[B];
+#pragma unroll
+      for (int b = 0; b < B; ++b)
+        for (int a = 0; a < B * group + b; ++a) x[b].advance(SX);
+      int d = 0, tile = tile_begin, s = B * group;  // the iteration's first stage: stage s of `tile`
       while (s >= n_stages) s -= n_stages, ++tile;
-      for (int i = group; i < total && ok; i += 2) {
+      for (int i = B * group; i < total && ok; i += 2 * B) {
         if (group == 0) {
-          // The products of this stage's tile need the accumulator of the tile two before it: that one must have been
-          // read by now. The one before, as soon as it happens to be complete.
-          while (ok && next_finish <= tile - 2) ok = finish(next_finish++);
+          // The products of a stage's tile need the accumulator of the tile two before it: that one must have been
+          // read by now (the iteration's second stage may already belong to the next tile). The one before, as soon as
+          // it happens to be complete.
+          const int tile_hi = s + 1 >= n_stages ? tile + 1 : tile;
+          while (ok && next_finish <= tile_hi - 2) ok = finish(next_finish++);
           if (ok && next_finish < tile && mbar_try_wait(d_full((next_finish - tile_begin) & 1), ((next_finish - tile_begin) >> 1) & 1))
             ok = finish(next_finish++);
           if (!ok) break;
         }
-        wait_landed();  // the oldest group in flight, this stage's
-        uint32_t w[kQ][3][4];
+        wait_landed();  // the oldest group in flight, this iteration's
+        uint32_t w[B][3][4];
 #pragma unroll
-        for (int u = 0; u < kQ; ++u) {
+        for (int b = 0; b < B; ++b) {
           float v[V];
-          take(d, u, v);
-          make_planes<kAct, kXBF, V>(v, sc, w[u]);
+          take(d, b, v);
+          make_planes<kAct, kXBF, V>(v, sc, w[b]);
         }
-        issue(ahead_i < total ? ahead_s : -1, d);
-        ahead_i += 2;
-        step2(ahead_s, ahead_tile);
+        issue(d);
         if (++d == D) d = 0;
-        if (i >= SX && !tc_wait(x_empty(x.slot), x.lap ^ 1u, P.status)) {
-          ok = false;
-          break;
-        }
-        uint8_t* block = xring + static_cast<size_t>(x.slot) * x_bytes;
-        if (row_live) {
 #pragma unroll
-          for (int u = 0; u < kQ; ++u)
-            for (int j = 0; j < P.planes; ++j)
-              *reinterpret_cast<uint4*>(block + block_offset(NC, (kg + 16 * u) * 16, j * P.Mp + m)) =
-                  make_uint4(w[u][j][0], w[u][j][1], w[u][j][2], w[u][j][3]);
+        for (int b = 0; b < B; ++b) {
+          if (i + b >= total) break;
+          if (i + b >= SX && !tc_wait(x_empty(x[b].slot), x[b].lap ^ 1u, P.status)) {
+            ok = false;
+            break;
+          }
+          uint8_t* block = xring + static_cast<size_t>(x[b].slot) * x_bytes;
+          if (row_live) {
+#pragma unroll
+            for (int j = 0; j < 3; ++j)
+              if (j < P.planes)
+                *reinterpret_cast<uint4*>(block + block_offset(NC, kg * 16, j * P.Mp + m)) = make_uint4(w[b][j][0], w[b][j][1], w[b][j][2], w[b][j][3]);
+          }
         }
+        if (!ok) break;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads what these threads wrote
         __syncwarp();
-        if (lane == 0) mbar_arrive(x_full(x.slot));
-        x.advance(SX);
-        x.advance(SX);
-        step2(s, tile);
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+          if (lane == 0 && i + b < total) mbar_arrive(x_full(x[b].slot));
+#pragma unroll
+          for (int a = 0; a < 2 * B; ++a) x[b].advance(SX);
+        }
+        s += 2 * B;
+        while (s >= n_stages) s -= n_stages, ++tile;
       }
       asm volatile("cp.async.wait_group 0;" ::: "memory");
       if (group == 0) {
@@ -855,8 +871,13 @@ int tc_launch(const lx_weight& w, TcParams P, cudaStream_t stream, int* grid_out
     P.SW = std::min(12, small_sw);
     smem = static_cast<size_t>(P.SW) * w_stage + std::max(P.SX * P.x_bytes + kStaging, 16 * 1024) + kBars;
   } else {
-    P.SX = P.x_bytes > 24 * 1024 ? 2 : 3;
-    P.SW = std::min(12, (kLarge - P.SX * P.x_bytes - kStaging) / w_stage);
+    if (XMODE) {
+      // CTAs that prepare their own (small) activation blocks keep one ring: a block per weight stage, one barrier for both
+      P.SW = P.SX = std::min(12, (kLarge - kStaging) / (w_stage + P.x_bytes));
+    } else {
+      P.SX = P.x_bytes > 24 * 1024 ? 2 : 3;
+      P.SW = std::min(12, (kLarge - P.SX * P.x_bytes - kStaging) / w_stage);
+    }
     if (P.SW < 2) return kNotSupported;
     P.tmem_cols = kTmemColumns, P.dstride = 256;
     // all of tensor memory: exactly one CTA may live on an SM, so ask for more than half of its shared memory

@@ -108,6 +108,32 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       : "memory");
 }
 // The mbarrier gets one arrival when every tcgen05.mma issued so far by this thread has completed.
+// The same with the two descriptors given as 32-bit halves: the issuing thread is one thread whose own instruction
+// stream bounds a stage (measured: ~1200 cycles per stage of eight products), so the 64-bit descriptor arithmetic is
+// kept out of it; per product the low words move by a constant.
+template <int kAct>
+__device__ __forceinline__ void umma_ss_halves(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                               uint32_t accumulate) {
+  if constexpr (kAct == kActE4m3) {
+    asm volatile(
+        "{ .reg .pred p; .reg .b64 da, db; setp.ne.u32 p, %6, 0; mov.b64 da, {%1, %2}; mov.b64 db, {%3, %4};\n"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %5, p; }" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else if constexpr (kAct == kActS8) {
+    asm volatile(
+        "{ .reg .pred p; .reg .b64 da, db; setp.ne.u32 p, %6, 0; mov.b64 da, {%1, %2}; mov.b64 db, {%3, %4};\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p; }" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{ .reg .pred p; .reg .b64 da, db; setp.ne.u32 p, %6, 0; mov.b64 da, {%1, %2}; mov.b64 db, {%3, %4};\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p; }" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
