@@ -266,7 +266,10 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, XMODE ? 
   const uint32_t bar0 = smem_u32(bars);
   auto w_full = [&](int s) { return bar0 + 8u * s; };                     // weight stage landed
   auto w_empty = [&](int s) { return bar0 + 8u * (SW + s); };             // its products are done
-  auto x_full = [&](int s) { return bar0 + 8u * (2 * SW + s); };          // activation block landed
+  // CTAs that prepare their own blocks into a ring of the weights' depth count them on the weights' barrier: the issuer
+  // waits once per stage
+  const bool one_full = kOwn && SW == SX;
+  auto x_full = [&](int s) { return one_full ? w_full(s) : bar0 + 8u * (2 * SW + s); };  // activation block landed
   auto x_empty = [&](int s) { return SW == SX ? w_empty(s) : bar0 + 8u * (2 * SW + SX + s); };  // its products are done (rings of one depth share the weights' barrier)
   auto d_full = [&](int b) { return bar0 + 8u * (2 * SW + 2 * SX + b); };       // accumulator b is complete
   auto d_empty = [&](int b) { return bar0 + 8u * (2 * SW + 2 * SX + 2 + b); };  // accumulator b has been read
@@ -283,12 +286,12 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, XMODE ? 
 
   if (tid == 0) {
     for (int s = 0; s < SW; ++s) {
-      mbar_init(w_full(s), 1);
+      mbar_init(w_full(s), one_full ? 5 : 1);  // the tile copies' bytes (and the four preparing warps)
       mbar_init(w_empty(s), 1);
     }
     for (int s = 0; s < SX; ++s) {
-      mbar_init(x_full(s), kOwn ? 4 : 1);  // the four preparing warps, or the bulk copy's bytes
-      mbar_init(x_empty(s), 1);
+      if (!one_full) mbar_init(x_full(s), kOwn ? 4 : 1);  // the four preparing warps, or the bulk copy's bytes
+      if (SW != SX) mbar_init(x_empty(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(d_full(b), 1);
@@ -372,7 +375,7 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, XMODE ? 
           tc_fence_after();
         }
         for (int s = 0; s < n_stages; ++s) {
-          if (!tc_wait(w_full(w.slot), w.lap, P.status) || !tc_wait(x_full(x.slot), x.lap, P.status)) {
+          if (!tc_wait(w_full(w.slot), w.lap, P.status) || (!one_full && !tc_wait(x_full(x.slot), x.lap, P.status))) {
             ok = false;
             break;
           }
@@ -874,6 +877,8 @@ int tc_launch(const lx_weight& w, TcParams P, cudaStream_t stream, int* grid_out
     if (XMODE) {
       // CTAs that prepare their own (small) activation blocks keep one ring: a block per weight stage, one barrier for both
       P.SW = P.SX = std::min(12, (kLarge - kStaging) / (w_stage + P.x_bytes));
+    } else if (F != LX_W_NVFP4 && kLarge / (w_stage + P.x_bytes) >= 4) {
+      P.SW = P.SX = std::min(12, kLarge / (w_stage + P.x_bytes));  // one ring again: one commit per stage
     } else {
       P.SX = P.x_bytes > 24 * 1024 ? 2 : 3;
       P.SW = std::min(12, (kLarge - P.SX * P.x_bytes - kStaging) / w_stage);

@@ -23,17 +23,11 @@ constexpr int kMaxExperts = 1024;
 constexpr int kMaxTopK = 32;
 
 // ---- routing (one warp per token) ------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) route_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
-                                                    int32_t* __restrict__ ids, float* __restrict__ weights,
-                                                    float* __restrict__ entropy, float* __restrict__ confidence, int T,
-                                                    int E, int top_k) {
-  pdl_trigger();
-  pdl_wait();
-  const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (t >= T) return;
-  const int lane = threadIdx.x & 31;
-  const float* row = logits + static_cast<int64_t>(t) * E;
-  // softmax statistics of the whole row
+// One warp routes one row of logits (global or shared memory): softmax statistics of the whole row, top_k picks by
+// logit + bias (descending, ties to the lower index), weights = softmax over the picks of their unbiased logits.
+// picks: top_k ints of shared memory private to the warp.
+__device__ __forceinline__ void route_row(const float* row, const float* __restrict__ bias, int E, int top_k, int lane, int* picks,
+                                          int32_t* __restrict__ ids, float* __restrict__ weights, float* entropy, float* confidence) {
   float m = -INFINITY;
   for (int i = lane; i < E; i += 32) m = fmaxf(m, row[i]);
   m = warp_max(m);
@@ -47,12 +41,10 @@ __global__ void __launch_bounds__(256) route_kernel(const float* __restrict__ lo
   }
   h = warp_sum(h);
   if (lane == 0) {
-    if (entropy) entropy[t] = h;
-    if (confidence) confidence[t] = 1.0f / z;
+    if (entropy) *entropy = h;
+    if (confidence) *confidence = 1.0f / z;
   }
-  // top_k by logit + bias, descending, ties to the lower index: top_k rounds of a warp arg-max over what is left
-  __shared__ int picks[8][32];
-  int* mine_picks = picks[threadIdx.x >> 5];
+  // top_k rounds of a warp arg-max over what is left
   int mine = -1;  // lane j keeps pick j
   float mine_logit = -INFINITY;
   for (int r = 0; r < top_k; ++r) {
@@ -60,7 +52,7 @@ __global__ void __launch_bounds__(256) route_kernel(const float* __restrict__ lo
     int best_i = E;
     for (int i = lane; i < E; i += 32) {
       bool taken = false;
-      for (int j = 0; j < r; ++j) taken |= mine_picks[j] == i;
+      for (int j = 0; j < r; ++j) taken |= picks[j] == i;
       if (taken) continue;
       const float v = row[i] + (bias ? bias[i] : 0.0f);
       if (v > best || (v == best && i < best_i)) best = v, best_i = i;
@@ -72,18 +64,99 @@ __global__ void __launch_bounds__(256) route_kernel(const float* __restrict__ lo
       if (ov > best || (ov == best && oi < best_i)) best = ov, best_i = oi;
     }
     if (lane == r) mine = best_i, mine_logit = best_i < E ? row[best_i] : -INFINITY;
-    if (lane == 0) mine_picks[r] = best_i;
+    if (lane == 0) picks[r] = best_i;
     __syncwarp();
   }
-  // weights: softmax over the picks of their unbiased logits
   const bool live = lane < top_k && mine >= 0 && mine < E;
   const float lmax = warp_max(live ? mine_logit : -INFINITY);
   const float ex = live ? expf(mine_logit - lmax) : 0.0f;
   const float sum = warp_sum(ex);
   if (lane < top_k) {
-    ids[static_cast<int64_t>(t) * top_k + lane] = live ? mine : 0;
-    weights[static_cast<int64_t>(t) * top_k + lane] = live ? ex / sum : 0.0f;
+    ids[lane] = live ? mine : 0;
+    weights[lane] = live ? ex / sum : 0.0f;
   }
+}
+
+__global__ void __launch_bounds__(256) route_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                                    int32_t* __restrict__ ids, float* __restrict__ weights,
+                                                    float* __restrict__ entropy, float* __restrict__ confidence, int T,
+                                                    int E, int top_k) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (t >= T) return;
+  __shared__ int picks[8][32];
+  route_row(logits + static_cast<int64_t>(t) * E, bias, E, top_k, threadIdx.x & 31, picks[threadIdx.x >> 5],
+            ids + static_cast<int64_t>(t) * top_k, weights + static_cast<int64_t>(t) * top_k, entropy ? entropy + t : nullptr,
+            confidence ? confidence + t : nullptr);
+}
+
+// ---- the router of a decode-sized step in one launch (lx_router_route) ---------------------------------------------
+// logits[m, e] = x[m, :] . w[e, :] + bias[e] for up to 8 rows, then the routing of route_row on those logits. One warp
+// per expert: its lanes walk K in float4 steps, every row's partial in registers, a fixed shuffle tree, so a logit's
+// bits depend on K only. The router weights are static and are in flight before the dependency wait. The block that
+// counts itself last on the ticket (which it leaves at zero again) stages the logits in shared memory and routes
+// them, one warp per row, with the arithmetic of lx_moe_route: every routing output equals that call on these logits
+// bit for bit.
+constexpr int kRouterRows = 8, kRouterMaxE = 1024, kRouterMaxK = 2048;
+__global__ void __launch_bounds__(256) router_kernel(const float* __restrict__ x, int ld_x, const float* __restrict__ w,
+                                                     const float* __restrict__ bias, float* __restrict__ logits,
+                                                     const float* __restrict__ selection_bias, int32_t* __restrict__ ids,
+                                                     float* __restrict__ weights, float* __restrict__ entropy,
+                                                     float* __restrict__ confidence, int32_t* __restrict__ ticket, int M, int E, int K,
+                                                     int top_k) {
+  pdl_trigger();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int e = blockIdx.x * 8 + warp;
+  const bool vec = K % 4 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && ld_x % 4 == 0;
+  // this lane's weights of the expert's row: K <= 2048 is at most 16 float4 steps of the warp
+  float4 wv[kRouterMaxK / 128];
+  const float* wrow = w + static_cast<int64_t>(e < E ? e : 0) * K;
+#pragma unroll
+  for (int q = 0; q < kRouterMaxK / 128; ++q) {
+    const int k = (q * 32 + lane) * 4;
+    wv[q] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (k < K) {
+      if (vec) wv[q] = __ldg(reinterpret_cast<const float4*>(wrow + k));
+      else wv[q] = make_float4(wrow[k], k + 1 < K ? wrow[k + 1] : 0.0f, k + 2 < K ? wrow[k + 2] : 0.0f, k + 3 < K ? wrow[k + 3] : 0.0f);
+    }
+  }
+  const float be = bias && e < E ? bias[e] : 0.0f;
+  pdl_wait();  // the activations come from the kernel before this one
+  for (int m = 0; m < M; ++m) {
+    const float* xr = x + static_cast<int64_t>(m) * ld_x;
+    float acc = 0.0f;
+#pragma unroll
+    for (int q = 0; q < kRouterMaxK / 128; ++q) {
+      const int k = (q * 32 + lane) * 4;
+      if (k >= K) continue;
+      float4 xv;
+      if (vec) xv = *reinterpret_cast<const float4*>(xr + k);
+      else xv = make_float4(xr[k], k + 1 < K ? xr[k + 1] : 0.0f, k + 2 < K ? xr[k + 2] : 0.0f, k + 3 < K ? xr[k + 3] : 0.0f);
+      acc = fmaf(xv.x, wv[q].x, acc);
+      acc = fmaf(xv.y, wv[q].y, acc);
+      acc = fmaf(xv.z, wv[q].z, acc);
+      acc = fmaf(xv.w, wv[q].w, acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0 && e < E) logits[static_cast<int64_t>(m) * E + e] = acc + be;
+  }
+  // publish this block's logits, then count it; the block that counts last routes every row
+  __shared__ int last;
+  __shared__ float rows[kRouterRows][kRouterMaxE];
+  __shared__ int picks[kRouterRows][32];
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) last = atomicAdd(ticket, 1) == static_cast<int>(gridDim.x) - 1;
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  if (threadIdx.x == 0) *ticket = 0;
+  for (int i = threadIdx.x; i < M * E; i += 256) rows[i / E][i % E] = __ldcg(logits + i);
+  __syncthreads();
+  if (warp < M)
+    route_row(rows[warp], selection_bias, E, top_k, lane, picks[warp], ids + static_cast<int64_t>(warp) * top_k,
+              weights + static_cast<int64_t>(warp) * top_k, entropy ? entropy + warp : nullptr, confidence ? confidence + warp : nullptr);
 }
 
 // ---- grouping --------------------------------------------------------------------------------------------------
@@ -389,6 +462,17 @@ extern "C" int lx_moe_route(const float* logits, const float* selection_bias, in
   if (top_k < 1 || top_k > kMaxTopK || top_k > E || !logits || !ids || !weights) return kInvalid;
   return launch_kernel(route_kernel, dim3((T + 7) / 8), dim3(256), 0, static_cast<cudaStream_t>(stream), logits,
                        selection_bias, ids, weights, entropy, confidence, T, E, top_k);
+}
+
+extern "C" int lx_router_route(const float* x, int ld_x, const float* w, const float* bias, float* logits,
+                               const float* selection_bias, int32_t* ids, float* weights, float* entropy, float* confidence,
+                               int32_t* ticket, int M, int E, int K, int top_k, void* stream) {
+  if (M <= 0) return kOk;
+  if (M > kRouterRows || E < 1 || E > kRouterMaxE || K < 1 || K > kRouterMaxK || top_k < 1 || top_k > kMaxTopK || top_k > E)
+    return kInvalid;
+  if (!x || !w || !logits || !ids || !weights || !ticket || ld_x < K) return kInvalid;
+  return launch_kernel(router_kernel, dim3((E + 7) / 8), dim3(256), 0, static_cast<cudaStream_t>(stream), x, ld_x, w, bias, logits,
+                       selection_bias, ids, weights, entropy, confidence, ticket, M, E, K, top_k);
 }
 
 extern "C" int64_t lx_moe_grouped_workspace_bytes(int T, int L, int I, int E, int top_k, lx_math math) {

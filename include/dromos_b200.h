@@ -131,8 +131,14 @@ LX_API int64_t lx_moe_bf16x_workspace_bytes(int T, int I, int top_k);
  * reference. kernels.h:224 (engine/cuda/moe.cu:288-310). */
 LX_API int lx_moe_experts(const void* latent, const int32_t* ids, const float* weights, const void* gate_up,
                           const void* down, float* out, int T, int L, int I, int top_k, void* stream);
-/* Not exported yet (the engine's dispatcher then falls back to lx_moe_route on logits it computes itself, as
- * kernels.h:211-215 says hosts do): lx_router_route (kernels.h:216). */
+/* The router of a decode-sized step (M <= 8, E <= 1024, K <= 2048) in one launch: logits = x @ w^T + bias, then the
+ * routing of lx_moe_route on those logits; ticket is one zeroed int32 word the call leaves at zero. kernels.h:211-218
+ * (engine/cuda/moe.cu:82-157, 264-286). The routing outputs equal lx_moe_route on the returned logits bit for bit; the
+ * logits are this library's own f32 sums (one warp per expert), not those of lx_spec_gemv_f32, which is outside the
+ * path and not exported. */
+LX_API int lx_router_route(const float* x, int ld_x, const float* w, const float* bias, float* logits,
+                           const float* selection_bias, int32_t* ids, float* weights, float* entropy, float* confidence,
+                           int32_t* ticket, int M, int E, int K, int top_k, void* stream);
 
 /* ---- architecture and variant table (tunable.h:37-75, engine/cuda/tunable.cu) ---------------------------- */
 typedef struct {

@@ -149,3 +149,70 @@ def test_token_bits_do_not_depend_on_batch(lx):
         util.check_status(lx)
         outs[t] = util.host(out).view(np.uint32).copy()
     assert np.array_equal(outs[1], outs[8][:1]) and np.array_equal(outs[3], outs[8][:3])
+
+
+def router_case(lx, M, E, K, top_k, with_bias, seed, tie=False):
+    rng = np.random.default_rng(seed)
+    ld_x = K + 3
+    w = (rng.standard_normal((E, K)) * 0.05).astype(np.float32)
+    bias = rng.standard_normal(E).astype(np.float32) if with_bias else None
+    sel = (rng.standard_normal(E) * 0.3).astype(np.float32) if with_bias else None
+    if tie:  # experts 16.. repeat experts 0..15: equal logits and biases tie, the lower index wins; a NaN bias is never picked
+        dup = np.arange(16, E) % 16
+        w[16:], bias[16:], sel[16:] = w[dup], bias[dup], sel[dup]
+        sel[5] = np.nan
+    x = rng.standard_normal((M, ld_x)).astype(np.float32)
+    x_d, w_d = util.dev(x), util.dev(w)
+    bias_d = None if bias is None else util.dev(bias)
+    sel_d = None if sel is None else util.dev(sel)
+    logits = torch.full((M, E), float("nan"), device="cuda")
+    ids = torch.full((M, top_k), -7, dtype=torch.int32, device="cuda")
+    weights = torch.full((M, top_k), float("nan"), device="cuda")
+    ent = torch.full((M,), float("nan"), device="cuda")
+    conf = torch.full((M,), float("nan"), device="cuda")
+    ticket = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(2):  # twice on the same ticket: the call leaves it at zero
+        st = lx.lx_router_route(abi.ptr(x_d), ld_x, abi.ptr(w_d), abi.ptr(bias_d), abi.ptr(logits), abi.ptr(sel_d), abi.ptr(ids),
+                                abi.ptr(weights), abi.ptr(ent), abi.ptr(conf), abi.ptr(ticket), M, E, K, top_k, util.stream_ptr())
+        assert st == 0, st
+        torch.cuda.synchronize()
+        assert int(ticket.item()) == 0
+    want = x[:, :K].astype(np.float64) @ w.astype(np.float64).T + (0.0 if bias is None else bias.astype(np.float64))
+    got = util.host(logits)
+    assert np.abs(got - want).max() <= 1e-5 * max(1.0, np.abs(want).max())
+    # the routing is lx_moe_route on these logits, bit for bit
+    ids2 = torch.full((M, top_k), -1, dtype=torch.int32, device="cuda")
+    w2, e2, c2 = torch.zeros((M, top_k), device="cuda"), torch.zeros(M, device="cuda"), torch.zeros(M, device="cuda")
+    assert lx.lx_moe_route(abi.ptr(logits), abi.ptr(sel_d), abi.ptr(ids2), abi.ptr(w2), abi.ptr(e2), abi.ptr(c2), M, E, top_k,
+                           util.stream_ptr()) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(ids, ids2)
+    for a, b in ((weights, w2), (ent, e2), (conf, c2)):
+        assert torch.equal(a.view(torch.int32), b.view(torch.int32))
+    return util.host(ids), got, sel
+
+
+@pytest.mark.parametrize("E,K,top_k", [(128, 1280, 4), (192, 1280, 4), (128, 1000, 4), (64, 300, 8), (1024, 2048, 32)])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_router_in_one_launch(lx, E, K, top_k, with_bias):
+    """lx_router_route for every row count of a decode-sized step (mirrors the reference's tests/kernels/test_moe.py:255-284)."""
+    for M in range(1, 9):
+        ids, logits, sel = router_case(lx, M, E, K, top_k, with_bias, seed=M + E)
+        ids_o, _, _, _ = O.moe_route(logits, sel, top_k)
+        assert np.array_equal(ids, ids_o)
+
+
+def test_router_breaks_ties_like_the_route_call(lx):
+    for M in (1, 5, 8):
+        ids, _, _ = router_case(lx, M, 128, 1280, 4, True, seed=2 + M, tie=True)
+        assert not np.any(ids == 5)
+
+
+def test_router_refuses_what_the_reference_refuses(lx):
+    z = torch.zeros(16, device="cuda")
+    zi = torch.zeros(16, dtype=torch.int32, device="cuda")
+    args = lambda M, E, K, k, ld: (abi.ptr(z), ld, abi.ptr(z), None, abi.ptr(z), None, abi.ptr(zi), abi.ptr(z), None, None, abi.ptr(zi), M, E, K, k, None)
+    assert lx.lx_router_route(*args(9, 4, 4, 1, 4)) == 1       # more than eight rows
+    assert lx.lx_router_route(*args(1, 2000, 4, 1, 4)) == 1    # more experts than the epilogue stages
+    assert lx.lx_router_route(*args(1, 4, 4, 1, 3)) == 1       # a row stride shorter than the row
+    assert lx.lx_router_route(*args(0, 4, 4, 1, 4)) == 0       # nothing to do
