@@ -109,3 +109,45 @@ def test_full_size_routed_experts(lx):
     alone = layer(latent[T - 1:].contiguous(), ids[T - 1:].contiguous(), weights[T - 1:].contiguous()).clone()
     torch.cuda.synchronize()
     assert torch.equal(alone[0], out[T - 1]), "a token's bits depend on its batch"
+
+
+def test_full_size_few_token_experts(lx):
+    """The C5 stacks (E = 64, top-8, L = 4096, I = 1536, FP8) through lx_moe_experts_decode at T = 1 and T = 8: sampled
+    tokens against the float64 oracle on the device's own bytes of the experts they picked, and every token of the batch
+    equal to that token alone, bit for bit."""
+    E, top_k, L, I, T = 64, 8, 4096, 1536, 8
+    gen = torch.Generator(device="cuda").manual_seed(12)
+    gu = host.store_weight(lx, (torch.randn((E, 2 * I, L), generator=gen, device="cuda") * 0.02).to(torch.bfloat16), abi.W_FP8)
+    dn = host.store_weight(lx, (torch.randn((E, L, I), generator=gen, device="cuda") * 0.02).to(torch.bfloat16), abi.W_FP8)
+    latent = torch.randn((T, L), generator=gen, device="cuda").to(torch.bfloat16)
+    logits = torch.randn((T, E), generator=gen, device="cuda")
+    ids, weights = host.Experts(lx, gu, dn, E, L, I, top_k).route(logits)
+    ws = torch.full((lx.lx_moe_decode_workspace_bytes(T, I, top_k),), 0xFF, dtype=torch.uint8, device="cuda")
+
+    def decode(t0, t1):
+        out = torch.full((t1 - t0, L), float("nan"), device="cuda")
+        st = lx.lx_moe_experts_decode(abi.ptr(latent[t0:t1]), abi.ptr(ids[t0:t1]), abi.ptr(weights[t0:t1]), gu.ref(), dn.ref(),
+                                      abi.ptr(out), abi.ptr(ws), t1 - t0, L, I, top_k, util.stream_ptr())
+        assert st == 0, st
+        util.check_status(lx)
+        return out
+
+    batch = decode(0, T)
+    for t in range(T):
+        assert torch.equal(decode(t, t + 1)[0], batch[t]), f"token {t} of the batch differs from the token alone"
+    got = batch.cpu().numpy()
+    ids_h, w_h = ids.cpu().numpy(), weights.cpu().numpy()
+    lat_h = O.bf16_bits_to_f32(latent.view(torch.int16).cpu().numpy().view(np.uint16)).astype(np.float64)
+    gu_data, gu_scale = gu.data.view(E, 2 * I, L), gu.scale.view(E, 2 * I)
+    dn_data, dn_scale = dn.data.view(E, L, I), dn.scale.view(E, L)
+    for t in (0, T - 1):
+        want = np.zeros(L, dtype=np.float64)
+        for k in range(top_k):
+            e = int(ids_h[t, k])
+            wg = O.weight_f64(O.Weight(O.W_FP8, gu_data[e].cpu().numpy(), gu_scale[e].cpu().numpy()))
+            wd = O.weight_f64(O.Weight(O.W_FP8, dn_data[e].cpu().numpy(), dn_scale[e].cpu().numpy()))
+            h = wg @ lat_h[t]
+            g, u = h[:I], h[I:]
+            mid = O.bf16_bits_to_f32(O.f32_to_bf16_bits((g / (1.0 + np.exp(-g)) * u).astype(np.float32))).astype(np.float64)
+            want += float(w_h[t, k]) * (wd @ mid)
+        util.assert_close(got[t], want, what=f"few-token experts, token {t}")
