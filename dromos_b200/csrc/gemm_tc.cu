@@ -571,17 +571,26 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, XMODE ? 
         for (int a = 0; a < B * group + b; ++a) x[b].advance(SX);
       int d = 0, tile = tile_begin, s = B * group;  // the iteration's first stage: stage s of `tile`
       while (s >= n_stages) s -= n_stages, ++tile;
-      for (int i = B * group; i < total && ok; i += 2 * B) {
+      for (int i = B * group; ok; i += 2 * B) {
+        const bool draining = i >= total;  // past the last stage: group 0 reads the accumulators that are left
         if (group == 0) {
           // The products of a stage's tile need the accumulator of the tile two before it: that one must have been
           // read by now (the iteration's second stage may already belong to the next tile). The one before, as soon as
-          // it happens to be complete.
+          // it happens to be complete. (One call site: the epilogue is 9 KB of code, and code size shows whenever the
+          // stream alternates between kernels.)
           const int tile_hi = s + 1 >= n_stages ? tile + 1 : tile;
-          while (ok && next_finish <= tile_hi - 2) ok = finish(next_finish++);
-          if (ok && next_finish < tile && mbar_try_wait(d_full((next_finish - tile_begin) & 1), ((next_finish - tile_begin) >> 1) & 1))
+          for (;;) {
+            const bool must = draining ? next_finish < tile_end : next_finish <= tile_hi - 2;
+            bool go = must;
+            if (!go && !draining && next_finish < tile)
+              go = mbar_try_wait(d_full((next_finish - tile_begin) & 1), ((next_finish - tile_begin) >> 1) & 1);
+            if (!go) break;
             ok = finish(next_finish++);
+            if (!ok || !must) break;
+          }
           if (!ok) break;
         }
+        if (draining) break;
         wait_landed();  // the oldest group in flight, this iteration's
         uint32_t w[B][3][4];
 #pragma unroll
@@ -621,7 +630,6 @@ __global__ void __launch_bounds__(XMODE ? kOwnThreads : kDirectThreads, XMODE ? 
       }
       asm volatile("cp.async.wait_group 0;" ::: "memory");
       if (group == 0) {
-        while (ok && next_finish < tile_end) ok = finish(next_finish++);
         if constexpr (PEERS) signal_peers(P, lane, cta_count);
       }
     }
