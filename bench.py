@@ -416,18 +416,26 @@ def main():
     yh = {M: torch.empty((M, (n1 - n0) * (world if world > 1 else 1)), dtype=torch.float32).pin_memory() for M in Ms}
     xd = {M: torch.empty_like(xs[M]) for M in Ms}
 
+    # The device-to-host copy of a product's outputs runs on a second stream under the next product of the step (largest
+    # outputs first, so that the longest copy has the most to hide behind); the step ends when every copy has landed.
+    copy_stream = torch.cuda.Stream()
+
     def e2e_work(i):
-        for j, M in enumerate(Ms):
+        main = torch.cuda.current_stream()
+        for j, M in sorted(enumerate(Ms), key=lambda jm: -jm[1]):
             xd[M].copy_(xh[M], non_blocking=True)
             if fused is not None:
-                yh[M].copy_(fused[(i * len(Ms) + j) % copies](xd[M]), non_blocking=True)
-                continue
-            layers[(i * len(Ms) + j) % copies](xd[M], ys[M])
-            if world > 1:
-                dist.all_gather_into_tensor(gathered[M].view(world * M, n1 - n0), ys[M])
-                yh[M].copy_(gathered[M].permute(1, 0, 2).reshape(M, -1), non_blocking=True)
+                src = fused[(i * len(Ms) + j) % copies](xd[M])
             else:
-                yh[M].copy_(ys[M], non_blocking=True)
+                layers[(i * len(Ms) + j) % copies](xd[M], ys[M])
+                src = ys[M]
+                if world > 1:
+                    dist.all_gather_into_tensor(gathered[M].view(world * M, n1 - n0), ys[M])
+                    src = gathered[M].permute(1, 0, 2).reshape(M, -1)
+            copy_stream.wait_stream(main)
+            with torch.cuda.stream(copy_stream):
+                yh[M].copy_(src, non_blocking=True)
+        main.wait_stream(copy_stream)
 
     run_e2e, _ = replayer(e2e_work, period)
 
