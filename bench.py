@@ -418,7 +418,7 @@ def main():
 
     # The device-to-host copy of a product's outputs runs on a second stream under the next product of the step (largest
     # outputs first, so that the longest copy has the most to hide behind); the step ends when every copy has landed.
-    copy_stream = torch.cuda.Stream()
+    copy_stream = torch.cuda.Stream() if world == 1 else None
 
     def e2e_work(i):
         main = torch.cuda.current_stream()
@@ -432,10 +432,14 @@ def main():
                 if world > 1:
                     dist.all_gather_into_tensor(gathered[M].view(world * M, n1 - n0), ys[M])
                     src = gathered[M].permute(1, 0, 2).reshape(M, -1)
+            if world > 1:  # with collectives in the step everything stays on one stream
+                yh[M].copy_(src, non_blocking=True)
+                continue
             copy_stream.wait_stream(main)
             with torch.cuda.stream(copy_stream):
                 yh[M].copy_(src, non_blocking=True)
-        main.wait_stream(copy_stream)
+        if world == 1:
+            main.wait_stream(copy_stream)
 
     run_e2e, _ = replayer(e2e_work, period)
 
