@@ -28,6 +28,9 @@ constexpr int kStatusPartWait = 4;   // a CTA waited for another CTA's partial s
 extern std::atomic<int64_t> g_launches;
 // The device status word of the current device (allocated on first use, one per device, never freed).
 int* status_word();
+// The status word of the entry point that works in the library's own static array (its first word), once that entry
+// point has looked the array up on the current device; null before.
+int* static_scratch_status();
 
 inline int launch_status() {
   g_launches.fetch_add(1, std::memory_order_relaxed);

@@ -5,6 +5,7 @@
 #include <cstdlib>
 #include <cstring>
 
+#include "gemv.cuh"
 #include "launch.cuh"
 #include "scalar.cuh"
 #include "variants.h"
@@ -77,45 +78,63 @@ int launch_dense_format(const StreamParams& P, cudaStream_t stream) {
   const int cols = std::min(P.M * T, 64);
   // NVFP4 holds four times the values per byte, so its stages span four times the K: shorter stages for wide tiles.
   constexpr int UW = F == LX_W_NVFP4 ? 1 : 2;
-  if (cols <= 8) {
-    // Bytes of activation units for the whole of K; up to 32 KB stays resident in the small buffer.
+  if (P.M <= 8) {
+    // Up to 8 activation rows. A format keeps ONE warp layout (consumer warps, warp rows, steps per stage: what fixes
+    // the order a row's products are added in) whatever M and the activation dtype are; only the number of 8-column
+    // tiles follows them. So a row's bits do not depend on its batch; BF16 and BF16X share their layout, so the
+    // lossless format reproduces bf16's bits.
     const int64_t unit_bytes = static_cast<int64_t>(P.K) / (k8 ? 16 : 8) * 16 * cols;
-    const bool big_x = unit_bytes > 32 * 1024;
-    const int tuned = lx_tune_get(gemv_kernel_name(F), P.M, P.N, P.K);
-    if (tuned < 0) {
-      // Defaults. A format keeps ONE warp layout (consumer warps, warp rows, steps per stage: what fixes the order a
-      // row's products are added in) for every M = 1..8, with the large activation buffer when the rows need it, so a
-      // row's bits do not depend on its batch; BF16 and BF16X share theirs, so the lossless format reproduces bf16's
-      // bits. Picked from sweeps of the variants at M = 1 on the decode shapes.
-      if constexpr (F == LX_W_BF16 || F == LX_W_BF16X)
-        return big_x ? launch_stream<F, 16, 1, 2, 1, 2, 2, 64, kDense>(P, stream, P.N) : launch_stream<F, 16, 1, 2, 1, 2, 5, 16, kDense>(P, stream, P.N);
-      if constexpr (F == LX_W_NVFP4)
-        return big_x ? launch_stream<F, 16, 1, 4, 1, 2, 2, 64, kDense>(P, stream, P.N) : launch_stream<F, 16, 1, 4, 1, 2, 4, 16, kDense>(P, stream, P.N);
-    }
-    if (big_x) return launch_stream<F, 8, 1, 2, 1, 2, 4, 64, kDense>(P, stream, P.N);
-    // decode GEMV: the variant the table holds for this shape (keyed on M's power-of-two bucket), else variant 0
-    switch (tuned) {
-      case 1: return launch_stream<F, 8, 1, 2, 1, 2, 8, 16, kDense>(P, stream, P.N);
-      case 2: return launch_stream<F, 8, 1, 2, 1, 2 * UW, 4, 16, kDense>(P, stream, P.N);
-      case 3: return launch_stream<F, 16, 1, 4, 1, 2, 4, 16, kDense>(P, stream, P.N);
-      case 4: return launch_stream<F, 8, 1, 1, 1, 1, 6, 16, kDense>(P, stream, P.N);
-      case 5: return launch_stream<F, 16, 1, 2, 1, 1, 6, 16, kDense>(P, stream, P.N);
-      case 6: return launch_stream<F, 8, 1, 1, 1, 2 * UW, 4, 32, kDense>(P, stream, P.N);
-      case 7: return launch_stream<F, 16, 1, 2, 1, UW, 4, 16, kDense>(P, stream, P.N);
-      case 8: return launch_stream<F, 16, 1, 2, 1, UW, 5, 16, kDense>(P, stream, P.N);
-      case 9: return launch_stream<F, 16, 1, 4, 1, 2 * UW, 3, 16, kDense>(P, stream, P.N);
-      // the deepest rings shared memory allows, for activations of at most 16 KB (32 KB for NVFP4)
-      case 10: return launch_stream<F, 8, 1, 2, 1, 2 * UW, (F == LX_W_NVFP4 ? 9 : 6), (F == LX_W_NVFP4 ? 16 : 8), kDense>(P, stream, P.N);
-      case 11: return launch_stream<F, 16, 1, 2, 1, UW, (F == LX_W_NVFP4 ? 9 : 6), (F == LX_W_NVFP4 ? 16 : 8), kDense>(P, stream, P.N);
-      case 12: return launch_stream<F, 8, 1, 2, 1, UW, (F == LX_W_NVFP4 ? 18 : 12), (F == LX_W_NVFP4 ? 16 : 8), kDense>(P, stream, P.N);
-      case 13: return launch_stream<F, 16, 1, 4, 1, UW, (F == LX_W_NVFP4 ? 9 : 6), (F == LX_W_NVFP4 ? 16 : 8), kDense>(P, stream, P.N);
-      default: return launch_stream<F, 8, 1, 2, 1, 2, 4, 16, kDense>(P, stream, P.N);
+    const bool big_x = unit_bytes > 32 * 1024;  // up to 32 KB of activation units stay resident in the small buffer
+    if constexpr (F == LX_W_BF16 || F == LX_W_BF16X) {
+      if (cols <= 8) return big_x ? launch_stream<F, 16, 1, 2, 1, 2, 2, 64, kDense>(P, stream, P.N) : launch_stream<F, 16, 1, 2, 1, 2, 5, 16, kDense>(P, stream, P.N);
+      return cols <= 16 ? launch_stream<F, 16, 1, 2, 2, 2, 2, 64, kDense>(P, stream, P.N) : launch_stream<F, 16, 1, 2, 3, 2, 2, 64, kDense>(P, stream, P.N);
+    } else if constexpr (F == LX_W_NVFP4) {
+      if (cols <= 8) return big_x ? launch_stream<F, 16, 1, 4, 1, 2, 2, 64, kDense>(P, stream, P.N) : launch_stream<F, 16, 1, 4, 1, 2, 4, 16, kDense>(P, stream, P.N);
+      return cols <= 16 ? launch_stream<F, 16, 1, 4, 2, 2, 2, 64, kDense>(P, stream, P.N) : launch_stream<F, 16, 1, 4, 3, 2, 2, 64, kDense>(P, stream, P.N);
+    } else {
+      if (cols <= 8) return big_x ? launch_stream<F, 8, 1, 2, 1, 2, 4, 64, kDense>(P, stream, P.N) : launch_stream<F, 8, 1, 2, 1, 2, 4, 16, kDense>(P, stream, P.N);
+      return cols <= 16 ? launch_stream<F, 8, 1, 2, 2, 2, 4, 64, kDense>(P, stream, P.N) : launch_stream<F, 8, 1, 2, 3, 2, 4, 64, kDense>(P, stream, P.N);
     }
   }
   if (cols <= 16) return launch_stream<F, 8, 1, 2, 2, 2, 4, 64, kDense>(P, stream, P.N);
   if (cols <= 24) return launch_stream<F, 8, 1, 2, 3, 2, 4, 64, kDense>(P, stream, P.N);
   if (cols <= 32) return launch_stream<F, 8, 2, 2, 4, UW, 3, 32, kDense>(P, stream, P.N);
   return launch_stream<F, 8, 2, 4, 8, UW, 2, 32, kDense>(P, stream, P.N);
+}
+
+// ---- the decode GEMV (gemv.cuh): up to 8 rows, every format ----------------------------------------------------------
+template <int F, int NT, int CPS>
+int launch_gemv_inst(const GemvParams& P, size_t smem, cudaStream_t stream) {
+  auto kernel = gemv_kernel<F, NT, CPS>;
+  if (int e = allow_dynamic_smem<4096 + F * 64 + NT * 8 + CPS>(kernel)) return e;
+  const int sms = sm_count();
+  if (!sms) return kInvalid;
+  const unsigned grid = static_cast<unsigned>(std::max(1, std::min(P.N, sms * CPS)));
+  return launch_kernel(kernel, dim3(grid), dim3(kGemvThreads), smem, stream, P);
+}
+
+// variant: an index into kGemvVariantNames (see variants.h), -1 = two CTAs per SM when their shared memory allows
+template <int F>
+int launch_gemv(GemvParams P, int variant, cudaStream_t stream) {
+  P.planes = terms_for(GemvFmt<F>::kMma, P.x_dtype == LX_BF16);
+  P.ncols = P.M * P.planes;
+  P.pitch = gemv_pitch(P.K, F);
+  P.steps = P.K / GemvFmt<F>::kStepValues;
+  const size_t smem = gemv_smem(P.K, F, P.ncols);
+  const int NT = (P.ncols + 7) / 8;
+  // BF16X decodes in registers and wants more of them than two CTAs per SM leave (measured: 36 us against 55 on the
+  // 14336 x 4096 matrix), so one CTA per SM is its default; the table can still name d4c2.
+  const bool two = variant == kGemvD4C2 || (variant < 0 && F != LX_W_BF16X);
+  const int cps = (smem <= 110 * 1024 && two) ? 2 : 1;
+  switch (NT * 10 + cps) {
+    case 11: return launch_gemv_inst<F, 1, 1>(P, smem, stream);
+    case 12: return launch_gemv_inst<F, 1, 2>(P, smem, stream);
+    case 21: return launch_gemv_inst<F, 2, 1>(P, smem, stream);
+    case 22: return launch_gemv_inst<F, 2, 2>(P, smem, stream);
+    case 31: return launch_gemv_inst<F, 3, 1>(P, smem, stream);
+    case 32: return launch_gemv_inst<F, 3, 2>(P, smem, stream);
+  }
+  return kInvalid;
 }
 
 int row_bytes_of(int type, int K) {
@@ -127,12 +146,71 @@ int row_bytes_of(int type, int K) {
   }
 }
 
+int gemv_env_variant() {
+  static const int v = [] {
+    const char* name = std::getenv("LX_B200_GEMV_VARIANT");
+    for (int i = 0; name && i < kGemvVariants; ++i)
+      if (std::strcmp(name, kGemvVariantNames[i]) == 0) return i;
+    return -1;
+  }();
+  return v;
+}
+
+bool gemv_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("LX_B200_GEMV");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+
+// Can the decode GEMV take this weight? Whole 64-byte steps per row, the data aligned for the widest load the format
+// uses, and the activation columns of EIGHT rows within shared memory (so that the answer is the same for every M).
+bool gemv_ok(const lx_weight& w, int K, bool x_bf16) {
+  if (!gemv_shape_ok(w.type, K, x_bf16)) return false;
+  switch (w.type) {
+    case LX_W_BF16X: return aligned(w.data, 8);
+    case LX_W_NVFP4: return aligned(w.data, 16) && aligned(w.scale, 2);
+    default: return aligned(w.data, 16);
+  }
+}
+
 // The product itself, arguments already validated.
 int dense_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const void* bias, int bias_dtype, void* y,
                   int y_dtype, int ld_y, int M, int N, int K, float alpha, float beta, cudaStream_t stream) {
-  // Up to 8 rows of INT8 / FP8 weights with enough rows per SM: the tensor-core product (the choice never depends on M)
-  if (M <= 8 && !force_scalar() && tc_rows_ok(w, N, K))
-    return tc_product_rows(x, x_dtype, ld_x, w, bias, bias_dtype, y, y_dtype, ld_y, M, N, K, alpha, beta, stream);
+  // Up to 8 rows: the decode GEMV of gemv.cuh whenever the weight's shape and alignment allow, except INT8 weights wide
+  // enough for the tcgen05 product, which is the faster one there (measured on 14336 x 4096: 15.4 / 17.1 us at M = 1 / 8
+  // against 16.5 / 23.2). The choice never depends on M. The variant table can name another residency of the GEMV (same
+  // bits), or, through lx_tune_force only, another implementation: the TMA-ring mma.sync kernel of stream.cuh ("ring"),
+  // the tcgen05 product ("tc", INT8 / FP8 weights with enough rows per SM). LX_B200_GEMV=0 restores the ring / tc pair.
+  if (M <= 8 && !force_scalar()) {
+    int tuned = lx_tune_get(gemv_kernel_name(w.type), M, N, K);
+    if (tuned < 0) tuned = gemv_env_variant();  // LX_B200_GEMV_VARIANT=<name>: the variant of shapes the table does not hold
+    const bool gemv_named = tuned == kGemvD4C2 || tuned == kGemvD8C1;
+    const bool want_tc = tuned == kGemvTc || (tuned < 0 && (!gemv_enabled() || w.type == LX_W_INT8));
+    const bool want_ring = tuned == kGemvRing || (tuned < 0 && !gemv_enabled());
+    if (want_tc && tc_rows_ok(w, N, K))
+      return tc_product_rows(x, x_dtype, ld_x, w, bias, bias_dtype, y, y_dtype, ld_y, M, N, K, alpha, beta, stream);
+    if (!want_ring && (!want_tc || gemv_named || !tc_rows_ok(w, N, K)) && gemv_ok(w, K, x_dtype == LX_BF16)) {
+      GemvParams G{};
+      G.w = static_cast<const uint8_t*>(w.data);
+      G.scale = static_cast<const uint8_t*>(w.scale);
+      G.global = w.global;
+      G.row_bytes = row_bytes_of(w.type, K);
+      G.N = N, G.K = K;
+      G.x = x, G.x_dtype = x_dtype, G.ld_x = ld_x, G.M = M;
+      G.bias = bias, G.bias_dtype = bias_dtype;
+      G.y = y, G.y_dtype = y_dtype, G.ld_y = ld_y;
+      G.alpha = alpha, G.beta = beta;
+      switch (w.type) {
+        case LX_W_BF16: return launch_gemv<LX_W_BF16>(G, tuned, stream);
+        case LX_W_INT8: return launch_gemv<LX_W_INT8>(G, tuned, stream);
+        case LX_W_FP8: return launch_gemv<LX_W_FP8>(G, tuned, stream);
+        case LX_W_NVFP4: return launch_gemv<LX_W_NVFP4>(G, tuned, stream);
+        case LX_W_BF16X: return launch_gemv<LX_W_BF16X>(G, tuned, stream);
+      }
+    }
+  }
   StreamParams P{};
   P.w = static_cast<const uint8_t*>(w.data);
   P.scale = static_cast<const uint8_t*>(w.scale);
@@ -220,6 +298,14 @@ extern "C" int lx_gemv_bf16x(const void* x, lx_dtype x_dtype, int ld_x, const vo
 // per-row scales, FP4 block scales, each 256-byte aligned). BF16 math needs none here, but the size answered is the
 // reference's so that callers sized for either library work with both.
 namespace b200 {
+// The part of the decode GEMV's admission that depends on the format, K and the activation dtype only.
+bool gemv_shape_ok(int wtype, int K, bool x_bf16) {
+  if (wtype < LX_W_BF16 || wtype > LX_W_BF16X) return false;
+  if (K <= 0 || K % gemv_step_values(wtype) != 0) return false;
+  if (wtype == LX_W_BF16X && K >= (1 << 23)) return false;
+  return gemv_smem(K, wtype, 8 * terms_for(gemv_mma_of(wtype), x_bf16)) <= kGemvSmemMax;
+}
+
 ActLayout act_layout(int M, int K, int math) {
   auto round_up = [](int64_t v, int64_t a) { return (v + a - 1) / a * a; };
   ActLayout l{};
@@ -260,11 +346,9 @@ extern "C" int lx_gemm_w(const void* x, lx_dtype x_dtype, int ld_x, const lx_wei
   // Weight rows must be whole 16-byte chunks, as for the reference's tensor-core kernels.
   const int64_t rowb = row_bytes_of(w->type, K);
   if (rowb % 16 != 0 || !aligned(w->data, 16) || (w->type == LX_W_NVFP4 && K % 64 != 0)) return kNotSupported;
-  // With a workspace every row count goes through the tcgen05 product, so that a row's bits do not depend on M
-  // (up to 8 rows of INT8 / FP8 prepare their own activations there and give the same bits). LX_B200_TC=0 keeps the
-  // mma.sync streaming kernel.
-  if (tc_enabled() && workspace && aligned(workspace, 16) && !(M <= 8 && tc_rows_ok(*w, N, K)) &&
-      (w->type != LX_W_NVFP4 || (K % 256 == 0 && aligned(w->scale, 16))))
+  // With a workspace every row count goes through the tcgen05 product, so that within this entry point a row's bits
+  // do not depend on M. LX_B200_TC=0 keeps the mma.sync kernels.
+  if (tc_enabled() && workspace && aligned(workspace, 16) && (w->type != LX_W_NVFP4 || (K % 256 == 0 && aligned(w->scale, 16))))
     return tc_product(x, x_dtype, ld_x, *w, bias, bias_dtype, y, y_dtype, ld_y, M, N, K, alpha, beta, workspace,
                       static_cast<cudaStream_t>(stream));
   return dense_product(x, x_dtype, ld_x, *w, bias, bias_dtype, y, y_dtype, ld_y, M, N, K, alpha, beta,

@@ -956,11 +956,13 @@ bool tc_enabled() {
 // rows of whole 16-byte pieces. The answer depends on the weight and its shape only, never on the row count, so that
 // a row's bits do not depend on its batch. (BF16 stays with the streaming kernel, whose bits the lossless BF16X
 // format must reproduce.)
-bool tc_rows_ok(const lx_weight& w, int N, int K) {
-  if (!tc_enabled() || (w.type != LX_W_INT8 && w.type != LX_W_FP8)) return false;
-  if (K % 16 != 0 || (reinterpret_cast<uintptr_t>(w.data) & 15) != 0) return false;
+bool tc_rows_shape_ok(int wtype, int N, int K) {
+  if (!tc_enabled() || (wtype != LX_W_INT8 && wtype != LX_W_FP8) || K % 16 != 0) return false;
   const int sms = sm_count();
   return sms > 0 && tile_rows(N, sms) >= 40;
+}
+bool tc_rows_ok(const lx_weight& w, int N, int K) {
+  return tc_rows_shape_ok(w.type, N, K) && (reinterpret_cast<uintptr_t>(w.data) & 15) == 0;
 }
 
 // Up to 8 activation rows, prepared by the product kernel itself: one launch, no workspace.

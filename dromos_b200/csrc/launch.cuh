@@ -189,6 +189,8 @@ int experts_tc(const void* latent, const float* weights, const lx_weight& gate_u
                const int32_t* pairs, uint16_t* mid, float* rows, uint8_t* ws, int64_t base, int T, int L, int I, int E, int top_k,
                int* status, cudaStream_t stream);
 bool tc_rows_ok(const lx_weight& w, int N, int K);
+bool gemv_shape_ok(int wtype, int K, bool x_bf16);
+bool tc_rows_shape_ok(int wtype, int N, int K);
 int tc_product_rows(const void* x, int x_dtype, int ld_x, const lx_weight& w, const void* bias, int bias_dtype, void* y, int y_dtype,
                     int ld_y, int M, int N, int K, float alpha, float beta, cudaStream_t stream);
 

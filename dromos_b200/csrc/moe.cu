@@ -194,6 +194,7 @@ __global__ void __launch_bounds__(1024) group_kernel(const int32_t* __restrict__
   }
   __syncthreads();
   if (e <= E) offsets[e] = start[e];
+  if (e == 0) offsets[E] = start[E];  // with E equal to the thread count no thread has e == E
   const int row0 = e < E ? start[e] : 0, rows = count;
   if (e < E) {
     int at = row0;
@@ -518,28 +519,40 @@ constexpr int64_t kStaticHeaderBytes = 256;  // the first bytes hold this entry 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 namespace {
+std::mutex g_static_mu;
+uint8_t* g_static_base[64] = {};
 // In host code `g_static_scratch` is only a handle: the address kernels can use comes from cudaGetSymbolAddress, asked
 // once per device with that device current.
 int static_scratch(uint8_t** ptr) {
-  static std::mutex mu;
-  static uint8_t* base[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return static_cast<int>(cudaGetLastError());
   dev &= 63;
-  std::lock_guard<std::mutex> lock(mu);
-  if (!base[dev]) {
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (!g_static_base[dev]) {
     void* p = nullptr;
     const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
     if (e != cudaSuccess) {
       cudaGetLastError();
       return static_cast<int>(e);
     }
-    base[dev] = static_cast<uint8_t*>(p);
+    g_static_base[dev] = static_cast<uint8_t*>(p);
   }
-  *ptr = base[dev];
+  *ptr = g_static_base[dev];
   return kOk;
 }
 }  // namespace
+
+namespace b200 {
+int* static_scratch_status() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  return reinterpret_cast<int*>(g_static_base[dev & 63]);
+}
+}  // namespace b200
 
 extern "C" int64_t lx_b200_moe_static_scratch_bytes(void) { return kStaticScratchBytes - kStaticHeaderBytes; }
 

@@ -147,9 +147,30 @@ int lx_tune_get(const char* kernel, int M, int N, int K) {
   return it == table().end() ? -1 : it->second;
 }
 
-// Every variant of a kernel sums a row's products in one order class per (N, K) that does not depend on M, so the
-// table admits any registered variant; an unknown variant index is refused.
+// The admission rule of the decode GEMV kernels (the reference's order-class rule, engine/cuda/tunable.cu:104-118): a
+// variant is stored only if it adds a row's products in the same order as what runs by default for that format and K,
+// because a row's bits must not depend on the M bucket the table is keyed on, and the BF16X kernel must keep the bits of
+// the bf16 kernel. The default is the tcgen05 product for INT8 weights wide enough for it (class 2), else the decode
+// GEMV where the shape admits it (class 0), else the TMA-ring kernel (class 1); a GEMV variant named for a shape the
+// GEMV cannot take changes nothing and is admitted.
 int lx_tune_set(const char* kernel, int M, int N, int K, int variant) {
+  if (!kernel) return kInvalid;
+  const VariantList* v = find_kernel(kernel);
+  if (v && (variant < 0 || variant >= v->count)) return LX_ERR_TUNE_VARIANT;
+  const int wtype = gemv_kernel_wtype(kernel);
+  if (wtype >= 0) {
+    const bool eligible = gemv_shape_ok(wtype, K, true);
+    const bool wide_int8 = wtype == LX_W_INT8 && tc_rows_shape_ok(wtype, N, K);
+    const int cls = gemv_order_class(variant), default_cls = wide_int8 ? 2 : eligible ? 0 : 1;
+    if (cls != default_cls && !(cls == 0 && !eligible && !wide_int8)) return LX_ERR_TUNE_REJECTED;
+  }
+  std::lock_guard<std::mutex> lock(g_mu);
+  table()[TableKey{kernel, m_bucket(M), N, K}] = variant;
+  return kOk;
+}
+
+// Stores a variant with no admission check (tunable.h:50-52): for tests and benchmarks that run every variant.
+int lx_tune_force(const char* kernel, int M, int N, int K, int variant) {
   if (!kernel) return kInvalid;
   const VariantList* v = find_kernel(kernel);
   if (v && (variant < 0 || variant >= v->count)) return LX_ERR_TUNE_VARIANT;
@@ -157,8 +178,6 @@ int lx_tune_set(const char* kernel, int M, int N, int K, int variant) {
   table()[TableKey{kernel, m_bucket(M), N, K}] = variant;
   return kOk;
 }
-
-int lx_tune_force(const char* kernel, int M, int N, int K, int variant) { return lx_tune_set(kernel, M, N, K, variant); }
 
 void lx_tune_clear(void) {
   std::lock_guard<std::mutex> lock(g_mu);
@@ -221,6 +240,13 @@ int lx_b200_last_error(void) {
   int v = 0;
   if (cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -static_cast<int>(cudaGetLastError());
   if (v) cudaMemset(w, 0, sizeof(int));
+  // the entry point that allocates nothing keeps its kernels' status in the first word of its own array
+  if (int* sw = static_scratch_status()) {
+    int sv = 0;
+    if (cudaMemcpy(&sv, sw, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -static_cast<int>(cudaGetLastError());
+    if (sv) cudaMemset(sw, 0, sizeof(int));
+    if (!v) v = sv;
+  }
   return v;
 }
 

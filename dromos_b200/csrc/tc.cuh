@@ -355,6 +355,24 @@ int allow_big_smem(Kernel kernel) {
   return kOk;
 }
 
+// The same opt-in without the carve-out preference: a kernel that reads through L1 (plain loads, many in flight) wants
+// the driver to leave L1 everything its shared memory does not need. Measured: with the whole of L1 carved out as shared
+// memory the decode GEMV streamed at 2.4 TB/s instead of 6.
+template <int Tag, typename Kernel>
+int allow_dynamic_smem(Kernel kernel) {
+  static std::mutex mu;
+  static bool done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 63;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!done[dev]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) != cudaSuccess) return static_cast<int>(cudaGetLastError());
+    done[dev] = true;
+  }
+  return kOk;
+}
+
 inline int act_of(int wtype) {
   return wtype == LX_W_BF16 ? kActBf16 : wtype == LX_W_INT8 ? kActS8 : wtype == LX_W_FP8 ? kActE4m3 : kActF16;
 }

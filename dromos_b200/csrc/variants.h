@@ -1,7 +1,14 @@
 // The kernels that have alternatives and the names of their variants (the registry behind lx_tune_kernels,
-// lx_tune_variants and lx_tune_variant_name). A decode GEMV variant is "s<ring stages>r<rows per tile>u<64-byte steps
-// per warp per stage>[w<consumer warps, 8 when absent>]"; index 0 is what runs when the table holds nothing for a shape.
+// lx_tune_variants and lx_tune_variant_name). The five decode GEMV kernels (one per weight format) share one list:
+//   d4c2   the decode GEMV of gemv.cuh, two CTAs per SM, 64 bytes per row in flight per lane
+//   d8c1   the same kernel, one CTA per SM, 128 bytes in flight; both add a row's products in the same order (same bits)
+//   ring   the TMA-ring mma.sync kernel of stream.cuh       another order: lx_tune_set refuses it, lx_tune_force takes it
+//   tc     the tcgen05 product (INT8 / FP8, wide weights)   another order again
+// What runs when the table holds nothing for a shape: d4c2 when two CTAs' activation columns fit an SM, else d8c1
+// (BF16X: always d8c1, it needs the registers).
 #pragma once
+
+#include <cstring>
 
 namespace b200 {
 
@@ -11,10 +18,10 @@ struct VariantList {
   const char* const* names;
 };
 
-constexpr int kGemvVariants = 14;
-inline const char* const kGemvVariantNames[kGemvVariants] = {"s4r32u2", "s8r32u2", "s4r32u4", "s4r64u2w16", "s6r16u1", "s6r32u1w16",
-                                                                "s4r16u4", "s4r32u2w16", "s5r32u2w16", "s3r64u4w16",
-                                                                "s6r32u4x8", "s6r32u2w16x8", "s12r32u2x8", "s6r64u2w16x8"};
+enum GemvVariant { kGemvD4C2 = 0, kGemvD8C1 = 1, kGemvRing = 2, kGemvTc = 3, kGemvVariants = 4 };
+inline const char* const kGemvVariantNames[kGemvVariants] = {"d4c2", "d8c1", "ring", "tc"};
+// Variants of one class add a row's products in the same order (same bits).
+inline int gemv_order_class(int variant) { return variant == kGemvRing ? 1 : variant == kGemvTc ? 2 : 0; }
 
 constexpr int kVariantKernels = 5;
 inline const VariantList kVariantTable[kVariantKernels] = {
@@ -25,6 +32,11 @@ inline const VariantList kVariantTable[kVariantKernels] = {
 
 inline const char* gemv_kernel_name(int wtype) {
   return wtype >= 0 && wtype < kVariantKernels ? kVariantTable[wtype].kernel : nullptr;
+}
+inline int gemv_kernel_wtype(const char* name) {
+  for (int i = 0; i < kVariantKernels; ++i)
+    if (name && std::strcmp(kVariantTable[i].kernel, name) == 0) return i;
+  return -1;
 }
 
 }  // namespace b200

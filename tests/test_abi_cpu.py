@@ -39,11 +39,38 @@ def test_host_only_entry_points_answer_without_a_gpu():
     n = lib.lx_tune_kernels(None, 0)
     assert n == 5
     assert lib.lx_tune_variants(b"gemv_w_fp8") >= 1 and lib.lx_tune_variants(b"nope") == 0
-    assert re.match(rb"s\d+", lib.lx_tune_variant_name(b"gemv_w_fp8", 0))
+    names = [lib.lx_tune_variant_name(b"gemv_w_fp8", i) for i in range(lib.lx_tune_variants(b"gemv_w_fp8"))]
+    assert re.match(rb"d\d+c\d+", names[0]) and b"ring" in names and b"tc" in names
+    assert lib.lx_tune_variant_name(b"gemv_w_fp8", len(names)) is None
     assert lib.lx_tune_set(b"gemv_w_fp8", 1, 64, 64, 10**6) == abi.ERR_TUNE_VARIANT
     assert lib.lx_tune_set(b"gemv_w_fp8", 3, 64, 64, 1) == 0 and lib.lx_tune_get(b"gemv_w_fp8", 4, 64, 64) == 1  # M bucket 4
     lib.lx_tune_clear()
     assert lib.lx_tune_get(b"gemv_w_fp8", 4, 64, 64) == -1
+
+
+def test_tune_set_refuses_another_summation_order():
+    """The order-class rule (engine/cuda/tunable.cu:104-118, tests/kernels/test_gemv_w.py:293-318): lx_tune_set stores a
+    variant only if it adds a row's products in the order of the shape's default; lx_tune_force stores anything."""
+    lib = abi.Library(abi.default_library_path())
+    lib.lx_tune_clear()
+    for kernel in (b"gemv_w_bf16", b"gemv_w_int8", b"gemv_w_fp8", b"gemv_w_nvfp4", b"gemv_bf16x"):
+        n = lib.lx_tune_variants(kernel)
+        names = [lib.lx_tune_variant_name(kernel, i) for i in range(n)]
+        same = [i for i, nm in enumerate(names) if re.match(rb"d\d+c\d+", nm)]
+        other = [i for i in range(n) if i not in same]
+        assert same and other
+        for v in same:  # K = 4096: every format's decode GEMV takes it
+            assert lib.lx_tune_set(kernel, 1, 4096, 4096, v) == 0
+            assert lib.lx_tune_get(kernel, 1, 4096, 4096) == v
+        for v in other:
+            assert lib.lx_tune_set(kernel, 1, 4096, 4096, v) == abi.ERR_TUNE_REJECTED
+            assert lib.lx_tune_get(kernel, 1, 4096, 4096) == same[-1]  # the table is unchanged
+            assert lib.lx_tune_force(kernel, 8, 4096, 4096, v) == 0 and lib.lx_tune_get(kernel, 8, 4096, 4096) == v
+        # K = 40 is not whole 64-byte steps for any format: the default there is the other kernel family
+        ring = names.index(b"ring")
+        assert lib.lx_tune_set(kernel, 1, 4096, 40, ring) == 0
+        assert lib.lx_tune_set(kernel, 1, 4096, 40, names.index(b"tc")) == abi.ERR_TUNE_REJECTED
+    lib.lx_tune_clear()
 
 
 def test_product_never_imports_the_oracle():

@@ -142,25 +142,42 @@ def test_gemm_w_odd_tiles_and_long_k(lx, fmt, case):
     assert np.array_equal(outs[0], outs[1]), "two runs differ"
 
 
-WIDE = [O.W_INT8, O.W_FP8]  # formats whose small batches run on the tensor-core product when N gives every SM >= 64 rows
+WIDE = [O.W_INT8, O.W_FP8]  # formats that also have a tcgen05 product for up to 8 rows when N gives every SM >= 40 rows
 
 
-@pytest.mark.parametrize("fmt", WIDE, ids=lambda f: NAMES[f])
+@pytest.mark.parametrize("fmt", FORMATS, ids=lambda f: NAMES[f])
 @pytest.mark.parametrize("M", [1, 3, 8])
 @pytest.mark.parametrize("x_f32", [False, True], ids=["xbf16", "xf32"])
 def test_gemv_wide_weight(lx, fmt, M, x_f32):
-    """N large enough that lx_gemv_w takes the tcgen05 path (tiles of 65 rows, a ragged last tile, K ending inside a
-    stage), with bias, alpha and beta."""
-    N, K = 9605, 1040
+    """N large enough that every CTA has several 16-row units with a ragged last one, K ending inside a warp's slice,
+    with bias, alpha and beta."""
+    N, K = 9605, 1152
     got, want, y0 = run(lx, fmt, M, N, K, seed=20 + M, x_f32=x_f32, bias_dtype=abi.BF16, alpha=1.5, beta=-0.5)
     check(got, want, y0, N, True, f"{NAMES[fmt]} M={M}")
 
 
 @pytest.mark.parametrize("fmt", WIDE, ids=lambda f: NAMES[f])
-def test_wide_weight_rows_do_not_depend_on_batch(lx, fmt):
-    """On the tensor-core path too, a row's bits are the same alone, in any batch of up to 8 (which prepare their own
-    activations) and in an lx_gemm_w call of 16 rows (activations prepared by a kernel of their own)."""
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("x_f32", [False, True], ids=["xbf16", "xf32"])
+def test_gemv_wide_weight_tensor_core_variant(lx, fmt, M, x_f32):
+    """The tcgen05 product for up to 8 rows (tiles of 65 rows, a ragged last tile, K ending inside a stage), reached
+    through the variant table."""
     N, K = 9605, 1040
+    kernel = b"gemv_w_int8" if fmt == O.W_INT8 else b"gemv_w_fp8"
+    names = [lx.lx_tune_variant_name(kernel, i) for i in range(lx.lx_tune_variants(kernel))]
+    assert lx.lx_tune_force(kernel, M, N, K, names.index(b"tc")) == 0
+    try:
+        got, want, y0 = run(lx, fmt, M, N, K, seed=20 + M, x_f32=x_f32, bias_dtype=abi.BF16, alpha=1.5, beta=-0.5)
+    finally:
+        lx.lx_tune_clear()
+    check(got, want, y0, N, True, f"{NAMES[fmt]} M={M}")
+
+
+@pytest.mark.parametrize("fmt", [O.W_BF16, O.W_INT8, O.W_FP8, O.W_NVFP4], ids=lambda f: NAMES[f])
+def test_gemm_w_rows_do_not_depend_on_batch(lx, fmt):
+    """Within lx_gemm_w (a workspace given) a row's bits are the same in a call of 1, 5, 8, 9 or 16 rows: every row count
+    runs on the tcgen05 product (the reference promises this under LX_BATCH_INVARIANT=1, engine/cuda/gemm_w.cu:160-168)."""
+    N, K = 9605, 1024
     w_bits = util.bf16_normal((N, K), 0.02, 31)
     dw = util.DeviceWeight(util.make_weight(w_bits, fmt))
     x = util.bf16_normal((16, K), 1.0, 32)
@@ -169,32 +186,35 @@ def test_wide_weight_rows_do_not_depend_on_batch(lx, fmt):
     ws = torch.empty(lx.lx_gemm_workspace_bytes(16, K, 0), dtype=torch.uint8, device="cuda")
     assert util.gemv(lx, x_dev, abi.BF16, K, dw, big, abi.F32, N, 16, N, K, fn="lx_gemm_w", workspace=ws) == 0
     want = util.host(big).view(np.uint32)
-    for M in (1, 2, 5, 8):
+    for M in (1, 5, 8, 9):
         y = torch.full((M, N), float("nan"), device="cuda")
-        assert util.gemv(lx, x_dev, abi.BF16, K, dw, y, abi.F32, N, M, N, K) == 0
+        assert util.gemv(lx, x_dev, abi.BF16, K, dw, y, abi.F32, N, M, N, K, fn="lx_gemm_w", workspace=ws) == 0
         assert np.array_equal(util.host(y).view(np.uint32), want[:M]), f"rows at M={M} differ from the same rows at M=16"
     util.check_status(lx)
 
 
 @pytest.mark.parametrize("fmt", FORMATS, ids=lambda f: NAMES[f])
-@pytest.mark.parametrize("K", [2048, 4096], ids=["K2048", "K4096"])  # 8 rows of K = 4096 need the large activation buffer
-def test_rows_do_not_depend_on_batch_and_runs_repeat(lx, fmt, K):
-    N = 256
+@pytest.mark.parametrize("K", [2048, 4096], ids=["K2048", "K4096"])
+@pytest.mark.parametrize("x_f32", [False, True], ids=["xbf16", "xf32"])
+@pytest.mark.parametrize("N", [256, 2500])
+def test_rows_do_not_depend_on_batch_and_runs_repeat(lx, fmt, K, x_f32, N):
+    """A row's bits are the same at every M = 1..8, for bf16 and for f32 activations, whether the weight is a few rows
+    (one short unit per CTA) or thousands, and a second run repeats the first bit for bit."""
     w_bits = util.bf16_normal((N, K), 0.02, 11)
     wt = util.make_weight(w_bits, fmt)
     dw = util.DeviceWeight(wt)
-    x = util.bf16_normal((8, K), 1.0, 12)
-    x_dev = util.dev(x)
+    x_dev = util.dev(util.f32_normal((8, K), 1.0, 12)) if x_f32 else util.dev(util.bf16_normal((8, K), 1.0, 12))
+    x_dt = abi.F32 if x_f32 else abi.BF16
     outs = {}
-    for M in (1, 2, 4, 8):
+    for M in range(1, 9):
         y = torch.full((M, N), float("nan"), device="cuda")
-        assert util.gemv(lx, x_dev, abi.BF16, K, dw, y, abi.F32, N, M, N, K) == 0
+        assert util.gemv(lx, x_dev, x_dt, K, dw, y, abi.F32, N, M, N, K) == 0
         outs[M] = util.host(y).view(np.uint32).copy()
     y2 = torch.full((8, N), float("nan"), device="cuda")
-    assert util.gemv(lx, x_dev, abi.BF16, K, dw, y2, abi.F32, N, 8, N, K) == 0
+    assert util.gemv(lx, x_dev, x_dt, K, dw, y2, abi.F32, N, 8, N, K) == 0
     util.check_status(lx)
     assert np.array_equal(outs[8], util.host(y2).view(np.uint32)), "two runs differ"
-    for M in (1, 2, 4):
+    for M in range(1, 8):
         assert np.array_equal(outs[M], outs[8][:M]), f"rows at M={M} differ from the same rows at M=8"
 
 
@@ -207,14 +227,14 @@ def test_bf16x_product_equals_bf16_product_bitwise(lx):
     w_bits[17, ::9] = O.f32_to_bf16_bits(np.float32([2.0**-90]))[0]
     dw16 = util.DeviceWeight(util.make_weight(w_bits, O.W_BF16))
     dwx = util.DeviceWeight(util.make_weight(w_bits, O.W_BF16X))
-    x_dev = util.dev(util.bf16_normal((8, K), 1.0, 6))
-    for M in (1, 8):
-        ya = torch.full((M, N), float("nan"), device="cuda")
-        yb = torch.full((M, N), float("nan"), device="cuda")
-        assert util.gemv(lx, x_dev, abi.BF16, K, dw16, ya, abi.F32, N, M, N, K) == 0
-        assert util.gemv(lx, x_dev, abi.BF16, K, dwx, yb, abi.F32, N, M, N, K) == 0
-        util.check_status(lx)
-        assert np.array_equal(util.host(ya).view(np.uint32), util.host(yb).view(np.uint32))
+    for x_dt, x_dev in ((abi.BF16, util.dev(util.bf16_normal((8, K), 1.0, 6))), (abi.F32, util.dev(util.f32_normal((8, K), 1.0, 6)))):
+        for M in (1, 5, 8):
+            ya = torch.full((M, N), float("nan"), device="cuda")
+            yb = torch.full((M, N), float("nan"), device="cuda")
+            assert util.gemv(lx, x_dev, x_dt, K, dw16, ya, abi.F32, N, M, N, K) == 0
+            assert util.gemv(lx, x_dev, x_dt, K, dwx, yb, abi.F32, N, M, N, K) == 0
+            util.check_status(lx)
+            assert np.array_equal(util.host(ya).view(np.uint32), util.host(yb).view(np.uint32))
 
 
 @pytest.mark.parametrize("fmt", FORMATS, ids=lambda f: NAMES[f])
