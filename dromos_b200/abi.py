@@ -82,10 +82,13 @@ EXTENSIONS = {
     "lx_b200_last_error": (c_int, []),
     "lx_b200_moe_experts_grouped_static": (c_int, [c_ptr, c_ptr, c_ptr, _W, _W, c_int, c_ptr, c_int, c_int, c_int, c_int, c_int, c_ptr]),
     "lx_b200_moe_static_scratch_bytes": (c_i64, []),
+    "lx_b200_moe_static_scratch_ptr": (c_ptr, []),
     # x, x_dtype, ld_x, w, bias, bias_dtype, y_all, arrivals, ranks, rank, col0, y_dtype, ld_y, M, N, K, alpha, workspace, arrivals_added, stream
     "lx_b200_linear_allgather": (c_int, [c_ptr, c_int, c_int, _W, c_ptr, c_int, c_ptr, c_ptr, c_int, c_int, c_i64, c_int, c_int, c_int, c_int,
                                          c_int, ctypes.c_float, c_ptr, c_ptr, c_ptr]),
     "lx_b200_wait_arrivals": (c_int, [c_ptr, c_int, c_ptr]),
+    # y_all, arrivals, ranks, rank, col0, cols, y_dtype, ld_y, M, stream
+    "lx_b200_exchange_slices": (c_int, [c_ptr, c_ptr, c_int, c_int, c_i64, c_int, c_int, c_int, c_int, c_ptr]),
 }
 ERR_SCRATCH = 804
 

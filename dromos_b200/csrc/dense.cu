@@ -90,7 +90,8 @@ int launch_dense_format(const StreamParams& P, cudaStream_t stream) {
       return cols <= 16 ? launch_stream<F, 16, 1, 2, 2, 2, 2, 64, kDense>(P, stream, P.N) : launch_stream<F, 16, 1, 2, 3, 2, 2, 64, kDense>(P, stream, P.N);
     } else if constexpr (F == LX_W_NVFP4) {
       if (cols <= 8) return big_x ? launch_stream<F, 16, 1, 4, 1, 2, 2, 64, kDense>(P, stream, P.N) : launch_stream<F, 16, 1, 4, 1, 2, 4, 16, kDense>(P, stream, P.N);
-      return cols <= 16 ? launch_stream<F, 16, 1, 4, 2, 2, 2, 64, kDense>(P, stream, P.N) : launch_stream<F, 16, 1, 4, 3, 2, 2, 64, kDense>(P, stream, P.N);
+      // (48 KB halves: with 64 KB the two-tile layout no longer fits an SM's shared memory)
+      return cols <= 16 ? launch_stream<F, 16, 1, 4, 2, 2, 2, 48, kDense>(P, stream, P.N) : launch_stream<F, 16, 1, 4, 3, 2, 2, 48, kDense>(P, stream, P.N);
     } else {
       if (cols <= 8) return big_x ? launch_stream<F, 8, 1, 2, 1, 2, 4, 64, kDense>(P, stream, P.N) : launch_stream<F, 8, 1, 2, 1, 2, 4, 16, kDense>(P, stream, P.N);
       return cols <= 16 ? launch_stream<F, 8, 1, 2, 2, 2, 4, 64, kDense>(P, stream, P.N) : launch_stream<F, 8, 1, 2, 3, 2, 4, 64, kDense>(P, stream, P.N);
@@ -381,6 +382,10 @@ extern "C" int lx_b200_wait_arrivals(int* counter, int total, void* stream) {
   return tc_wait_arrivals(counter, total, static_cast<cudaStream_t>(stream));
 }
 
+// The skinny decode GEMM's contract is that a row's bits depend on that row, the weight and the epilogue alone: not on
+// M, not on the row's place in the call (kernels.h:457-475). The decode GEMV gives exactly that for up to 8 rows, so
+// the call runs as chunks of 8 rows on it: every row of every M goes through the same kernel with the same K slices.
+// (Beyond 8 rows the chunks re-read the weight, from L2 where it fits; the engine itself never calls this entry point.)
 extern "C" int lx_gemm_skinny(const void* x, lx_dtype x_dtype, int ld_x, const lx_weight* w, const void* bias,
                               lx_dtype bias_dtype, void* y, lx_dtype y_dtype, int ld_y, int M, int N, int K, float alpha,
                               float beta, void* stream) {
@@ -389,7 +394,21 @@ extern "C" int lx_gemm_skinny(const void* x, lx_dtype x_dtype, int ld_x, const l
   if (!x || !y || !w->data) return kInvalid;
   if (!valid_dtype(y_dtype) || (bias && !valid_dtype(bias_dtype))) return kInvalid;
   if (w->type != LX_W_BF16 || x_dtype != LX_BF16 || N % 16 != 0 || K % 64 != 0) return kNotSupported;
-  return dense_product(x, x_dtype, ld_x, *w, bias, bias_dtype, y, y_dtype, ld_y, M, N, K, alpha, beta,
-                       static_cast<cudaStream_t>(stream));
+  if (!gemv_ok(*w, K, true)) return kNotSupported;
+  GemvParams G{};
+  G.w = static_cast<const uint8_t*>(w->data);
+  G.row_bytes = 2ll * K;
+  G.global = 1.0f;
+  G.N = N, G.K = K;
+  G.x_dtype = x_dtype, G.ld_x = ld_x;
+  G.bias = bias, G.bias_dtype = bias_dtype;
+  G.y_dtype = y_dtype, G.ld_y = ld_y;
+  G.alpha = alpha, G.beta = beta;
+  for (int m0 = 0; m0 < M; m0 += 8) {
+    G.M = std::min(8, M - m0);
+    G.x = static_cast<const uint8_t*>(x) + static_cast<int64_t>(m0) * ld_x * 2;
+    G.y = static_cast<uint8_t*>(y) + static_cast<int64_t>(m0) * ld_y * (y_dtype == LX_BF16 ? 2 : 4);
+    if (int e = launch_gemv<LX_W_BF16>(G, -1, static_cast<cudaStream_t>(stream))) return e;
+  }
+  return kOk;
 }
-

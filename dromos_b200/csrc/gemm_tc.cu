@@ -1028,14 +1028,14 @@ int tc_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const v
 // A counting semaphore: waits (bounded) until the counter holds at least `total` arrivals, then takes them. Arrivals of
 // a later round that come early stay in the counter, and nothing here depends on how often the call has run before, so
 // a captured graph can be replayed.
-__global__ void wait_arrivals_kernel(int* counter, int total, int* status) {
+__global__ void wait_arrivals_kernel(int* counter, int total, int* status, uint64_t budget_ns) {
   pdl_trigger();
   const uint64_t t0 = global_timer_ns();
   for (;;) {
     int v;
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
     if (v >= total) break;
-    if (global_timer_ns() - t0 > 1000000000ull) {  // a peer that never arrives: give up after a second and say so
+    if (global_timer_ns() - t0 > budget_ns) {  // a peer that never arrives: give up (after a second by default) and say so
       if (status) atomicExch(status, kStatusTcWait);
       return;
     }
@@ -1043,8 +1043,11 @@ __global__ void wait_arrivals_kernel(int* counter, int total, int* status) {
   asm volatile("red.relaxed.sys.global.add.s32 [%0], %1;" ::"l"(counter), "r"(-total) : "memory");
 }
 
+// LX_B200_WAIT_MS: how long a wait for peers may last before it gives up (default 1000; read on every call).
 int tc_wait_arrivals(int* counter, int total, cudaStream_t stream) {
-  return launch_kernel(wait_arrivals_kernel, dim3(1), dim3(1), 0, stream, counter, total, status_word());
+  uint64_t ms = 1000;
+  if (const char* v = std::getenv("LX_B200_WAIT_MS")) ms = static_cast<uint64_t>(std::max(1, std::min(10000, atoi(v))));
+  return launch_kernel(wait_arrivals_kernel, dim3(1), dim3(1), 0, stream, counter, total, status_word(), ms * 1000000ull);
 }
 
 // One pass (M <= 64 rows for bf16 activations) of BF16 / INT8 / FP8 weights whose outputs go straight into every rank's

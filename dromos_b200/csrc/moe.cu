@@ -556,6 +556,11 @@ int* static_scratch_status() {
 
 extern "C" int64_t lx_b200_moe_static_scratch_bytes(void) { return kStaticScratchBytes - kStaticHeaderBytes; }
 
+extern "C" void* lx_b200_moe_static_scratch_ptr(void) {
+  uint8_t* base = nullptr;
+  return static_scratch(&base) == kOk ? base : nullptr;
+}
+
 extern "C" int lx_b200_moe_experts_grouped_static(const void* latent, const int32_t* ids, const float* weights,
                                                   const lx_weight* gate_up, const lx_weight* down, lx_math math, float* out,
                                                   int T, int L, int I, int E, int top_k, void* stream) {

@@ -270,6 +270,65 @@ class ExpertParallel:
         return out
 
 
+class PeerBuffers:
+    """What the ranks of a row-sharded layer share: two whole-y buffers used in turn (so that a rank one call ahead never
+    overwrites the y a slower rank still reads) and the arrival counters, all torch symmetric memory (plain peer mappings,
+    multicast off), exchanged once at construction. One set serves any number of layers of the same output width."""
+
+    def __init__(self, N: int, max_rows: int, device, dtype=torch.float32, group=None):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        self.dist, self.group = dist, group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if self.world > 8:
+            raise RuntimeError("the exchange kernel addresses at most 8 ranks")
+        self.N, self.max_rows, self.dtype = N, max_rows, dtype
+        self.y = symm.empty((2, max_rows, N), dtype=dtype, device=device)
+        self.counter = symm.empty((64,), dtype=torch.int32, device=device)
+        self.counter.zero_()
+        hy, hc = symm.rendezvous(self.y, self.group), symm.rendezvous(self.counter, self.group)
+        self.y_ptrs, self.c_ptrs = [int(p) for p in hy.buffer_ptrs], [int(p) for p in hc.buffer_ptrs]
+        self.c_array = (ctypes.c_void_p * self.world)(*self.c_ptrs)
+        self.calls = 0
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+
+    def next_half(self) -> int:
+        half = self.calls & 1
+        self.calls += 1
+        return half
+
+    def y_array(self, half: int):
+        stride = self.max_rows * self.N * self.y.element_size()
+        return (ctypes.c_void_p * self.world)(*[p + half * stride for p in self.y_ptrs])
+
+
+class PeerShardedLinear:
+    """ShardedLinear without the collective library: the product writes this rank's columns straight into its own copy of
+    the whole y, and lx_b200_exchange_slices (one kernel: peer stores over NVLink, one arrival per rank, a bounded wait)
+    makes every rank's copy whole. Any weight format and row count: the product is the plain Linear."""
+
+    def __init__(self, lib, stored: StoredWeight, N: int, K: int, buffers: PeerBuffers):
+        self.lib, self.buf, self.N, self.K = lib, buffers, N, K
+        self.n0, self.n1 = shard_rows(N, buffers.rank, buffers.world)
+        self.local = Linear(lib, stored, self.n1 - self.n0, K)
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        """x: bf16 or f32 [M, K], the same on every rank. Returns this rank's whole y [M, N] (valid on the stream)."""
+        M, b = x.shape[0], self.buf
+        assert M <= b.max_rows
+        half = b.next_half()
+        self.local(x, b.y[half, :M, self.n0:self.n1])
+        y_dt = abi.BF16 if b.dtype == torch.bfloat16 else abi.F32
+        st = self.lib.lx_b200_exchange_slices(b.y_array(half), b.c_array, b.world, b.rank, self.n0, self.n1 - self.n0, y_dt, self.N, M,
+                                              _stream())
+        if st:
+            raise RuntimeError(f"lx_b200_exchange_slices failed: {st}")
+        return b.y[half, :M]
+
+
 class FusedShardedLinear:
     """ShardedLinear without the collective: every rank's product stores its slice of y straight into every rank's copy
     of the whole y (lx_b200_linear_allgather: NVLink stores from the kernel's epilogue through peer-mapped pointers) and

@@ -193,6 +193,17 @@ LX_API int lx_b200_linear_allgather(const void* x, lx_dtype x_dtype, int ld_x, c
                                     lx_dtype y_dtype, int ld_y, int M, int N, int K, float alpha, void* workspace,
                                     int* arrivals_added, void* stream);
 LX_API int lx_b200_wait_arrivals(int* counter, int total, void* stream);
+/* The all-gather of a row-sharded product's outputs as one kernel, for any product entry point (no counterpart in the
+ * reference, which is single-GPU). Rank `rank` has written its slice, columns col0 .. col0 + cols - 1 of the whole
+ * [M, ld_y] output, into its own buffer y_all[rank] (e.g. lx_gemv_w with y pointing at that column and ld_y as the row
+ * stride); the call stores the slice into every other rank's y_all[r] (host array of `ranks` peer-mapped device pointers),
+ * adds one arrival to every rank's semaphore arrivals[r][0] (arrivals[r]: two int32 words, peer-mapped, zero before the
+ * first call; word 1 is rank r's own) and waits until this rank's semaphore holds `ranks` arrivals, which it takes: when
+ * the kernel is done this rank's y is whole. The wait is bounded (LX_B200_WAIT_MS, default 1000); a wait that gives up
+ * shows as 6 in lx_b200_last_error. Every rank must make the call once per round; callers alternate two y buffers so
+ * that a rank one round ahead never overwrites what a slower rank still reads. */
+LX_API int lx_b200_exchange_slices(void* const* y_all, int* const* arrivals, int ranks, int rank, int64_t col0, int cols,
+                                   lx_dtype y_dtype, int ld_y, int M, void* stream);
 
 /* Routed experts for callers that must not allocate. No counterpart in the reference: its lx_moe_experts_grouped always
  * takes a caller workspace. Same arguments, result and error codes as lx_moe_experts_grouped above minus the workspace:
@@ -203,12 +214,17 @@ LX_API int lx_b200_wait_arrivals(int* counter, int total, void* stream);
  * each device looks the array's device address up (cudaGetSymbolAddress, with that device current) and keeps it; make
  * that first call outside any stream capture. All calls on a device share the one array, which keeps whatever the last
  * call left in it (nothing in it needs to start at zero): calls that overlap on the GPU, on any streams, race on it and
- * are the caller's to serialize. */
+ * are the caller's to serialize. A bounded wait that gives up inside this call shows in lx_b200_last_error() like any
+ * other. */
 #define LX_B200_ERR_SCRATCH 804
 LX_API int lx_b200_moe_experts_grouped_static(const void* latent, const int32_t* ids, const float* weights,
                                               const lx_weight* gate_up, const lx_weight* down, lx_math math, float* out,
                                               int T, int L, int I, int E, int top_k, void* stream);
 LX_API int64_t lx_b200_moe_static_scratch_bytes(void);
+/* The device address of that array on the current device (null if the lookup fails). Its first 256 bytes are a header:
+ * word 0 is the status word this entry point's kernels write when one of their bounded waits gives up;
+ * lx_b200_last_error() reads and clears it together with the library's own status word. */
+LX_API void* lx_b200_moe_static_scratch_ptr(void);
 
 #ifdef __cplusplus
 }

@@ -53,14 +53,27 @@ def test_quantize_weight_bytes_and_dequantized_values(lx, wtype, rows, K):
 
 
 def test_nvfp4_tie_cases(lx):
-    # a block whose values sit exactly on e2m1 midpoints: ties go to the even code (reference test_quant.py:107-126)
+    """The reference's own known answer (tests/kernels/test_quant.py:107-126): a block with amax 2688 sets the global to 1;
+    a block with amax 12 gets the e4m3 scale 2 (byte 0x40) and its values / 2 sit on midpoints of the e2m1 grid: ties go
+    to the even code, and -0.25 rounds to a zero stored without a sign. Asserted as literal bytes on the GPU quantizer
+    and on the oracle."""
     K = 16
-    vals = np.zeros((1, K), dtype=np.float32)
-    vals[0, :8] = [2688.0, 0.25 * 448, 0.75 * 448, 1.25 * 448, 1.75 * 448, 2.5 * 448, 3.5 * 448, 5.0 * 448]
+    vals = np.zeros((2, K), dtype=np.float32)
+    vals[0, 0] = 2688.0
+    vals[1, 0] = 12.0
+    vals[1, 1:8] = [0.5, 1.5, 2.5, 3.5, 5.0, 7.0, 10.0]
+    vals[1, 8:15] = [-0.5, -1.5, -2.5, -3.5, -5.0, -7.0, -10.0]
     w = O.f32_to_bf16_bits(vals)
     want = O.quantize_weight(w, O.W_NVFP4)
-    assert float(want.glob) == 1.0 and want.scale[0, 0] == 0x7E or True
     data, scale, lw = quantize_on_gpu(lx, w, O.W_NVFP4)
+    for name, d, sc, g in (("oracle", want.data.reshape(2, K // 2), want.scale.reshape(2, 1), float(want.glob)),
+                           ("gpu", util.host(data).reshape(2, K // 2), util.host(scale).reshape(2, 1), float(lw.glob))):
+        assert g == 1.0, f"{name}: global {g}"
+        codes = np.stack([d & 15, d >> 4], axis=-1).reshape(2, K)
+        assert codes[1, 0] == 7, f"{name}: 12 / 2 is 6, the largest code"
+        assert codes[1, 1:8].tolist() == [0, 2, 2, 4, 4, 6, 6], f"{name}: positive ties {codes[1, 1:8].tolist()}"
+        assert codes[1, 8:15].tolist() == [0, 8 + 2, 8 + 2, 8 + 4, 8 + 4, 8 + 6, 8 + 6], f"{name}: negative ties {codes[1, 8:15].tolist()}"
+        assert int(sc[1, 0]) == 0x40, f"{name}: block scale byte {int(sc[1, 0]):#x}"
     assert np.array_equal(util.host(data), want.data.reshape(-1))
     assert np.array_equal(util.host(scale), want.scale.reshape(-1))
 

@@ -27,7 +27,7 @@ def case(T, L, I, E, top_k, wtype, seed):
     return gu, dn, latent, ids, weights
 
 
-@pytest.mark.parametrize("wtype", [O.W_FP8, O.W_BF16])
+@pytest.mark.parametrize("wtype", [O.W_FP8, O.W_BF16, O.W_NVFP4])
 def test_static_scratch_matches_workspace_entry_point_twice(lx, wtype):
     T, L, I, E, top_k = 32, 512, 256, 16, 4
     results = []
@@ -49,6 +49,59 @@ def test_static_scratch_matches_workspace_entry_point_twice(lx, wtype):
         util.assert_close(g, O.moe_experts_reference(latent, ids, weights, gu, dn, I), what=f"call {call}")
         results.append(g)
     assert not np.array_equal(results[0], results[1])  # the two calls really were different problems
+
+
+def test_static_scratch_call_allocates_nothing(lx):
+    """What the entry point is for: after a first call (which looks the array up), further calls neither take nor give
+    back device memory, and they can be captured in a graph (a capture refuses cudaMalloc)."""
+    T, L, I, E, top_k = 16, 512, 256, 8, 2
+    gu, dn, latent, ids, weights = case(T, L, I, E, top_k, O.W_FP8, 3)
+    dgu, ddn = util.DeviceWeight(gu), util.DeviceWeight(dn)
+    latent_d, ids_d, weights_d = util.dev(latent), util.dev(ids), util.dev(weights)
+    out = torch.full((T, L), float("nan"), device="cuda")
+
+    def call():
+        assert lx.lx_b200_moe_experts_grouped_static(abi.ptr(latent_d), abi.ptr(ids_d), abi.ptr(weights_d), dgu.ref(), ddn.ref(),
+                                                     abi.MATH_BF16, abi.ptr(out), T, L, I, E, top_k, util.stream_ptr()) == 0
+
+    call()  # the first call on the device: address lookup, function attributes
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the device's free memory"
+    first = util.host(out).copy()
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        out.fill_(float("nan"))
+        with torch.cuda.graph(g, stream=side):
+            call()
+        g.replay()
+    torch.cuda.synchronize()
+    assert np.array_equal(util.host(out).view(np.uint32), first.view(np.uint32))
+    util.check_status(lx)
+
+
+def test_static_scratch_status_word_is_reported(lx):
+    """A bounded wait that gives up inside this entry point leaves its code in the array's first word, not in the
+    library's own status word: lx_b200_last_error() must report and clear both. The test plants a code there (nothing
+    is made to time out) and reads it back through the public call."""
+    import ctypes
+
+    base = lx.lx_b200_moe_static_scratch_ptr()
+    assert base, "the array's address could not be looked up"
+    assert lx.lx_b200_last_error() == 0
+    planted = torch.tensor([5], dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    cudart = ctypes.CDLL("libcudart.so.12")  # the runtime the library itself is linked against (already loaded)
+    cudart.cudaMemcpy.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
+    cudart.cudaMemcpy.restype = ctypes.c_int
+    assert cudart.cudaMemcpy(base, planted.data_ptr(), 4, 3) == 0  # device to device: 4 bytes into word 0 of the array
+    torch.cuda.synchronize()
+    assert lx.lx_b200_last_error() == 5, "the static array's status word was not read"
+    assert lx.lx_b200_last_error() == 0, "the status word was not cleared"
 
 
 def test_static_scratch_refuses_what_does_not_fit(lx):
