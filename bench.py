@@ -233,6 +233,7 @@ def cpu_moe(name, steps, warmup):
     latent = _bf16_normal_host(rng, (T, L), 1.0)
     logits = [rng.standard_normal((T, E), dtype=np.float32) for _ in range(8)]
     ids, wts = np.zeros((T, top_k), dtype=np.int32), np.zeros((T, top_k), dtype=np.float32)
+    ent, conf = np.zeros(T, dtype=np.float32), np.zeros(T, dtype=np.float32)
     out = np.zeros((T, L), dtype=np.float32)
     ws = np.zeros(max(256, lib.lx_moe_grouped_workspace_bytes(T, L, I, E, top_k, abi.MATH_BF16)), dtype=np.uint8)
     per_expert = (2 * I * L + L * I) + 4 * (2 * I + L)
@@ -240,7 +241,7 @@ def cpu_moe(name, steps, warmup):
 
     def step(i):
         lg = logits[i % len(logits)]
-        assert lib.lx_moe_route(abi.ptr(lg), None, abi.ptr(ids), abi.ptr(wts), None, None, T, E, top_k, None) == 0
+        assert lib.lx_moe_route(abi.ptr(lg), None, abi.ptr(ids), abi.ptr(wts), abi.ptr(ent), abi.ptr(conf), T, E, top_k, None) == 0
         assert lib.lx_moe_experts_grouped(abi.ptr(latent), abi.ptr(ids), abi.ptr(wts), ctypes.byref(gu), ctypes.byref(dn), abi.MATH_BF16,
                                           abi.ptr(out), abi.ptr(ws), T, L, I, E, top_k, None) == 0
         return len(np.unique(ids))
@@ -259,7 +260,10 @@ def cpu_moe(name, steps, warmup):
 def cpu_leg(name, steps, warmup):
     if cpu_library() is None:
         return {"value": None, "unit": "TB/s", "cores": os.cpu_count(), "kind": "reference", "sample": "oracle/_ref/libdromos_cpu.so not built"}, None
-    tbs, ms, cores, sample = (cpu_moe if name in MOE else cpu_dense)(name, steps, warmup)
+    try:
+        tbs, ms, cores, sample = (cpu_moe if name in MOE else cpu_dense)(name, steps, warmup)
+    except Exception as exc:  # a reported baseline: its failure is recorded beside the GPU numbers, which stay valid
+        return {"value": None, "unit": "TB/s", "cores": os.cpu_count(), "kind": "reference", "sample": f"failed: {type(exc).__name__}: {exc}"[:200]}, None
     return {"value": tbs, "unit": "TB/s", "cores": cores, "kind": "reference", "sample": sample}, ms
 
 

@@ -54,6 +54,10 @@ __device__ __forceinline__ void store_from_f32(void* p, int dtype, int64_t i, fl
 }
 // One e4m3 byte as f32, exact (the byte's 7 magnitude bits placed at f32 bits 20..26 and rebased by 2^120;
 // subnormals come out right because f32 subnormals scale the same way).
+// Nearest e4m3 (ties to even), magnitudes beyond 448 saturate.
+__device__ __forceinline__ uint32_t e4m3_encode(float v) {
+  return static_cast<uint32_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
 __device__ __forceinline__ float e4m3_to_f32(uint32_t b) {
   const float mag = __uint_as_float((b & 0x7fu) << 20) * 0x1p120f;
   return (b & 0x80u) ? -mag : mag;

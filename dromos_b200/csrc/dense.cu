@@ -342,13 +342,20 @@ extern "C" int lx_gemm_w(const void* x, lx_dtype x_dtype, int ld_x, const lx_wei
   if (!valid_dtype(x_dtype) || !valid_dtype(y_dtype) || (bias && !valid_dtype(bias_dtype))) return kInvalid;
   if (math < LX_MATH_BF16 || math > LX_MATH_FP4) return kInvalid;
   if (w->type < LX_W_BF16 || w->type > LX_W_NVFP4) return kNotSupported;
-  if (math != LX_MATH_BF16) return kNotSupported;  // activations stay bf16: weight-only products
+  if (int e = math_admitted(math, w->type)) return e;
+  const bool quantized = math != LX_MATH_BF16;
   if (w->type != LX_W_BF16 && !w->scale) return kInvalid;
   // Weight rows must be whole 16-byte chunks, as for the reference's tensor-core kernels.
   const int64_t rowb = row_bytes_of(w->type, K);
   if (rowb % 16 != 0 || !aligned(w->data, 16) || (w->type == LX_W_NVFP4 && K % 64 != 0)) return kNotSupported;
   // With a workspace every row count goes through the tcgen05 product, so that within this entry point a row's bits
   // do not depend on M. LX_B200_TC=0 keeps the mma.sync kernels.
+  if (quantized) {  // activations quantized per token into the workspace, then s8 x s8 -> s32 or e4m3 x e4m3 -> f32 on the tensor cores
+    if (!workspace) return kInvalid;
+    if (!tc_enabled() || !aligned(workspace, 16)) return kNotSupported;
+    return tc_product(x, x_dtype, ld_x, *w, bias, bias_dtype, y, y_dtype, ld_y, M, N, K, alpha, beta, workspace,
+                      static_cast<cudaStream_t>(stream), true);
+  }
   if (tc_enabled() && workspace && aligned(workspace, 16) && (w->type != LX_W_NVFP4 || (K % 256 == 0 && aligned(w->scale, 16))))
     return tc_product(x, x_dtype, ld_x, *w, bias, bias_dtype, y, y_dtype, ld_y, M, N, K, alpha, beta, workspace,
                       static_cast<cudaStream_t>(stream));

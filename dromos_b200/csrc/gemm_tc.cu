@@ -82,7 +82,10 @@ struct TcLayout {
 // is found by every block of the row again (the row is a few KB, from L2), which saves a second kernel. Plane j of
 // row u is column j * Mp + u. k past K is written as zero up to the end of the last stage; columns that no row owns
 // are never written (their accumulator columns are never read).
-template <int ACT, bool XBF>
+// QUANT (int8 / e4m3 only): the low-precision maths of lx_gemm_w. The row is quantized once, as lx_quantize_act does
+// (scale = max|x| / 127 or / 448, values rounded to nearest even and clamped; engine/cuda/quant.cu), into ONE plane,
+// and the row's sums are multiplied by that scale.
+template <int ACT, bool XBF, bool QUANT = false>
 __global__ void __launch_bounds__(128) tc_prep_kernel(const void* __restrict__ x, int ld_x, int rows, int K, int NC, int Mp, int planes,
                                                       uint8_t* __restrict__ out, float* __restrict__ inv_scales, int n_stages) {
   constexpr int kElem = act_elem(ACT), V = 16 / kElem, kKS = ks_of(ACT);
@@ -97,17 +100,24 @@ __global__ void __launch_bounds__(128) tc_prep_kernel(const void* __restrict__ x
   // this thread's values first (the loads are in flight while the row's largest magnitude is found)
   float v[V];
   if (in_range) load_values<XBF, V>(x, row, k0, K, aligned16, v);
-  float sc = 1.0f;
+  float sc = 1.0f, back = 1.0f;
   if constexpr (ACT != kActBf16) {
     float a = warp_max(row_max_share<XBF>(x, row, K, aligned16, tid, 128));
     if ((tid & 31) == 0) part[tid >> 5] = a;
     __syncthreads();
-    sc = scale_of<ACT>(fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])));
+    a = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
+    if constexpr (QUANT) {
+      quant_scales<ACT>(a, sc, back);
+    } else {
+      sc = scale_of<ACT>(a);
+      back = 1.0f / sc;
+    }
   }
-  if (blockIdx.x == 0 && tid == 0) inv_scales[u] = 1.0f / sc;
+  if (blockIdx.x == 0 && tid == 0) inv_scales[u] = back;
   if (!in_range) return;
   uint32_t w[3][4];
-  make_planes<ACT, XBF, V>(v, sc, w);
+  if constexpr (QUANT) quantize_plane<ACT>(v, sc, w[0]);
+  else make_planes<ACT, XBF, V>(v, sc, w);
   uint8_t* block = out + static_cast<size_t>(k0 / kKS) * (static_cast<size_t>(NC) * kKS * kElem);
   const int kb = (k0 % kKS) * kElem;
   for (int j = 0; j < planes; ++j) *reinterpret_cast<uint4*>(block + block_offset(NC, kb, j * Mp + u)) = make_uint4(w[j][0], w[j][1], w[j][2], w[j][3]);
@@ -924,12 +934,12 @@ int rows_per_pass(int act, bool x_bf16) { return (act == kActBf16 && !x_bf16) ? 
 
 // Fills what every pass shares.
 TcParams base_params(const lx_weight& w, const void* bias, int bias_dtype, int y_dtype, int ld_y, int N, int K, float alpha, float beta,
-                     int act, bool x_bf16, int rows) {
+                     int act, bool x_bf16, int rows, bool quantized = false) {
   TcParams P{};
   P.scale = static_cast<const uint8_t*>(w.scale);
   P.global = w.global;
   P.N = N, P.K = K, P.M = rows;
-  P.planes = act_planes(act, x_bf16);
+  P.planes = quantized ? 1 : act_planes(act, x_bf16);
   P.digit = act == kActS8 ? 0.0078125f : act == kActE4m3 ? 0.0625f : 1.0f;
   P.Mp = (rows + 7) / 8 * 8;
   P.NC = (P.planes * P.Mp + 15) / 16 * 16;
@@ -977,17 +987,19 @@ int tc_product_rows(const void* x, int x_dtype, int ld_x, const lx_weight& w, co
   return kNotSupported;
 }
 
-// The product, in passes of at most 64 activation rows. workspace: at least tc_workspace_bytes.
+// The product, in passes of at most 64 activation rows. workspace: at least tc_workspace_bytes. quantized (INT8 and
+// FP8 weights only): activations quantized per row to the weight's number type instead of split into exact digits.
 int tc_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const void* bias, int bias_dtype, void* y, int y_dtype,
-               int ld_y, int M, int N, int K, float alpha, float beta, void* workspace, cudaStream_t stream) {
+               int ld_y, int M, int N, int K, float alpha, float beta, void* workspace, cudaStream_t stream, bool quantized) {
   const bool x_bf16 = x_dtype == LX_BF16;
+  if (quantized && w.type != LX_W_INT8 && w.type != LX_W_FP8) return kNotSupported;
   const int act = act_of(w.type), elem = act_elem(act), kKS = ks_of(act);
   const int per_pass = rows_per_pass(act, x_bf16);
   const int n_stages = (K + kKS - 1) / kKS;
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   for (int m0 = 0; m0 < M; m0 += per_pass) {
     const int rows = std::min(per_pass, M - m0);
-    TcParams P = base_params(w, bias, bias_dtype, y_dtype, ld_y, N, K, alpha, beta, act, x_bf16, rows);
+    TcParams P = base_params(w, bias, bias_dtype, y_dtype, ld_y, N, K, alpha, beta, act, x_bf16, rows, quantized);
     const TcLayout L(P.NC, act, n_stages);
     P.xprep = ws;
     P.inv_scales = reinterpret_cast<const float*>(ws + L.scales);
@@ -1000,6 +1012,10 @@ int tc_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const v
                            reinterpret_cast<float*>(ws + L.scales), n_stages);
     };
     int pe;
+    if (quantized) {
+      if (act == kActS8) pe = x_bf16 ? prep(tc_prep_kernel<kActS8, true, true>) : prep(tc_prep_kernel<kActS8, false, true>);
+      else pe = x_bf16 ? prep(tc_prep_kernel<kActE4m3, true, true>) : prep(tc_prep_kernel<kActE4m3, false, true>);
+    } else
     switch (act * 2 + (x_bf16 ? 1 : 0)) {
       case kActBf16 * 2: pe = prep(tc_prep_kernel<kActBf16, false>); break;
       case kActBf16 * 2 + 1: pe = prep(tc_prep_kernel<kActBf16, true>); break;

@@ -155,9 +155,24 @@ int launch_stream(StreamParams P, cudaStream_t stream, int64_t stack_rows) {
   return launch_kernel(kernel, dim3(grid), dim3(C::kThreads), smem, stream, wmap, smap, P);
 }
 
+// Which (math, stored format) pairs lx_gemm_w and lx_moe_experts_grouped compute, decided as the reference decides it
+// (lernex/dromos engine/cuda/gemm_w.cuh:274-289): nothing below architecture 80; BF16 math with every format; INT8 math
+// with INT8 weights; FP8 math with FP8 weights from architecture 89. FP8 math on NVFP4 weights and FP4 math are products
+// of the 12x parts only. 0 = admitted, else the error to return. lx_arch() honours the architecture override.
+inline int math_admitted(int math, int wtype) {
+  const int arch = lx_arch();
+  if (arch < 80) return kNotSupported;
+  switch (math) {
+    case LX_MATH_BF16: return kOk;
+    case LX_MATH_INT8: return wtype == LX_W_INT8 ? kOk : kNotSupported;
+    case LX_MATH_FP8: return wtype == LX_W_FP8 && arch >= 89 ? kOk : kNotSupported;
+    default: return kNotSupported;
+  }
+}
+
 // gemm_tc.cu: the tcgen05 product for batched decode rows, and the workspace its prepared activations need.
 int tc_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const void* bias, int bias_dtype, void* y, int y_dtype,
-               int ld_y, int M, int N, int K, float alpha, float beta, void* workspace, cudaStream_t stream);
+               int ld_y, int M, int N, int K, float alpha, float beta, void* workspace, cudaStream_t stream, bool quantized = false);
 int64_t tc_workspace_bytes(int M, int K);
 bool tc_enabled();
 // Where the all-gather epilogue of a sharded product stores: every rank's copy of the whole y and arrival counter.
@@ -187,7 +202,7 @@ bool experts_tc_ok(const lx_weight& gate_up, const lx_weight& down, int L, int I
 int64_t experts_tc_workspace(int64_t base, int P, int E, int L, int I);
 int experts_tc(const void* latent, const float* weights, const lx_weight& gate_up, const lx_weight& down, const int32_t* offsets,
                const int32_t* pairs, uint16_t* mid, float* rows, uint8_t* ws, int64_t base, int T, int L, int I, int E, int top_k,
-               int* status, cudaStream_t stream);
+               int* status, cudaStream_t stream, bool quantized = false);
 bool tc_rows_ok(const lx_weight& w, int N, int K);
 bool gemv_shape_ok(int wtype, int K, bool x_bf16);
 bool tc_rows_shape_ok(int wtype, int N, int K);

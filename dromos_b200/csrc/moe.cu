@@ -398,7 +398,7 @@ int launch_expert_stage(const StreamParams& P, int type, cudaStream_t s, int64_t
 int run_experts(const void* latent, const int32_t* ids, const float* weights, const lx_weight& gate_up, const lx_weight& down,
                 float* out,
                 uint8_t* ws, const Layout& l, bool indirect, int groups, int experts, int T, int L, int I, int top_k,
-                cudaStream_t s, int* status = nullptr) {
+                cudaStream_t s, int* status = nullptr, bool quantized = false) {
   StreamParams g{};
   g.w = static_cast<const uint8_t*>(gate_up.data);
   g.scale = static_cast<const uint8_t*>(gate_up.scale);
@@ -421,12 +421,13 @@ int run_experts(const void* latent, const int32_t* ids, const float* weights, co
   if (!indirect && experts_tc_ok(gate_up, down, L, I)) {
     if (int e = experts_tc(latent, weights, gate_up, down, reinterpret_cast<const int32_t*>(ws + l.offsets),
                            reinterpret_cast<const int32_t*>(ws + l.pairs), reinterpret_cast<uint16_t*>(ws + l.mid),
-                           reinterpret_cast<float*>(ws + l.rows), ws, l.total, T, L, I, experts, top_k, g.status, s))
+                           reinterpret_cast<float*>(ws + l.rows), ws, l.total, T, L, I, experts, top_k, g.status, s, quantized))
       return e;
     const int64_t n = static_cast<int64_t>(T) * L;
     return launch_kernel(ordered_sum_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, s,
                          reinterpret_cast<const float*>(ws + l.rows), out, T, L, top_k);
   }
+  if (quantized) return kNotSupported;  // the low-precision maths exist on the tensor-core kernels only
   // weights the streaming kernel cannot take run both stages on the scalar kernels (intermediate rows by pair index)
   const bool fast_gu = stack_streams(gate_up, L) && stack_streams(down, I), fast_dn = fast_gu;
   if (int e = fast_gu ? launch_expert_stage<kGateUp>(g, gate_up.type, s, static_cast<int64_t>(experts) * 2 * I)
@@ -490,11 +491,16 @@ extern "C" int lx_moe_experts_grouped(const void* latent, const int32_t* ids, co
   if (math < LX_MATH_BF16 || math > LX_MATH_FP4) return kInvalid;
   if (T == 0) return kOk;
   if (!latent || !ids || !weights || !out || !workspace || !gate_up->data || !down->data) return kInvalid;
-  if ((gate_up->type != LX_W_BF16 && !gate_up->scale) || (down->type != LX_W_BF16 && !down->scale)) return kInvalid;
-  if (E > kMaxExperts || static_cast<int64_t>(T) * top_k > (1ll << 30)) return kNotSupported;
+  // formats this entry point does not take (the lossless BF16X among them) are "not supported", whatever their scale pointers
   if (gate_up->type < LX_W_BF16 || gate_up->type > LX_W_NVFP4 || down->type < LX_W_BF16 || down->type > LX_W_NVFP4)
     return kNotSupported;
-  if (math != LX_MATH_BF16) return kNotSupported;  // activations stay bf16: weight-only products
+  if ((gate_up->type != LX_W_BF16 && !gate_up->scale) || (down->type != LX_W_BF16 && !down->scale)) return kInvalid;
+  if (E > kMaxExperts || static_cast<int64_t>(T) * top_k > (1ll << 30)) return kNotSupported;
+  // One math for both stages, admitted per stack as lx_gemm_w admits it (engine/cuda/moe_grouped.cu:400-402).
+  const bool quantized = math != LX_MATH_BF16;
+  if (int e = math_admitted(math, gate_up->type)) return e;
+  if (int e = math_admitted(math, down->type)) return e;
+  if (quantized && !experts_tc_ok(*gate_up, *down, L, I)) return kNotSupported;
   if (I % 8 != 0 || L % 8 != 0) return kNotSupported;
   if (gate_up->type == LX_W_NVFP4 && (L % 16 != 0 || I % 16 != 0)) return kInvalid;
   auto s = static_cast<cudaStream_t>(stream);
@@ -505,7 +511,7 @@ extern "C" int lx_moe_experts_grouped(const void* latent, const int32_t* ids, co
   if (int e = launch_kernel(group_kernel, dim3(1), dim3(1024), 0, s, ids, P, E, reinterpret_cast<int32_t*>(ws + l.offsets),
                             reinterpret_cast<int32_t*>(ws + l.pairs), chunks))
     return e;
-  return run_experts(latent, ids, weights, *gate_up, *down, out, ws, l, false, E, E, T, L, I, top_k, s);
+  return run_experts(latent, ids, weights, *gate_up, *down, out, ws, l, false, E, E, T, L, I, top_k, s, nullptr, quantized);
 }
 
 // ---- the same routed experts with no allocation anywhere -------------------------------------------------------------

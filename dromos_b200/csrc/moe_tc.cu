@@ -58,7 +58,8 @@ struct ExpertParams {
 // ---- activation blocks of the chunks -----------------------------------------------------------------------------------
 // Block (k piece, sorted position u): as tc_prep_kernel, but the row is gathered (src row = pairs[u] / top_k for the
 // latent, u itself for the intermediate rows) and goes to column pos_col[u] of its chunk's blocks.
-template <int ACT>
+// QUANT: one plane of per-row quantized values (the low-precision maths) instead of exact digits.
+template <int ACT, bool QUANT = false>
 __global__ void __launch_bounds__(128) expert_prep_kernel(const uint16_t* __restrict__ src, int ld, int top_k_or_0, int K, int NC,
                                                           const int32_t* __restrict__ pairs, const int32_t* __restrict__ pos_chunk,
                                                           const int32_t* __restrict__ pos_col, uint8_t* __restrict__ out, int64_t chunk_stride,
@@ -74,20 +75,27 @@ __global__ void __launch_bounds__(128) expert_prep_kernel(const uint16_t* __rest
   const bool aligned16 = (reinterpret_cast<uintptr_t>(src) & 15) == 0 && ld % 8 == 0;
   float v[V];
   if (in_range) load_values<true, V>(src, row, k0, K, aligned16, v);
-  float sc = 1.0f;
+  float sc = 1.0f, back = 1.0f;
   if constexpr (ACT != kActBf16) {
     float a = warp_max(row_max_share<true>(src, row, K, aligned16, tid, 128));
     if ((tid & 31) == 0) part[tid >> 5] = a;
     __syncthreads();
-    sc = scale_of<ACT>(fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])));
+    a = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
+    if constexpr (QUANT) {
+      quant_scales<ACT>(a, sc, back);
+    } else {
+      sc = scale_of<ACT>(a);
+      back = 1.0f / sc;
+    }
   }
-  if (blockIdx.x == 0 && tid == 0) inv_scales[u] = 1.0f / sc;
+  if (blockIdx.x == 0 && tid == 0) inv_scales[u] = back;
   if (!in_range) return;
   uint32_t w[3][4];
-  make_planes<ACT, true, V>(v, sc, w);
+  if constexpr (QUANT) quantize_plane<ACT>(v, sc, w[0]);
+  else make_planes<ACT, true, V>(v, sc, w);
   uint8_t* block = out + pos_chunk[u] * chunk_stride + static_cast<size_t>(k0 / kKS) * (static_cast<size_t>(NC) * kKS * kElem);
   const int kb = (k0 % kKS) * kElem, col = pos_col[u];
-  constexpr int planes = ACT == kActS8 ? 3 : ACT == kActE4m3 ? 2 : 1;
+  constexpr int planes = QUANT ? 1 : ACT == kActS8 ? 3 : ACT == kActE4m3 ? 2 : 1;
 #pragma unroll
   for (int j = 0; j < planes; ++j)
     *reinterpret_cast<uint4*>(block + block_offset(NC, kb, j * kChunkRows + col)) = make_uint4(w[j][0], w[j][1], w[j][2], w[j][3]);
@@ -395,7 +403,7 @@ bool experts_tc_ok(const lx_weight& gate_up, const lx_weight& down, int L, int I
 // caller's workspace like `tc_ws`, the region ExpertTcLayout describes.
 int experts_tc(const void* latent, const float* weights, const lx_weight& gate_up, const lx_weight& down, const int32_t* offsets,
                const int32_t* pairs, uint16_t* mid, float* rows, uint8_t* ws, int64_t base, int T, int L, int I, int E, int top_k,
-               int* status, cudaStream_t stream) {
+               int* status, cudaStream_t stream, bool quantized) {
   const int P = T * top_k;
   const ExpertTcLayout lay(base, P, E, L, I);
   int32_t* n_chunks = reinterpret_cast<int32_t*>(ws + lay.n_chunks);
@@ -408,7 +416,8 @@ int experts_tc(const void* latent, const float* weights, const lx_weight& gate_u
   uint8_t* xprep = ws + lay.xprep;
   (void)offsets;  // the chunk tables were written together with the grouping tables (group_kernel)
   const int act = act_of(gate_up.type), elem = act_elem(act), KS = ks_of(act);
-  const int planes = act_planes(act, true);
+  if (quantized && act != kActS8 && act != kActE4m3) return kNotSupported;
+  const int planes = quantized ? 1 : act_planes(act, true);
   ExpertParams Pm{};
   Pm.tab = ExpertTables{n_chunks, chunk_expert, chunk_row0, chunk_rows, pairs};
   Pm.planes = planes;
@@ -423,6 +432,15 @@ int experts_tc(const void* latent, const float* weights, const lx_weight& gate_u
     const int per_block = 128 * 16 / elem;
     const dim3 grid((n_stages * KS + per_block - 1) / per_block, P);
     const int64_t stride = static_cast<int64_t>(n_stages) * Pm.x_bytes;
+    if (quantized) {
+      if (act == kActS8)
+        return launch_kernel(expert_prep_kernel<kActS8, true>, grid, dim3(128), 0, stream, src, ld, gather_top_k, K, Pm.NC,
+                             static_cast<const int32_t*>(pairs), static_cast<const int32_t*>(pos_chunk), static_cast<const int32_t*>(pos_col),
+                             xprep, stride, inv, n_stages);
+      return launch_kernel(expert_prep_kernel<kActE4m3, true>, grid, dim3(128), 0, stream, src, ld, gather_top_k, K, Pm.NC,
+                           static_cast<const int32_t*>(pairs), static_cast<const int32_t*>(pos_chunk), static_cast<const int32_t*>(pos_col),
+                           xprep, stride, inv, n_stages);
+    }
     switch (act) {
       case kActBf16:
         return launch_kernel(expert_prep_kernel<kActBf16>, grid, dim3(128), 0, stream, src, ld, gather_top_k, K, Pm.NC,

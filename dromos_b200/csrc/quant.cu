@@ -11,10 +11,6 @@ namespace {
 
 constexpr int kBlock = 256;
 
-__device__ __forceinline__ uint32_t e4m3_encode(float v) {
-  return static_cast<uint32_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
-}
-
 // Nearest e2m1 code (0, .5, 1, 1.5, 2, 3, 4, 6 with a sign bit): the code is how many midpoints lie below |x|, a
 // value on a midpoint goes to the even neighbour, magnitudes saturate at 6, and a zero result carries no sign.
 __device__ __forceinline__ uint32_t e2m1_encode(float x) {

@@ -256,6 +256,29 @@ __device__ __forceinline__ float scale_of(float a) {
   return __uint_as_float(static_cast<uint32_t>(254 + kTop - ex) << 23);
 }
 
+// The low-precision maths (INT8 weights x int8 activations, FP8 x e4m3): a row is quantized once as lx_quantize_act
+// quantizes it (lernex/dromos engine/cuda/quant.cu; kernels.h "lx_quantize_act"): scale = max|x| / top with top = 127 or
+// 448 (1 for an all-zero row), values x * (top / max|x|) rounded to nearest even and clamped.
+template <int ACT>
+__device__ __forceinline__ void quant_scales(float a, float& to_q, float& back) {
+  constexpr float kTop = ACT == kActS8 ? 127.0f : 448.0f;
+  to_q = a > 0.0f ? __fdiv_rn(kTop, a) : 0.0f;
+  back = a > 0.0f ? __fdiv_rn(a, kTop) : 1.0f;
+}
+template <int ACT>
+__device__ __forceinline__ void quantize_plane(const float (&v)[16], float to_q, uint32_t (&w)[4]) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) w[q] = 0;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float r = v[i] * to_q;
+    uint32_t b;
+    if constexpr (ACT == kActS8) b = static_cast<uint32_t>(static_cast<int>(fminf(fmaxf(rintf(r), -127.0f), 127.0f))) & 0xffu;
+    else b = e4m3_encode(r) & 0xffu;
+    w[i / 4] |= b << ((i % 4) * 8);
+  }
+}
+
 // V = 16 / element size scaled values to the 16 bytes of each plane.
 template <int ACT, bool XBF, int V>
 __device__ __forceinline__ void make_planes(const float (&v)[V], float sc, uint32_t (&w)[3][4]) {

@@ -233,6 +233,18 @@ def quantize_act(x: np.ndarray, math: int):
     return pack_nibbles(codes.reshape(M, K)), g, s8
 
 
+def act_operand(x: np.ndarray, math: int) -> np.ndarray:
+    """The activations as a product's math sees them, float64: x itself under BF16 math, else the per-row quantization
+    of quantize_act times its scale (the reference's tests/kernels/wformats.py:174-180; INT8 and FP8 maths)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    if math == MATH_BF16:
+        return x.astype(np.float64)
+    assert math in (MATH_INT8, MATH_FP8), "FP4 math is a product of other parts only"
+    q, scale, _ = quantize_act(x, math)
+    vals = q.view(np.int8).astype(np.float64) if math == MATH_INT8 else e4m3_to_f32(q).astype(np.float64)
+    return vals * scale.astype(np.float64)[:, None]
+
+
 # ---------------------------------------------------------------------------------------------------
 # BF16X, the lossless encoding (engine/cuda/bf16x.cuh:13-49, engine/cpu/bf16x.cpp:60-199)
 # ---------------------------------------------------------------------------------------------------
@@ -403,10 +415,12 @@ def silu(v):
     return v / (1.0 + np.exp(-v))
 
 
-def moe_experts_reference(latent_bits, ids, weights, gate_up: Weight, down: Weight, I: int) -> np.ndarray:
+def moe_experts_reference(latent_bits, ids, weights, gate_up: Weight, down: Weight, I: int, math: int = MATH_BF16) -> np.ndarray:
     """out[t] = sum_k w[t, k] * down[e] @ bf16(silu(gate . x) * (up . x)), float64 except the one bf16 rounding of
-    the intermediate (kernels.h:217-225, 495-511). gate_up [E, 2I, L], down [E, L, I]."""
-    x = bf16_bits_to_f32(latent_bits).astype(np.float64)
+    the intermediate (kernels.h:217-225, 495-511). gate_up [E, 2I, L], down [E, L, I]. Under the INT8 / FP8 maths the
+    latent (per token) and the rounded intermediate (per pair row) are what act_operand makes of them
+    (engine/cuda/moe_grouped.cu:434-490; tests/kernels/test_moe_grouped.py:99-118)."""
+    x = act_operand(bf16_bits_to_f32(latent_bits), math)
     T, L = x.shape
     gu = weight_f64(gate_up)
     dn = weight_f64(down)
@@ -416,7 +430,7 @@ def moe_experts_reference(latent_bits, ids, weights, gate_up: Weight, down: Weig
             e = int(ids[t, k])
             h = gu[e] @ x[t]
             mid = (silu(h[:I]) * h[I:]).astype(np.float32)
-            mid = bf16_bits_to_f32(f32_to_bf16_bits(mid)).astype(np.float64)
+            mid = act_operand(bf16_bits_to_f32(f32_to_bf16_bits(mid))[None, :], math)[0]
             out[t] += float(weights[t, k]) * (dn[e] @ mid)
     return out
 

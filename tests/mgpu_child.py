@@ -1,0 +1,92 @@
+"""Child of tests/test_multi_gpu.py: one process per GPU (launched by torch.distributed.run). Checks on real peers what
+the single-GPU suite cannot: the one-kernel exchange of output slices against the unsharded product, bit for bit, and a
+peer that never arrives (the wait gives up, reports, and the next round works). Nothing here faults or hangs a GPU: the
+rank that "never arrives" simply skips one call and stays alive; NVLS / multicast are off."""
+
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+
+from dromos_b200 import abi, host  # noqa: E402
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    lib = abi.Library()
+    failures = []
+    N, K = 2 * 4096 + 64, 2048  # shards of different sizes when world does not divide N evenly
+    gen = torch.Generator(device=dev).manual_seed(5)  # the same on every rank
+    w = (torch.randn((N, K), generator=gen, device=dev) * 0.02).to(torch.bfloat16)
+    n0, n1 = host.shard_rows(N, rank, world)
+    for wtype in (abi.W_BF16, abi.W_INT8, abi.W_FP8, abi.W_NVFP4, abi.W_BF16X):
+        buffers = host.PeerBuffers(N, 64, dev)
+        whole = host.Linear(lib, host.store_weight(lib, w, wtype), N, K)
+        layer = host.PeerShardedLinear(lib, host.store_weight(lib, w[n0:n1].contiguous(), wtype), N, K, buffers)
+        for rnd, M in enumerate((1, 8, 3, 16, 64, 5)):
+            x = torch.randn((M, K), generator=gen, device=dev).to(torch.bfloat16)
+            got = layer(x).clone()
+            want = whole(x)
+            torch.cuda.synchronize()
+            if wtype == abi.W_NVFP4:  # a shard quantized alone has its own global scale: compare by value
+                ok = torch.allclose(got, want, rtol=0, atol=2e-2 * float(want.abs().max()))
+            else:
+                ok = torch.equal(got.view(torch.int32), want.view(torch.int32))
+            if not ok:
+                failures.append(f"rank {rank} wtype {wtype} round {rnd} M={M}: exchanged y differs from the unsharded product "
+                                f"(max abs {float((got - want).abs().max()):.3e})")
+        if lib.lx_b200_last_error() != 0:
+            failures.append(f"rank {rank} wtype {wtype}: a bounded wait ran out")
+        dist.barrier()
+
+    # ---- a peer that never arrives ----
+    os.environ["LX_B200_WAIT_MS"] = "50"
+    buffers = host.PeerBuffers(N, 8, dev)
+    layer = host.PeerShardedLinear(lib, host.store_weight(lib, w[n0:n1].contiguous(), abi.W_FP8), N, K, buffers)
+    x = torch.randn((2, K), generator=gen, device=dev).to(torch.bfloat16)
+    layer(x)
+    torch.cuda.synchronize()
+    dist.barrier()
+    if rank == 0:
+        layer(x)  # the others skip this round: rank 0 waits 50 ms, gives up and says so
+        torch.cuda.synchronize()
+        code = lib.lx_b200_last_error()
+        if code != 6:
+            failures.append(f"rank 0: expected status 6 after a round nobody joined, got {code}")
+    else:
+        buffers.next_half()  # keep the buffer halves in step with rank 0
+    dist.barrier()
+    # rank 0's lone arrival is still in everyone's semaphore: drain it, then a normal round works again
+    buffers.counter.zero_()
+    torch.cuda.synchronize()
+    dist.barrier()
+    got = layer(x).clone()
+    torch.cuda.synchronize()
+    want = host.Linear(lib, host.store_weight(lib, w, abi.W_FP8), N, K)(x)
+    torch.cuda.synchronize()
+    if not torch.equal(got.view(torch.int32), want.view(torch.int32)) or lib.lx_b200_last_error() != 0:
+        failures.append(f"rank {rank}: the round after the abandoned one is wrong")
+    flag = torch.tensor([len(failures)], device=dev)
+    dist.all_reduce(flag)
+    for f in failures:
+        print("FAIL", f, flush=True)
+    dist.barrier()
+    torch.cuda.synchronize()
+    if rank == 0:
+        print("MGPU_OK" if int(flag.item()) == 0 else "MGPU_FAILED", flush=True)
+    sys.stdout.flush()
+    os._exit(0 if int(flag.item()) == 0 else 1)
+
+
+if __name__ == "__main__":
+    main()
