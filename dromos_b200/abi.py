@@ -49,6 +49,7 @@ SIGNATURES = {
     "lx_bf16x_bytes": (c_i64, [c_ptr, c_i64, c_int, c_ptr]),
     "lx_bf16x_encode": (c_int, [c_ptr, c_i64, c_int, c_ptr, c_i64, c_ptr]),
     "lx_bf16x_decode": (c_int, [c_ptr, c_i64, c_int, c_ptr, c_ptr]),
+    "lx_spec_gemv_f32": (c_int, [c_ptr, c_int, c_ptr, c_ptr, c_ptr, c_int, c_int, c_int, c_int, c_ptr]),
     "lx_moe_route": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_int, c_int, c_ptr]),
     "lx_router_route": (c_int, [c_ptr, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_int, c_int, c_int, c_ptr]),
     "lx_moe_experts_grouped": (c_int, [c_ptr, c_ptr, c_ptr, _W, _W, c_int, c_ptr, c_ptr, c_int, c_int, c_int, c_int, c_int, c_ptr]),

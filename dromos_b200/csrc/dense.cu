@@ -149,10 +149,7 @@ int row_bytes_of(int type, int K) {
 
 int gemv_env_variant() {
   static const int v = [] {
-    const char* name = std::getenv("LX_B200_GEMV_VARIANT");
-    for (int i = 0; name && i < kGemvVariants; ++i)
-      if (std::strcmp(name, kGemvVariantNames[i]) == 0) return i;
-    return -1;
+    return gemv_variant_by_name(std::getenv("LX_B200_GEMV_VARIANT"));
   }();
   return v;
 }
@@ -182,8 +179,8 @@ int dense_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, cons
   // Up to 8 rows: the decode GEMV of gemv.cuh whenever the weight's shape and alignment allow, except INT8 weights wide
   // enough for the tcgen05 product, which is the faster one there (measured on 14336 x 4096: 15.4 / 17.1 us at M = 1 / 8
   // against 16.5 / 23.2). The choice never depends on M. The variant table can name another residency of the GEMV (same
-  // bits), or, through lx_tune_force only, another implementation: the TMA-ring mma.sync kernel of stream.cuh ("ring"),
-  // the tcgen05 product ("tc", INT8 / FP8 weights with enough rows per SM). LX_B200_GEMV=0 restores the ring / tc pair.
+  // bits), or, through lx_tune_force only, another implementation: the TMA-ring mma.sync kernel of stream.cuh ("s8ring"),
+  // the tcgen05 product ("s1tc", INT8 / FP8 weights with enough rows per SM). LX_B200_GEMV=0 restores the ring / tc pair.
   if (M <= 8 && !force_scalar()) {
     int tuned = lx_tune_get(gemv_kernel_name(w.type), M, N, K);
     if (tuned < 0) tuned = gemv_env_variant();  // LX_B200_GEMV_VARIANT=<name>: the variant of shapes the table does not hold
@@ -350,6 +347,9 @@ extern "C" int lx_gemm_w(const void* x, lx_dtype x_dtype, int ld_x, const lx_wei
   if (rowb % 16 != 0 || !aligned(w->data, 16) || (w->type == LX_W_NVFP4 && K % 64 != 0)) return kNotSupported;
   // With a workspace every row count goes through the tcgen05 product, so that within this entry point a row's bits
   // do not depend on M. LX_B200_TC=0 keeps the mma.sync kernels.
+  // f32 activations are rounded to bf16 (BF16 math) or quantized (the other maths) into the workspace, as in the
+  // reference (engine/cuda/gemm_w.cu:213-252), which answers "invalid" when there is none.
+  if (x_dtype == LX_F32 && !workspace) return kInvalid;
   if (quantized) {  // activations quantized per token into the workspace, then s8 x s8 -> s32 or e4m3 x e4m3 -> f32 on the tensor cores
     if (!workspace) return kInvalid;
     if (!tc_enabled() || !aligned(workspace, 16)) return kNotSupported;

@@ -82,10 +82,13 @@ struct TcLayout {
 // is found by every block of the row again (the row is a few KB, from L2), which saves a second kernel. Plane j of
 // row u is column j * Mp + u. k past K is written as zero up to the end of the last stage; columns that no row owns
 // are never written (their accumulator columns are never read).
-// QUANT (int8 / e4m3 only): the low-precision maths of lx_gemm_w. The row is quantized once, as lx_quantize_act does
-// (scale = max|x| / 127 or / 448, values rounded to nearest even and clamped; engine/cuda/quant.cu), into ONE plane,
-// and the row's sums are multiplied by that scale.
-template <int ACT, bool XBF, bool QUANT = false>
+// MODE kPrepQuant (int8 / e4m3 only): the low-precision maths of lx_gemm_w. The row is quantized once, as
+// lx_quantize_act does (scale = max|x| / 127 or / 448, values rounded to nearest even and clamped; engine/cuda/quant.cu),
+// into ONE plane, and the row's sums are multiplied by that scale.
+// MODE kPrepRound (f32 activations): every value is rounded to bf16 first and then treated as a bf16 activation, which
+// is what lx_gemm_w does with f32 activations under BF16 math (engine/cuda/gemm_w.cu:239-252: "a bf16 copy").
+enum { kPrepExact = 0, kPrepQuant = 1, kPrepRound = 2 };
+template <int ACT, bool XBF, int MODE = kPrepExact>
 __global__ void __launch_bounds__(128) tc_prep_kernel(const void* __restrict__ x, int ld_x, int rows, int K, int NC, int Mp, int planes,
                                                       uint8_t* __restrict__ out, float* __restrict__ inv_scales, int n_stages) {
   constexpr int kElem = act_elem(ACT), V = 16 / kElem, kKS = ks_of(ACT);
@@ -98,14 +101,24 @@ __global__ void __launch_bounds__(128) tc_prep_kernel(const void* __restrict__ x
   const int64_t row = static_cast<int64_t>(u) * ld_x;
   const bool aligned16 = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && ld_x % (XBF ? 8 : 4) == 0;
   // this thread's values first (the loads are in flight while the row's largest magnitude is found)
+  constexpr bool QUANT = MODE == kPrepQuant;
+  constexpr bool AS_BF16 = XBF || MODE == kPrepRound;  // the values are bf16 by the time they are split
+  static_assert(MODE != kPrepRound || !XBF, "only f32 activations are rounded");
   float v[V];
-  if (in_range) load_values<XBF, V>(x, row, k0, K, aligned16, v);
+  if (in_range) {
+    load_values<XBF, V>(x, row, k0, K, aligned16, v);
+    if constexpr (MODE == kPrepRound) {
+#pragma unroll
+      for (int i = 0; i < V; ++i) v[i] = bf16_bits_to_f32(f32_to_bf16_bits(v[i]));
+    }
+  }
   float sc = 1.0f, back = 1.0f;
   if constexpr (ACT != kActBf16) {
     float a = warp_max(row_max_share<XBF>(x, row, K, aligned16, tid, 128));
     if ((tid & 31) == 0) part[tid >> 5] = a;
     __syncthreads();
     a = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
+    if constexpr (MODE == kPrepRound) a = bf16_bits_to_f32(f32_to_bf16_bits(a));  // rounding is monotonic: the largest rounded value
     if constexpr (QUANT) {
       quant_scales<ACT>(a, sc, back);
     } else {
@@ -117,7 +130,7 @@ __global__ void __launch_bounds__(128) tc_prep_kernel(const void* __restrict__ x
   if (!in_range) return;
   uint32_t w[3][4];
   if constexpr (QUANT) quantize_plane<ACT>(v, sc, w[0]);
-  else make_planes<ACT, XBF, V>(v, sc, w);
+  else make_planes<ACT, AS_BF16, V>(v, sc, w);
   uint8_t* block = out + static_cast<size_t>(k0 / kKS) * (static_cast<size_t>(NC) * kKS * kElem);
   const int kb = (k0 % kKS) * kElem;
   for (int j = 0; j < planes; ++j) *reinterpret_cast<uint4*>(block + block_offset(NC, kb, j * Mp + u)) = make_uint4(w[j][0], w[j][1], w[j][2], w[j][3]);
@@ -994,12 +1007,12 @@ int tc_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const v
   const bool x_bf16 = x_dtype == LX_BF16;
   if (quantized && w.type != LX_W_INT8 && w.type != LX_W_FP8) return kNotSupported;
   const int act = act_of(w.type), elem = act_elem(act), kKS = ks_of(act);
-  const int per_pass = rows_per_pass(act, x_bf16);
+  const int per_pass = rows_per_pass(act, true);  // f32 activations become bf16 (or quantized) values: as many planes as bf16
   const int n_stages = (K + kKS - 1) / kKS;
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   for (int m0 = 0; m0 < M; m0 += per_pass) {
     const int rows = std::min(per_pass, M - m0);
-    TcParams P = base_params(w, bias, bias_dtype, y_dtype, ld_y, N, K, alpha, beta, act, x_bf16, rows, quantized);
+    TcParams P = base_params(w, bias, bias_dtype, y_dtype, ld_y, N, K, alpha, beta, act, true, rows, quantized);
     const TcLayout L(P.NC, act, n_stages);
     P.xprep = ws;
     P.inv_scales = reinterpret_cast<const float*>(ws + L.scales);
@@ -1013,18 +1026,19 @@ int tc_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, const v
     };
     int pe;
     if (quantized) {
-      if (act == kActS8) pe = x_bf16 ? prep(tc_prep_kernel<kActS8, true, true>) : prep(tc_prep_kernel<kActS8, false, true>);
-      else pe = x_bf16 ? prep(tc_prep_kernel<kActE4m3, true, true>) : prep(tc_prep_kernel<kActE4m3, false, true>);
-    } else
-    switch (act * 2 + (x_bf16 ? 1 : 0)) {
-      case kActBf16 * 2: pe = prep(tc_prep_kernel<kActBf16, false>); break;
-      case kActBf16 * 2 + 1: pe = prep(tc_prep_kernel<kActBf16, true>); break;
-      case kActF16 * 2: pe = prep(tc_prep_kernel<kActF16, false>); break;
-      case kActF16 * 2 + 1: pe = prep(tc_prep_kernel<kActF16, true>); break;
-      case kActE4m3 * 2: pe = prep(tc_prep_kernel<kActE4m3, false>); break;
-      case kActE4m3 * 2 + 1: pe = prep(tc_prep_kernel<kActE4m3, true>); break;
-      case kActS8 * 2: pe = prep(tc_prep_kernel<kActS8, false>); break;
-      default: pe = prep(tc_prep_kernel<kActS8, true>); break;
+      if (act == kActS8) pe = x_bf16 ? prep(tc_prep_kernel<kActS8, true, kPrepQuant>) : prep(tc_prep_kernel<kActS8, false, kPrepQuant>);
+      else pe = x_bf16 ? prep(tc_prep_kernel<kActE4m3, true, kPrepQuant>) : prep(tc_prep_kernel<kActE4m3, false, kPrepQuant>);
+    } else {
+      switch (act * 2 + (x_bf16 ? 1 : 0)) {
+        case kActBf16 * 2: pe = prep(tc_prep_kernel<kActBf16, false, kPrepRound>); break;
+        case kActBf16 * 2 + 1: pe = prep(tc_prep_kernel<kActBf16, true>); break;
+        case kActF16 * 2: pe = prep(tc_prep_kernel<kActF16, false, kPrepRound>); break;
+        case kActF16 * 2 + 1: pe = prep(tc_prep_kernel<kActF16, true>); break;
+        case kActE4m3 * 2: pe = prep(tc_prep_kernel<kActE4m3, false, kPrepRound>); break;
+        case kActE4m3 * 2 + 1: pe = prep(tc_prep_kernel<kActE4m3, true>); break;
+        case kActS8 * 2: pe = prep(tc_prep_kernel<kActS8, false, kPrepRound>); break;
+        default: pe = prep(tc_prep_kernel<kActS8, true>); break;
+      }
     }
     if (pe) return pe;
     int e;

@@ -159,6 +159,50 @@ __global__ void __launch_bounds__(256) router_kernel(const float* __restrict__ x
               weights + static_cast<int64_t>(warp) * top_k, entropy ? entropy + warp : nullptr, confidence ? confidence + warp : nullptr);
 }
 
+// ---- the f32 GEMV the router's logits are defined by (lx_spec_gemv_f32) --------------------------------------------
+// y[m, n] = x[m, :] . w[n, :] + bias[n] for up to 8 rows and any K, in exactly the order router_kernel adds: one warp
+// per output column, lane l takes the float4 steps l, l + 32, ... in ascending order (x, y, z, w inside a step, one
+// fmaf chain per row), then the fixed shuffle tree, then the bias. A row's bits depend on K alone, and for K <= 2048
+// they are router_kernel's logits bit for bit.
+__global__ void __launch_bounds__(256) rows_gemv_f32_kernel(const float* __restrict__ x, int ld_x, const float* __restrict__ w,
+                                                            const float* __restrict__ bias, float* __restrict__ y, int ld_y, int M, int N,
+                                                            int K) {
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 8 + warp;
+  if (n >= N) return;
+  const bool vec = K % 4 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && ld_x % 4 == 0;
+  const float* wrow = w + static_cast<int64_t>(n) * K;
+  float acc[kRouterRows];
+#pragma unroll
+  for (int m = 0; m < kRouterRows; ++m) acc[m] = 0.0f;
+  for (int k = lane * 4; k < K; k += 128) {
+    float4 wv;
+    if (vec) wv = __ldg(reinterpret_cast<const float4*>(wrow + k));
+    else wv = make_float4(wrow[k], k + 1 < K ? wrow[k + 1] : 0.0f, k + 2 < K ? wrow[k + 2] : 0.0f, k + 3 < K ? wrow[k + 3] : 0.0f);
+#pragma unroll
+    for (int m = 0; m < kRouterRows; ++m) {
+      if (m >= M) break;
+      const float* xr = x + static_cast<int64_t>(m) * ld_x;
+      float4 xv;
+      if (vec) xv = *reinterpret_cast<const float4*>(xr + k);
+      else xv = make_float4(xr[k], k + 1 < K ? xr[k + 1] : 0.0f, k + 2 < K ? xr[k + 2] : 0.0f, k + 3 < K ? xr[k + 3] : 0.0f);
+      acc[m] = fmaf(xv.x, wv.x, acc[m]);
+      acc[m] = fmaf(xv.y, wv.y, acc[m]);
+      acc[m] = fmaf(xv.z, wv.z, acc[m]);
+      acc[m] = fmaf(xv.w, wv.w, acc[m]);
+    }
+  }
+  const float b = bias ? bias[n] : 0.0f;
+#pragma unroll
+  for (int m = 0; m < kRouterRows; ++m) {
+    if (m >= M) break;
+    const float sum = warp_sum(acc[m]);
+    if (lane == 0) y[static_cast<int64_t>(m) * ld_y + n] = sum + b;
+  }
+}
+
 // ---- grouping --------------------------------------------------------------------------------------------------
 // offsets[e] = pairs of experts below e; pairs[offsets[e] + j] = the j-th pair (ascending) that chose expert e.
 // One CTA of 1024 threads, thread e walks the ids (staged in shared memory when there are at most 8192 of them: the
@@ -475,6 +519,14 @@ extern "C" int lx_router_route(const float* x, int ld_x, const float* w, const f
   if (!x || !w || !logits || !ids || !weights || !ticket || ld_x < K) return kInvalid;
   return launch_kernel(router_kernel, dim3((E + 7) / 8), dim3(256), 0, static_cast<cudaStream_t>(stream), x, ld_x, w, bias, logits,
                        selection_bias, ids, weights, entropy, confidence, ticket, M, E, K, top_k);
+}
+
+extern "C" int lx_spec_gemv_f32(const float* x, int ld_x, const float* w, const float* bias, float* y, int ld_y, int M, int N, int K,
+                                void* stream) {
+  if (M == 0 || N == 0) return kOk;
+  if (M < 0 || M > kRouterRows || K <= 0 || ld_x < K || ld_y < N || !x || !w || !y) return kInvalid;
+  return launch_kernel(rows_gemv_f32_kernel, dim3((N + 7) / 8), dim3(256), 0, static_cast<cudaStream_t>(stream), x, ld_x, w, bias, y, ld_y, M,
+                       N, K);
 }
 
 extern "C" int64_t lx_moe_grouped_workspace_bytes(int T, int L, int I, int E, int top_k, lx_math math) {

@@ -107,6 +107,11 @@ LX_API int lx_bf16x_decode(const void* data, int64_t rows, int K, void* w, void*
 /* kernels.h:208 (engine/cuda/moe.cu:249, route.cuh:18-81) */
 LX_API int lx_moe_route(const float* logits, const float* selection_bias, int32_t* ids, float* weights,
                         float* entropy, float* confidence, int T, int E, int top_k, void* stream);
+/* The f32 GEMV of decode-sized steps that defines the router's logits: y[M, N] = x[M, K] @ w[N, K]^T + bias[N],
+ * M <= 8, a row's bits independent of M; lx_router_route's logits equal it bit for bit. kernels.h:814-819
+ * (engine/cuda/spec.cu:933-940). */
+LX_API int lx_spec_gemv_f32(const float* x, int ld_x, const float* w, const float* bias, float* y, int ld_y, int M,
+                            int N, int K, void* stream);
 /* kernels.h:508, 511 (engine/cuda/moe_grouped.cu:381-388) */
 LX_API int lx_moe_experts_grouped(const void* latent, const int32_t* ids, const float* weights,
                                   const lx_weight* gate_up, const lx_weight* down, lx_math math, float* out,

@@ -25,7 +25,7 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     lib = abi.Library()
     failures = []
-    N, K = 2 * 4096 + 64, 2048  # shards of different sizes when world does not divide N evenly
+    N, K = 2 * 8192 + 72, 2048  # every shard wide enough that shard and whole weight pick the same kernel
     gen = torch.Generator(device=dev).manual_seed(5)  # the same on every rank
     w = (torch.randn((N, K), generator=gen, device=dev) * 0.02).to(torch.bfloat16)
     n0, n1 = host.shard_rows(N, rank, world)

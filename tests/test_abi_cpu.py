@@ -37,10 +37,11 @@ def test_host_only_entry_points_answer_without_a_gpu():
     assert lib.lx_gemm_workspace_bytes(0, 4096, 0) == 0 and lib.lx_gemm_workspace_bytes(32, 4096, 0) > 0
     assert lib.lx_moe_grouped_workspace_bytes(32, 4096, 1536, 64, 8, 0) > 0
     n = lib.lx_tune_kernels(None, 0)
-    assert n == 5
+    assert n == 11  # five decode GEMV kernels and the six lx_gemm_w families
+    assert lib.lx_tune_variants(b"gemm_w.f8.sm100") == 1 and lib.lx_tune_set(b"gemm_w.f8.sm100", 200, 384, 1024, 0) == 0
     assert lib.lx_tune_variants(b"gemv_w_fp8") >= 1 and lib.lx_tune_variants(b"nope") == 0
     names = [lib.lx_tune_variant_name(b"gemv_w_fp8", i) for i in range(lib.lx_tune_variants(b"gemv_w_fp8"))]
-    assert re.match(rb"d\d+c\d+", names[0]) and b"ring" in names and b"tc" in names
+    assert re.match(rb"s16d\d+c\d+", names[0]) and b"s8ring" in names and b"s1tc" in names
     assert lib.lx_tune_variant_name(b"gemv_w_fp8", len(names)) is None
     assert lib.lx_tune_set(b"gemv_w_fp8", 1, 64, 64, 10**6) == abi.ERR_TUNE_VARIANT
     assert lib.lx_tune_set(b"gemv_w_fp8", 3, 64, 64, 1) == 0 and lib.lx_tune_get(b"gemv_w_fp8", 4, 64, 64) == 1  # M bucket 4
@@ -56,9 +57,9 @@ def test_tune_set_refuses_another_summation_order():
     for kernel in (b"gemv_w_bf16", b"gemv_w_int8", b"gemv_w_fp8", b"gemv_w_nvfp4", b"gemv_bf16x"):
         n = lib.lx_tune_variants(kernel)
         names = [lib.lx_tune_variant_name(kernel, i) for i in range(n)]
-        same = [i for i, nm in enumerate(names) if re.match(rb"d\d+c\d+", nm)]
+        same = [i for i, nm in enumerate(names) if re.match(rb"(s16)?d\d+c\d+", nm)]
         other = [i for i in range(n) if i not in same]
-        assert same and other
+        assert same and (other or kernel == b"gemv_bf16x")  # the lossless kernel lists only its own order-keeping forms
         for v in same:  # K = 4096: every format's decode GEMV takes it
             assert lib.lx_tune_set(kernel, 1, 4096, 4096, v) == 0
             assert lib.lx_tune_get(kernel, 1, 4096, 4096) == v
@@ -67,9 +68,11 @@ def test_tune_set_refuses_another_summation_order():
             assert lib.lx_tune_get(kernel, 1, 4096, 4096) == same[-1]  # the table is unchanged
             assert lib.lx_tune_force(kernel, 8, 4096, 4096, v) == 0 and lib.lx_tune_get(kernel, 8, 4096, 4096) == v
         # K = 40 is not whole 64-byte steps for any format: the default there is the other kernel family
-        ring = names.index(b"ring")
-        assert lib.lx_tune_set(kernel, 1, 4096, 40, ring) == 0
-        assert lib.lx_tune_set(kernel, 1, 4096, 40, names.index(b"tc")) == abi.ERR_TUNE_REJECTED
+        if other:
+            assert lib.lx_tune_set(kernel, 1, 4096, 40, names.index(b"s8ring")) == 0
+            assert lib.lx_tune_set(kernel, 1, 4096, 40, names.index(b"s1tc")) == abi.ERR_TUNE_REJECTED
+        for v in same:  # naming a decode GEMV form for a shape it cannot take changes nothing: admitted
+            assert lib.lx_tune_set(kernel, 1, 4096, 40, v) == 0
     lib.lx_tune_clear()
 
 

@@ -180,6 +180,11 @@ def router_case(lx, M, E, K, top_k, with_bias, seed, tie=False):
     want = x[:, :K].astype(np.float64) @ w.astype(np.float64).T + (0.0 if bias is None else bias.astype(np.float64))
     got = util.host(logits)
     assert np.abs(got - want).max() <= 1e-5 * max(1.0, np.abs(want).max())
+    # the logits are lx_spec_gemv_f32's, bit for bit (kernels.h:211-213)
+    two = torch.full((M, E), float("nan"), device="cuda")
+    assert lx.lx_spec_gemv_f32(abi.ptr(x_d), ld_x, abi.ptr(w_d), abi.ptr(bias_d), abi.ptr(two), E, M, E, K, util.stream_ptr()) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(two.view(torch.int32), logits.view(torch.int32))
     # the routing is lx_moe_route on these logits, bit for bit
     ids2 = torch.full((M, top_k), -1, dtype=torch.int32, device="cuda")
     w2, e2, c2 = torch.zeros((M, top_k), device="cuda"), torch.zeros(M, device="cuda"), torch.zeros(M, device="cuda")
@@ -206,6 +211,27 @@ def test_router_breaks_ties_like_the_route_call(lx):
     for M in (1, 5, 8):
         ids, _, _ = router_case(lx, M, 128, 1280, 4, True, seed=2 + M, tie=True)
         assert not np.any(ids == 5)
+
+
+@pytest.mark.parametrize("N,K", [(300, 5000), (1000, 4096), (7, 33)])
+def test_rows_gemv_f32_rows_do_not_depend_on_batch(lx, N, K):
+    """lx_spec_gemv_f32 beyond the router's sizes: close to float64, and a row alone equals the row in a batch of 8."""
+    rng = np.random.default_rng(N + K)
+    x, w, bias = rng.standard_normal((8, K)).astype(np.float32), (rng.standard_normal((N, K)) * 0.05).astype(np.float32), rng.standard_normal(N).astype(np.float32)
+    x_d, w_d, b_d = util.dev(x), util.dev(w), util.dev(bias)
+    big = torch.full((8, N + 5), float("nan"), device="cuda")
+    assert lx.lx_spec_gemv_f32(abi.ptr(x_d), K, abi.ptr(w_d), abi.ptr(b_d), abi.ptr(big), N + 5, 8, N, K, util.stream_ptr()) == 0
+    got = util.host(big)
+    want = x.astype(np.float64) @ w.astype(np.float64).T + bias
+    assert np.abs(got[:, :N] - want).max() <= 1e-5 * max(1.0, np.abs(want).max()) and np.all(np.isnan(got[:, N:]))
+    for m in (0, 3, 7):
+        one = torch.full((1, N), float("nan"), device="cuda")
+        assert lx.lx_spec_gemv_f32(abi.ptr(x_d[m : m + 1]), K, abi.ptr(w_d), abi.ptr(b_d), abi.ptr(one), N, 1, N, K, util.stream_ptr()) == 0
+        assert np.array_equal(util.host(one)[0].view(np.uint32), got[m, :N].view(np.uint32))
+    z = torch.zeros(16, device="cuda")
+    assert lx.lx_spec_gemv_f32(abi.ptr(z), 4, abi.ptr(z), None, abi.ptr(z), 4, 9, 4, 4, None) == 1   # more than eight rows
+    assert lx.lx_spec_gemv_f32(abi.ptr(z), 3, abi.ptr(z), None, abi.ptr(z), 4, 1, 4, 4, None) == 1   # a stride shorter than the row
+    assert lx.lx_spec_gemv_f32(abi.ptr(z), 4, abi.ptr(z), None, abi.ptr(z), 4, 0, 4, 4, None) == 0
 
 
 def test_router_refuses_what_the_reference_refuses(lx):

@@ -66,7 +66,7 @@ def test_every_variant(lx, fmt, shape, x_f32):
         util.assert_close(outs[8], want, what=f"{NAMES[fmt]} variant {name.decode()}")
         for M in range(1, 8):
             assert np.array_equal(outs[M].view(np.uint32), outs[8][:M].view(np.uint32)), f"variant {name.decode()}: rows at M={M} differ from M=8"
-        cls = 0 if re.match(rb"d\d+c\d+", name) else name
+        cls = 0 if re.match(rb"(s16)?d\d+c\d+", name) else name
         by_class.setdefault(cls, []).append(outs[8].view(np.uint32).copy())
         lx.lx_tune_clear()
     same = by_class[0]
@@ -84,8 +84,8 @@ def test_bf16x_variants_keep_bf16_bits(lx):
     dx = util.DeviceWeight(util.make_weight(w_bits, O.W_BF16X))
     x_dev = util.dev(util.bf16_normal((8, K), 1.0, 71))
     n16, nx = variants(lx, b"gemv_w_bf16"), variants(lx, b"gemv_bf16x")
-    same16 = [i for i, n in enumerate(n16) if re.match(rb"d\d+c\d+", n)]
-    samex = [i for i, n in enumerate(nx) if re.match(rb"d\d+c\d+", n)]
+    same16 = [i for i, n in enumerate(n16) if re.match(rb"(s16)?d\d+c\d+", n)]
+    samex = [i for i, n in enumerate(nx) if re.match(rb"(s16)?d\d+c\d+", n)]
     for a in same16:
         for b in samex:
             lx.lx_tune_clear()
@@ -104,14 +104,22 @@ def test_order_class_admission_on_the_device(lx):
     K = 4096
     for kernel in KERNELS.values():
         names = variants(lx, kernel)
-        tc, ring = names.index(b"tc"), names.index(b"ring")
-        gemv = [i for i, n in enumerate(names) if re.match(rb"d\d+c\d+", n)]
+        gemv = [i for i, n in enumerate(names) if re.match(rb"(s16)?d\d+c\d+", n)]
         # a narrow weight: the GEMV is the default for every format
         for v in gemv:
             assert lx.lx_tune_set(kernel, 1, 1024, K, v) == 0
+        if kernel == b"gemv_bf16x":  # only its own order-keeping forms are listed: every one is admitted at every key
+            assert len(gemv) == len(names)
+            for v in gemv:
+                assert lx.lx_tune_set(kernel, 4, 14336, K, v) == 0 and lx.lx_tune_set(kernel, 2, 300, 1040, v) == 0
+            assert lx.lx_tune_set(kernel, 1, 14336, K, len(names)) == abi.ERR_TUNE_VARIANT
+            continue
+        tc, ring = names.index(b"s1tc"), names.index(b"s8ring")
         assert lx.lx_tune_set(kernel, 1, 1024, K, tc) == abi.ERR_TUNE_REJECTED
         assert lx.lx_tune_set(kernel, 1, 1024, K, ring) == abi.ERR_TUNE_REJECTED
         # a wide weight: INT8 runs on the tcgen05 product by default, so there only "tc" keeps the bits
+        splits = {int(re.match(rb"s(\d+)", names[v]).group(1)) for v in gemv}
+        assert len(splits) == 1, "variants admitted together carry one split in their names"
         wide_default_tc = kernel == b"gemv_w_int8"
         assert lx.lx_tune_set(kernel, 8, 14336, K, tc) == (0 if wide_default_tc else abi.ERR_TUNE_REJECTED)
         for v in gemv:
