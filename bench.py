@@ -405,7 +405,7 @@ def dense_leg(G, name, steps, warmup, scaling, peaks, sampler=None, parity=False
             try:
                 buffers = host.PeerBuffers(N_job, max(Ms), dev)
                 layers = [host.PeerShardedLinear(lib, s, N_job, K, buffers) for s in stored]
-                exchange = "lx_b200_exchange_slices (one kernel: peer stores over NVLink, bounded wait)"
+                exchange = "one kernel over peer memory: lx_b200_exchange_packets (flag-in-data packets) for small slices, lx_b200_exchange_slices (stores + semaphore) for large"
             except Exception as e:
                 print(f"[bench] peer exchange unavailable ({type(e).__name__}: {e}); using NCCL all-gather", file=sys.stderr)
                 layers = None
@@ -649,7 +649,7 @@ def main():
             leg, ms = cpu_leg(n, st, args.warmup if n == HEADLINE else 2)
             per_config[n] = {"workload": (DENSE.get(n) or MOE.get(n))[-1], "value": leg["value"], "unit": "TB/s", "ms_per_step": ms, "cpu_baseline": leg}
         head = per_config[HEADLINE]
-        exch = "none" if world == 1 else os.environ.get("LX_BENCH_EXCHANGE_NAME", "lx_b200_exchange_slices (one kernel: peer stores over NVLink, bounded wait)")
+        exch = "none" if world == 1 else os.environ.get("LX_BENCH_EXCHANGE_NAME", "one kernel over peer memory: lx_b200_exchange_packets (flag-in-data packets) for small slices, lx_b200_exchange_slices (stores + semaphore) for large")
         print(json.dumps({"impl": "reference", "metric": METRIC, "value": head["value"], "unit": "TB/s", "n_gpus": args.gpus, "steps": args.steps,
                           "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True,
                           "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": DTYPE[DENSE[HEADLINE][0]], "data": "synthetic",

@@ -73,6 +73,86 @@ __global__ void __launch_bounds__(256) exchange_kernel(const ExchangeParams P) {
   asm volatile("red.relaxed.sys.global.add.s32 [%0], %1;" ::"l"(P.arrive[P.self]), "r"(-P.ranks) : "memory");
 }
 
+
+// ---- the same exchange with the flag inside the data ---------------------------------------------------------------------
+// Below a megabyte or so the exchange above is all latency: stores, a system-wide fence (one NVLink round trip), the
+// count of finished CTAs, a second fence, the remote arrival, the poll: 12-14 us on two GPUs for a 57 KB slice. Here a
+// 16-byte packet carries 8 bytes of y and the call's sequence number twice ({d0, seq, d1, seq}, the low-latency packet of
+// collective libraries: an 8-byte half of a store arrives whole, so a half whose flag matches holds its data). Senders
+// store packets straight into every peer's receive buffer, receivers poll the packets themselves and unpack them into
+// y: no fence, no semaphore, one NVLink crossing on the critical path. Twice the bytes on the wire, so callers use it
+// for small slices only.
+//
+// The sequence number lives in device memory (the call can sit in a replayed graph): every CTA reads it on entry, the
+// last CTA to finish adds one. Callers alternate two receive buffers (each with its own sequence word), as they
+// alternate the two y buffers: a peer is never more than one call ahead of a rank that still polls.
+constexpr int kStatusExchangePoll = 7;  // a peer's packets did not arrive in time
+
+struct PacketParams {
+  uint8_t* y;                 // this rank's whole y
+  uint4* box[kMaxRanks];      // every rank's receive buffer (peer-mapped): region r holds what rank r sent
+  int64_t region;             // packets per region
+  int64_t col0[kMaxRanks + 1];  // first column of every rank's slice; col0[ranks] = all columns
+  uint32_t* seq;              // calls finished on this pair of buffers
+  int* done;                  // CTAs finished (zero between calls)
+  int ranks, self, M, elem;
+  int64_t pitch;              // bytes between rows of y
+  int* status;
+  uint64_t budget_ns;
+};
+
+__global__ void __launch_bounds__(256) exchange_packets_kernel(const PacketParams P) {
+  pdl_trigger();
+  pdl_wait();  // the slice comes from the product before this kernel
+  uint32_t seq;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(seq) : "l"(P.seq) : "memory");
+  seq += 1;  // the flag of this call: never zero in a zeroed buffer's lifetime
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x, nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  {  // send: this rank's slice, 8 bytes per packet, to region `self` of every peer
+    const int64_t per_row = (P.col0[P.self + 1] - P.col0[P.self]) * P.elem / 8, total = per_row * P.M;
+    const uint8_t* src = P.y + P.col0[P.self] * P.elem;
+    for (int64_t i = tid; i < total; i += nthreads) {
+      const int64_t m = i / per_row;
+      const uint2 d = *reinterpret_cast<const uint2*>(src + m * P.pitch + (i - m * per_row) * 8);
+      for (int r = 0; r < P.ranks; ++r)
+        if (r != P.self)
+          asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(P.box[r] + P.self * P.region + i), "r"(d.x), "r"(seq), "r"(d.y), "r"(seq)
+                       : "memory");
+    }
+  }
+  const uint64_t t0 = global_timer_ns();
+  bool gave_up = false;
+  for (int r = 0; r < P.ranks && !gave_up; ++r) {  // receive: poll every peer's packets and put them where they belong in y
+    if (r == P.self) continue;
+    const int64_t per_row = (P.col0[r + 1] - P.col0[r]) * P.elem / 8, total = per_row * P.M;
+    uint8_t* dst = P.y + P.col0[r] * P.elem;
+    const uint4* in = P.box[P.self] + r * P.region;
+    for (int64_t i = tid; i < total && !gave_up; i += nthreads) {
+      uint32_t a, fa, b, fb;
+      for (int spin = 0;; ++spin) {
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(fa), "=r"(b), "=r"(fb) : "l"(in + i) : "memory");
+        if (fa == seq && fb == seq) break;
+        if ((spin & 63) == 63 && global_timer_ns() - t0 > P.budget_ns) {  // a peer that never sends: give up and say so
+          gave_up = true;
+          break;
+        }
+      }
+      if (gave_up) break;
+      const int64_t m = i / per_row;
+      *reinterpret_cast<uint2*>(dst + m * P.pitch + (i - m * per_row) * 8) = make_uint2(a, b);
+    }
+  }
+  if (gave_up && P.status) atomicExch(P.status, kStatusExchangePoll);
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  __threadfence();
+  int before;
+  asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(before) : "l"(P.done) : "memory");
+  if (before != static_cast<int>(gridDim.x) - 1) return;
+  asm volatile("st.relaxed.gpu.global.s32 [%0], %1;" ::"l"(P.done), "r"(0) : "memory");
+  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(P.seq), "r"(seq) : "memory");  // also after a timeout: the next call uses the next number
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -107,4 +187,43 @@ extern "C" int lx_b200_exchange_slices(void* const* y_all, int* const* arrivals,
   if (V == 16) return launch_kernel(exchange_kernel<16>, dim3(grid), dim3(256), 0, s, P);
   if (V == 4) return launch_kernel(exchange_kernel<4>, dim3(grid), dim3(256), 0, s, P);
   return launch_kernel(exchange_kernel<2>, dim3(grid), dim3(256), 0, s, P);
+}
+
+// bounds: ranks + 1 column indices, rank r owns columns [bounds[r], bounds[r + 1]) of the [M, ld_y] output. boxes: every
+// rank's receive buffer of ranks * region packets of 16 bytes, zeroed once when allocated. seq and done: two zeroed
+// words of this rank's own memory that belong to these boxes. Every slice row must be whole 8-byte pieces.
+extern "C" int lx_b200_exchange_packets(void* y, void* const* boxes, int64_t region, uint32_t* seq, int* done, int ranks, int rank,
+                                        const int64_t* bounds, lx_dtype y_dtype, int ld_y, int M, void* stream) {
+  if (!y || !boxes || !seq || !done || !bounds || ranks < 1 || ranks > kMaxRanks || rank < 0 || rank >= ranks) return kInvalid;
+  if (M <= 0) return kOk;
+  if (!valid_dtype(y_dtype) || region <= 0) return kInvalid;
+  PacketParams P{};
+  P.elem = y_dtype == LX_BF16 ? 2 : 4;
+  P.pitch = static_cast<int64_t>(ld_y) * P.elem;
+  if (!aligned(y, 8) || P.pitch % 8 != 0) return kNotSupported;
+  int64_t most = 0;
+  for (int r = 0; r <= ranks; ++r) {
+    P.col0[r] = bounds[r];
+    if (r > 0) {
+      const int64_t cols = bounds[r] - bounds[r - 1];
+      if (cols < 0 || (cols * P.elem) % 8 != 0 || (bounds[r - 1] * P.elem) % 8 != 0) return cols < 0 ? kInvalid : kNotSupported;
+      if (cols * P.elem / 8 * M > region) return kInvalid;
+      most = std::max(most, cols * P.elem / 8 * M);
+    }
+  }
+  if (bounds[0] < 0 || bounds[ranks] > ld_y) return kInvalid;
+  for (int r = 0; r < ranks; ++r) {
+    if (!boxes[r] || !aligned(boxes[r], 16)) return kInvalid;
+    P.box[r] = static_cast<uint4*>(boxes[r]);
+  }
+  P.y = static_cast<uint8_t*>(y);
+  P.region = region;
+  P.seq = seq, P.done = done;
+  P.ranks = ranks, P.self = rank, P.M = M;
+  P.status = status_word();
+  uint64_t ms = 1000;  // LX_B200_WAIT_MS: how long the polls may last (default 1000; read on every call)
+  if (const char* v = std::getenv("LX_B200_WAIT_MS")) ms = static_cast<uint64_t>(std::max(1, std::min(10000, atoi(v))));
+  P.budget_ns = ms * 1000000ull;
+  const unsigned grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(148, (most + 255) / 256)));
+  return launch_kernel(exchange_packets_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), P);
 }

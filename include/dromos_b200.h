@@ -209,6 +209,18 @@ LX_API int lx_b200_wait_arrivals(int* counter, int total, void* stream);
  * that a rank one round ahead never overwrites what a slower rank still reads. */
 LX_API int lx_b200_exchange_slices(void* const* y_all, int* const* arrivals, int ranks, int rank, int64_t col0, int cols,
                                    lx_dtype y_dtype, int ld_y, int M, void* stream);
+/* The same all-gather for small slices, with the flag inside the data (no counterpart in the reference). Rank r owns
+ * columns bounds[r] .. bounds[r + 1] - 1 of the [M, ld_y] output y (this rank's own buffer; ranks + 1 host integers).
+ * The call sends this rank's slice as 16-byte packets {8 bytes of y, sequence, 8 bytes, sequence} into region `rank` of
+ * every peer's receive buffer boxes[r] (host array of peer-mapped device pointers; each buffer is ranks * region packets,
+ * zeroed once when allocated), polls the packets the peers send it and unpacks them into y: no fence and no semaphore on
+ * the critical path, twice the bytes on the wire. seq and done are two zeroed words of this rank's own device memory that
+ * belong to these buffers: the sequence number is kept on the device, so the call can sit in a replayed graph. Callers
+ * alternate two sets (boxes, seq, done, y) so that a rank one call ahead never overwrites packets a slower rank still
+ * polls. Slice rows must be whole 8-byte pieces (else LX_ERR_NOT_SUPPORTED). The polls are bounded (LX_B200_WAIT_MS);
+ * one that gives up shows as 7 in lx_b200_last_error and the next call still uses the next sequence number. */
+LX_API int lx_b200_exchange_packets(void* y, void* const* boxes, int64_t region, uint32_t* seq, int* done, int ranks, int rank,
+                                    const int64_t* bounds, lx_dtype y_dtype, int ld_y, int M, void* stream);
 
 /* Routed experts for callers that must not allocate. No counterpart in the reference: its lx_moe_experts_grouped always
  * takes a caller workspace. Same arguments, result and error codes as lx_moe_experts_grouped above minus the workspace:

@@ -32,16 +32,22 @@ def main():
     for wtype in (abi.W_BF16, abi.W_INT8, abi.W_FP8, abi.W_NVFP4, abi.W_BF16X):
         buffers = host.PeerBuffers(N, 64, dev)
         whole = host.Linear(lib, host.store_weight(lib, w, wtype), N, K)
-        layer = host.PeerShardedLinear(lib, host.store_weight(lib, w[n0:n1].contiguous(), wtype), N, K, buffers)
-        for rnd, M in enumerate((1, 8, 3, 16, 64, 5)):
+        if wtype == abi.W_NVFP4:  # a shard of an NVFP4 checkpoint keeps the whole matrix's global scale: slice the stored rows
+            s = whole.weight
+            shard = host.StoredWeight(wtype, s.data.view(N, K // 2)[n0:n1].contiguous(), s.scale.view(N, K // 16)[n0:n1].contiguous(), s.glob,
+                                      rows=n1 - n0, cols=K)
+        else:
+            shard = host.store_weight(lib, w[n0:n1].contiguous(), wtype)
+        layer = host.PeerShardedLinear(lib, shard, N, K, buffers)
+        for rnd, M in enumerate((1, 8, 3, 16, 64, 5, 2, 33)):
             x = torch.randn((M, K), generator=gen, device=dev).to(torch.bfloat16)
+            layer.packets = [None, True, False][rnd % 3]  # the default choice, packets forced, the semaphore exchange forced
+            if layer.packets and M * ((n1 - n0) * 4 // 8) > buffers.region:
+                layer.packets = None
             got = layer(x).clone()
             want = whole(x)
             torch.cuda.synchronize()
-            if wtype == abi.W_NVFP4:  # a shard quantized alone has its own global scale: compare by value
-                ok = torch.allclose(got, want, rtol=0, atol=2e-2 * float(want.abs().max()))
-            else:
-                ok = torch.equal(got.view(torch.int32), want.view(torch.int32))
+            ok = torch.equal(got.view(torch.int32), want.view(torch.int32))
             if not ok:
                 failures.append(f"rank {rank} wtype {wtype} round {rnd} M={M}: exchanged y differs from the unsharded product "
                                 f"(max abs {float((got - want).abs().max()):.3e})")
@@ -54,28 +60,36 @@ def main():
     buffers = host.PeerBuffers(N, 8, dev)
     layer = host.PeerShardedLinear(lib, host.store_weight(lib, w[n0:n1].contiguous(), abi.W_FP8), N, K, buffers)
     x = torch.randn((2, K), generator=gen, device=dev).to(torch.bfloat16)
-    layer(x)
-    torch.cuda.synchronize()
-    dist.barrier()
-    if rank == 0:
-        layer(x)  # the others skip this round: rank 0 waits 50 ms, gives up and says so
-        torch.cuda.synchronize()
-        code = lib.lx_b200_last_error()
-        if code != 6:
-            failures.append(f"rank 0: expected status 6 after a round nobody joined, got {code}")
-    else:
-        buffers.next_half()  # keep the buffer halves in step with rank 0
-    dist.barrier()
-    # rank 0's lone arrival is still in everyone's semaphore: drain it, then a normal round works again
-    buffers.counter.zero_()
-    torch.cuda.synchronize()
-    dist.barrier()
-    got = layer(x).clone()
-    torch.cuda.synchronize()
     want = host.Linear(lib, host.store_weight(lib, w, abi.W_FP8), N, K)(x)
-    torch.cuda.synchronize()
-    if not torch.equal(got.view(torch.int32), want.view(torch.int32)) or lib.lx_b200_last_error() != 0:
-        failures.append(f"rank {rank}: the round after the abandoned one is wrong")
+    for packets, code_wanted in ((False, 6), (True, 7)):
+        layer.packets = packets
+        layer(x)
+        torch.cuda.synchronize()
+        dist.barrier()
+        if rank == 0:
+            layer(x)  # the others skip this round: rank 0 waits 50 ms, gives up and says so
+            torch.cuda.synchronize()
+            code = lib.lx_b200_last_error()
+            if code != code_wanted:
+                failures.append(f"rank 0: expected status {code_wanted} after a round nobody joined, got {code}")
+        else:
+            buffers.next_half()  # keep the buffer halves in step with rank 0
+        dist.barrier()
+        if packets:
+            # the sequence numbers live on each rank: the ranks that skipped the call put theirs forward by hand, which a
+            # caller that abandons a round has to do (here: both buffers' words from rank 0, whose count is right)
+            seq = buffers.seq.clone()
+            dist.broadcast(seq, src=0)
+            buffers.seq[:, 0].copy_(seq[:, 0])
+        else:
+            # rank 0's lone arrival is still in everyone's semaphore: drain it, then a normal round works again
+            buffers.counter.zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+        got = layer(x).clone()
+        torch.cuda.synchronize()
+        if not torch.equal(got.view(torch.int32), want.view(torch.int32)) or lib.lx_b200_last_error() != 0:
+            failures.append(f"rank {rank}: the round after the abandoned one is wrong (packets={packets})")
     flag = torch.tensor([len(failures)], device=dev)
     dist.all_reduce(flag)
     for f in failures:
