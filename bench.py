@@ -86,7 +86,7 @@ def config_of(name, world, scaling, exchange):
     if world == 1:
         par = "single GPU"
     elif name in MOE:
-        par = f"experts split over {world} GPUs, routed rows exchanged"
+        par = f"experts split over {world} GPUs, routing and tokens replicated, weighted rows exchanged"
     elif scaling == "strong":
         par = f"the configuration's rows of W split over {world} GPUs, activations replicated, y slices exchanged"
     else:
@@ -531,44 +531,53 @@ def moe_leg(G, name, steps, warmup, peaks):
     torch, dist, lib, dev, world, rank = G.torch, G.dist, G.lib, G.dev, G.world, G.rank
     wtype, E, top_k, L, I, T, desc = MOE[name]
     e0, e1 = host.expert_range(E, rank, world)
-    gen = torch.Generator(device=dev).manual_seed(0)
+    gen = torch.Generator(device=dev).manual_seed(0)  # the same stacks, tokens and logits on every rank
     per_expert = (2 * I * L + L * I) + 4 * (2 * I + L)  # bytes of one expert: both stacks and their row scales
     local_bytes = per_expert * (e1 - e0)
     copies = max(2, -(-ROTATE_BYTES // local_bytes) + 1)
-    stacks = []
-    for c in range(copies):
-        if c == 0:
-            gu = host.store_weight(lib, (torch.randn((e1 - e0, 2 * I, L), generator=gen, device=dev) * 0.02).to(torch.bfloat16), wtype)
-            dn = host.store_weight(lib, (torch.randn((e1 - e0, L, I), generator=gen, device=dev) * 0.02).to(torch.bfloat16), wtype)
-        else:
-            gu = host.StoredWeight(wtype, stacks[0][0].data.clone(), stacks[0][0].scale.clone(), stacks[0][0].glob, rows=stacks[0][0].rows, cols=L)
-            dn = host.StoredWeight(wtype, stacks[0][1].data.clone(), stacks[0][1].scale.clone(), stacks[0][1].glob, rows=stacks[0][1].rows, cols=I)
-        stacks.append((gu, dn))
-    t0, t1 = T * rank // world, T * (rank + 1) // world  # this rank's tokens
+    whole_gu = host.store_weight(lib, (torch.randn((E, 2 * I, L), generator=gen, device=dev) * 0.02).to(torch.bfloat16), wtype)
+    whole_dn = host.store_weight(lib, (torch.randn((E, L, I), generator=gen, device=dev) * 0.02).to(torch.bfloat16), wtype)
+
+    def own_slice(s, rows_per, cols):  # this rank's experts of a stored stack (row-wise formats: the rows and their scales)
+        data = s.data.view(E, -1)[e0:e1].contiguous().view(-1)
+        scale = None if s.scale is None else s.scale.view(E, -1)[e0:e1].contiguous().view(-1)
+        return host.StoredWeight(wtype, data, scale, s.glob, rows=(e1 - e0) * rows_per, cols=cols)
+
+    stacks = [(own_slice(whole_gu, 2 * I, L), own_slice(whole_dn, L, I)) if world > 1 else (whole_gu, whole_dn)]
+    for c in range(1, copies):
+        g0, d0 = stacks[0]
+        stacks.append((host.StoredWeight(wtype, g0.data.clone(), None if g0.scale is None else g0.scale.clone(), g0.glob, rows=g0.rows, cols=L),
+                       host.StoredWeight(wtype, d0.data.clone(), None if d0.scale is None else d0.scale.clone(), d0.glob, rows=d0.rows, cols=I)))
+    t0, t1 = T * rank // world, T * (rank + 1) // world  # the tokens whose outputs this rank hands back end to end
     periods = 8  # distinct routings
-    logits = [torch.randn((T, E), generator=torch.Generator(device=dev).manual_seed(100 + i), device=dev)[t0:t1].contiguous() for i in range(periods)]
-    latent = torch.randn((T, L), generator=gen, device=dev).to(torch.bfloat16)[t0:t1].contiguous()
-    engines = [(host.Experts if world == 1 else host.ExpertParallel)(lib, gu, dn, E, L, I, top_k) for gu, dn in stacks]
-    router = host.Experts(lib, stacks[0][0], stacks[0][1], E, L, I, top_k)
-    out = torch.empty((t1 - t0, L), dtype=torch.float32, device=dev)
-    touched = []
-    for i in range(periods):  # the experts each routing touches, whole job (the same seeds on every rank give the same T x E logits)
-        full = torch.randn((T, E), generator=torch.Generator(device=dev).manual_seed(100 + i), device=dev)
-        touched.append(int(torch.unique(torch.topk(full, top_k, dim=1).indices).numel()))
+    logits = [torch.randn((T, E), generator=torch.Generator(device=dev).manual_seed(100 + i), device=dev) for i in range(periods)]
+    latent = torch.randn((T, L), generator=gen, device=dev).to(torch.bfloat16)
+    if world == 1:
+        engines = [host.Experts(lib, gu, dn, E, L, I, top_k) for gu, dn in stacks]
+    else:  # routing and tokens replicated, each rank its own experts, the weighted rows exchanged as packets over peer memory
+        engines = [host.ReplicatedExpertParallel(lib, gu, dn, E, L, I, top_k, T, dev) for gu, dn in stacks]
+    router = host.Experts(lib, whole_gu, whole_dn, E, L, I, top_k)
+    out = torch.empty((T, L), dtype=torch.float32, device=dev)
+    touched = [int(torch.unique(torch.topk(lg, top_k, dim=1).indices).numel()) for lg in logits]  # experts each routing touches, whole job
 
     def step(i):
         ids, w = router.route(logits[i % periods])
-        if world == 1:
-            engines[i % copies](latent, ids, w, out)
-        else:
-            out.copy_(engines[i % copies](latent, ids, w))
+        engines[i % copies](latent, ids, w, out)
 
-    graphs_ok = G.use_graphs and world == 1  # the expert-parallel exchange sizes its buffers on the host
-    saved, G.use_graphs = G.use_graphs, graphs_ok
-    try:
-        ms, launches, _ = G.timed_steps(step, steps, warmup, periods * copies if graphs_ok else 1)
-    finally:
-        G.use_graphs = saved
+    parity = None
+    if world > 1:  # every rank holds the whole stacks once: the split result must be one GPU's, bit for bit
+        ids, w = router.route(logits[0])
+        want = router(latent, ids, w)
+        got = engines[0](latent, ids, w, out)
+        torch.cuda.synchronize()
+        bad = int((got.view(torch.int32) != want.view(torch.int32)).sum().item())
+        flag = torch.tensor([bad], device=dev)
+        dist.all_reduce(flag)
+        parity = {"ok": int(flag.item()) == 0, "columns": T * L, "mismatches": int(flag.item()),
+                  "how": "every rank also runs lx_moe_experts_grouped on the whole stacks and compares its split result bit for bit"}
+    if world == 1:
+        del whole_gu, whole_dn
+    ms, launches, _ = G.timed_steps(step, steps, warmup, periods * copies)
     step_bytes = [per_expert * touched[(warmup + i) % periods] for i in range(steps)]
     value = sum(step_bytes) / (ms * 1e-3) / 1e12
     peak, peak_kind, read_only = peaks
@@ -576,18 +585,15 @@ def moe_leg(G, name, steps, warmup, peaks):
     # end to end: logits and latent from pinned host memory in, the tokens' outputs out, every step
     lh = [x.cpu().pin_memory() for x in logits]
     xh = latent.cpu().pin_memory()
-    oh = torch.empty(out.shape, dtype=torch.float32).pin_memory()
+    oh = torch.empty((t1 - t0, L), dtype=torch.float32).pin_memory()
     ld, xd = torch.empty_like(logits[0]), torch.empty_like(latent)
 
     def e2e_step(i):
         ld.copy_(lh[i % periods], non_blocking=True)
         xd.copy_(xh, non_blocking=True)
         ids, w = router.route(ld)
-        if world == 1:
-            engines[i % copies](xd, ids, w, out)
-        else:
-            out.copy_(engines[i % copies](xd, ids, w))
-        oh.copy_(out, non_blocking=True)
+        engines[i % copies](xd, ids, w, out)
+        oh.copy_(out[t0:t1], non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     for i in range(3):
@@ -602,9 +608,13 @@ def moe_leg(G, name, steps, warmup, peaks):
                         "frac_of_read_only": achieved / read_only if read_only else None, "kernel": KERNELS[name],
                         "algorithmic_bytes_per_launch": sum(step_bytes) / len(step_bytes),
                         "achieved_is": "bytes of the experts a step's routing touches / step time (all kernels of the step), CUDA events"},
-           "e2e": {"value": e2e_bytes / (e2e_ms * 1e-3) / 1e12, "unit": "TB/s", "h2d_bytes_per_step": (t1 - t0) * (E * 4 + L * 2),
+           "e2e": {"value": e2e_bytes / (e2e_ms * 1e-3) / 1e12, "unit": "TB/s", "h2d_bytes_per_step": T * (E * 4 + L * 2),
                    "d2h_bytes_per_step": (t1 - t0) * L * 4},
-           "gpu_launches": int(launches), "exchange": "none" if world == 1 else "all-to-all of routed rows (NCCL)", "dtype": DTYPE[wtype]}
+           "gpu_launches": int(launches),
+           "exchange": "none" if world == 1 else "lx_b200_moe_exchange_rows (routing and tokens replicated; weighted rows as flag-in-data packets over peer memory)",
+           "dtype": DTYPE[wtype]}
+    if parity is not None:
+        rec["parity_check"] = parity
     del stacks, engines
     torch.cuda.empty_cache()
     return rec

@@ -90,6 +90,9 @@ EXTENSIONS = {
     "lx_b200_wait_arrivals": (c_int, [c_ptr, c_int, c_ptr]),
     # y_all, arrivals, ranks, rank, col0, cols, y_dtype, ld_y, M, stream
     "lx_b200_exchange_slices": (c_int, [c_ptr, c_ptr, c_int, c_int, c_i64, c_int, c_int, c_int, c_int, c_ptr]),
+    "lx_b200_moe_experts_owned": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_ptr]),
+    "lx_b200_moe_exchange_rows": (c_int, [c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_int, c_int, c_ptr, c_int, c_int, c_int, c_int, c_int, c_ptr]),
+    "lx_b200_moe_sum_rows": (c_int, [c_ptr, c_ptr, c_int, c_int, c_int, c_ptr]),
     "lx_b200_exchange_packets": (c_int, [c_ptr, c_ptr, c_i64, c_ptr, c_ptr, c_int, c_int, c_ptr, c_int, c_int, c_int, c_ptr]),
 }
 ERR_SCRATCH = 804

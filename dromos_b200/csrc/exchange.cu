@@ -84,13 +84,14 @@ __global__ void __launch_bounds__(256) exchange_kernel(const ExchangeParams P) {
 // for small slices only.
 //
 // The sequence number lives in device memory (the call can sit in a replayed graph): every CTA reads it on entry, the
-// last CTA to finish adds one. Callers alternate two receive buffers (each with its own sequence word), as they
-// alternate the two y buffers: a peer is never more than one call ahead of a rank that still polls.
+// last CTA to finish adds one. A peer can be one call ahead of a rank that still polls, never two, so every receive
+// buffer has two halves and a call uses the half its sequence number's parity names: chosen on the device, the same on
+// every rank, whatever the number of calls a replayed graph holds.
 constexpr int kStatusExchangePoll = 7;  // a peer's packets did not arrive in time
 
 struct PacketParams {
   uint8_t* y;                 // this rank's whole y
-  uint4* box[kMaxRanks];      // every rank's receive buffer (peer-mapped): region r holds what rank r sent
+  uint4* box[kMaxRanks];      // every rank's receive buffer (peer-mapped): two halves of `ranks` regions; region r holds what rank r sent
   int64_t region;             // packets per region
   int64_t col0[kMaxRanks + 1];  // first column of every rank's slice; col0[ranks] = all columns
   uint32_t* seq;              // calls finished on this pair of buffers
@@ -106,6 +107,7 @@ __global__ void __launch_bounds__(256) exchange_packets_kernel(const PacketParam
   pdl_wait();  // the slice comes from the product before this kernel
   uint32_t seq;
   asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(seq) : "l"(P.seq) : "memory");
+  const int64_t half = static_cast<int64_t>(seq & 1u) * P.ranks * P.region;  // this call's half of every receive buffer
   seq += 1;  // the flag of this call: never zero in a zeroed buffer's lifetime
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x, nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
   {  // send: this rank's slice, 8 bytes per packet, to region `self` of every peer
@@ -116,7 +118,7 @@ __global__ void __launch_bounds__(256) exchange_packets_kernel(const PacketParam
       const uint2 d = *reinterpret_cast<const uint2*>(src + m * P.pitch + (i - m * per_row) * 8);
       for (int r = 0; r < P.ranks; ++r)
         if (r != P.self)
-          asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(P.box[r] + P.self * P.region + i), "r"(d.x), "r"(seq), "r"(d.y), "r"(seq)
+          asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(P.box[r] + half + P.self * P.region + i), "r"(d.x), "r"(seq), "r"(d.y), "r"(seq)
                        : "memory");
     }
   }
@@ -126,7 +128,7 @@ __global__ void __launch_bounds__(256) exchange_packets_kernel(const PacketParam
     if (r == P.self) continue;
     const int64_t per_row = (P.col0[r + 1] - P.col0[r]) * P.elem / 8, total = per_row * P.M;
     uint8_t* dst = P.y + P.col0[r] * P.elem;
-    const uint4* in = P.box[P.self] + r * P.region;
+    const uint4* in = P.box[P.self] + half + r * P.region;
     for (int64_t i = tid; i < total && !gave_up; i += nthreads) {
       uint32_t a, fa, b, fb;
       for (int spin = 0;; ++spin) {
@@ -190,7 +192,7 @@ extern "C" int lx_b200_exchange_slices(void* const* y_all, int* const* arrivals,
 }
 
 // bounds: ranks + 1 column indices, rank r owns columns [bounds[r], bounds[r + 1]) of the [M, ld_y] output. boxes: every
-// rank's receive buffer of ranks * region packets of 16 bytes, zeroed once when allocated. seq and done: two zeroed
+// rank's receive buffer of 2 * ranks * region packets of 16 bytes, zeroed once when allocated. seq and done: two zeroed
 // words of this rank's own memory that belong to these boxes. Every slice row must be whole 8-byte pieces.
 extern "C" int lx_b200_exchange_packets(void* y, void* const* boxes, int64_t region, uint32_t* seq, int* done, int ranks, int rank,
                                         const int64_t* bounds, lx_dtype y_dtype, int ld_y, int M, void* stream) {

@@ -202,7 +202,7 @@ bool experts_tc_ok(const lx_weight& gate_up, const lx_weight& down, int L, int I
 int64_t experts_tc_workspace(int64_t base, int P, int E, int L, int I);
 int experts_tc(const void* latent, const float* weights, const lx_weight& gate_up, const lx_weight& down, const int32_t* offsets,
                const int32_t* pairs, uint16_t* mid, float* rows, uint8_t* ws, int64_t base, int T, int L, int I, int E, int top_k,
-               int* status, cudaStream_t stream, bool quantized = false);
+               int* status, cudaStream_t stream, bool quantized = false, int stack_experts = 0);
 bool tc_rows_ok(const lx_weight& w, int N, int K);
 bool gemv_shape_ok(int wtype, int K, bool x_bf16);
 bool tc_rows_shape_ok(int wtype, int N, int K);

@@ -208,9 +208,12 @@ __global__ void __launch_bounds__(256) rows_gemv_f32_kernel(const float* __restr
 // One CTA of 1024 threads, thread e walks the ids (staged in shared memory when there are at most 8192 of them: the
 // walk is then ~P shared-memory reads, not P dependent global loads); E <= 1024.
 constexpr int kGroupStaged = 8192;
+// own0 .. own1 - 1: the experts whose rows get chunks (all of them on one GPU; a rank's own experts when the experts are
+// split over ranks, and then a chunk names its expert by its index in the rank's stack). Rows of the other experts get
+// chunk -1: nothing is prepared or multiplied for them.
 __global__ void __launch_bounds__(1024) group_kernel(const int32_t* __restrict__ ids, int P, int E,
                                                      int32_t* __restrict__ offsets, int32_t* __restrict__ pairs,
-                                                     const ExpertChunkTables chunks) {
+                                                     const ExpertChunkTables chunks, int own0, int own1) {
   pdl_trigger();
   pdl_wait();
   __shared__ int32_t start[kMaxExperts + 1];
@@ -248,7 +251,10 @@ __global__ void __launch_bounds__(1024) group_kernel(const int32_t* __restrict__
   // The chunk tables of the tensor-core expert kernels: expert e's rows cut into chunks of up to 16.
   if (chunks.n_chunks) {
     __syncthreads();  // everyone has read start[]; it now holds each expert's chunk count
-    const int mine = (rows + kExpertChunkRows - 1) / kExpertChunkRows;
+    const bool own = e >= own0 && e < own1;
+    const int mine = own ? (rows + kExpertChunkRows - 1) / kExpertChunkRows : 0;
+    if (e < E && !own)
+      for (int m = 0; m < rows; ++m) chunks.pos_chunk[row0 + m] = -1;
     start[e] = e < E ? mine : 0;
     __syncthreads();
     int base = 0;
@@ -256,7 +262,7 @@ __global__ void __launch_bounds__(1024) group_kernel(const int32_t* __restrict__
     if (e == E - 1) *chunks.n_chunks = base + mine;
     for (int j = 0; j < mine; ++j) {
       const int c = base + j, first = row0 + j * kExpertChunkRows, n = min(kExpertChunkRows, rows - j * kExpertChunkRows);
-      chunks.chunk_expert[c] = e, chunks.chunk_row0[c] = first, chunks.chunk_rows[c] = n;
+      chunks.chunk_expert[c] = e - own0, chunks.chunk_row0[c] = first, chunks.chunk_rows[c] = n;
       for (int m = 0; m < n; ++m) chunks.pos_chunk[first + m] = c, chunks.pos_col[first + m] = m;
     }
   }
@@ -561,9 +567,170 @@ extern "C" int lx_moe_experts_grouped(const void* latent, const int32_t* ids, co
   auto* ws = static_cast<uint8_t*>(workspace);
   const ExpertChunkTables chunks = experts_tc_ok(*gate_up, *down, L, I) ? expert_chunk_tables(ws, l.total, P, E, L, I) : ExpertChunkTables{};
   if (int e = launch_kernel(group_kernel, dim3(1), dim3(1024), 0, s, ids, P, E, reinterpret_cast<int32_t*>(ws + l.offsets),
-                            reinterpret_cast<int32_t*>(ws + l.pairs), chunks))
+                            reinterpret_cast<int32_t*>(ws + l.pairs), chunks, 0, E))
     return e;
   return run_experts(latent, ids, weights, *gate_up, *down, out, ws, l, false, E, E, T, L, I, top_k, s, nullptr, quantized);
+}
+
+// ---- routed experts split over ranks (no counterpart in the reference, which is single-GPU) ----------------------------
+// Routing is replicated (every rank routes the same logits), and so are the tokens: at decode sizes the latent is a few
+// hundred KB, less than a dispatch would cost. A rank holds the stacks of its own experts only and computes the
+// weighted rows of the pairs that chose them (lx_b200_moe_experts_owned: grouping with an owned range, the two expert
+// stages); the rows then travel to every rank as flag-in-data packets (lx_b200_moe_exchange_rows) and every rank adds
+// each token's rows in k order (lx_b200_moe_sum_rows), exactly what one GPU with all experts adds: the result does not
+// depend on how the experts are split. Nothing here reads a device value on the host, so the three calls can be
+// captured in a graph.
+extern "C" int lx_b200_moe_experts_owned(const void* latent, const int32_t* ids, const float* weights, const lx_weight* gate_up,
+                                         const lx_weight* down, lx_math math, float* rows, void* workspace, int T, int L, int I,
+                                         int E, int own0, int own1, int top_k, void* stream) {
+  if (T < 0 || L <= 0 || I <= 0 || E <= 0 || top_k <= 0 || top_k > E || !gate_up || !down) return kInvalid;
+  if (own0 < 0 || own1 < own0 || own1 > E) return kInvalid;
+  if (math < LX_MATH_BF16 || math > LX_MATH_FP4) return kInvalid;
+  if (T == 0 || own1 == own0) return kOk;
+  if (!latent || !ids || !weights || !rows || !workspace || !gate_up->data || !down->data) return kInvalid;
+  if (gate_up->type < LX_W_BF16 || gate_up->type > LX_W_NVFP4 || down->type < LX_W_BF16 || down->type > LX_W_NVFP4)
+    return kNotSupported;
+  if ((gate_up->type != LX_W_BF16 && !gate_up->scale) || (down->type != LX_W_BF16 && !down->scale)) return kInvalid;
+  if (E > kMaxExperts || static_cast<int64_t>(T) * top_k > (1ll << 30)) return kNotSupported;
+  if (int e = math_admitted(math, gate_up->type)) return e;
+  if (int e = math_admitted(math, down->type)) return e;
+  if (I % 8 != 0 || L % 8 != 0 || !experts_tc_ok(*gate_up, *down, L, I)) return kNotSupported;  // the tensor-core kernels only
+  auto s = static_cast<cudaStream_t>(stream);
+  const int P = T * top_k;
+  const Layout l = layout(P, E, L, I);
+  auto* ws = static_cast<uint8_t*>(workspace);
+  const ExpertChunkTables chunks = expert_chunk_tables(ws, l.total, P, E, L, I);
+  if (int e = launch_kernel(group_kernel, dim3(1), dim3(1024), 0, s, ids, P, E, reinterpret_cast<int32_t*>(ws + l.offsets),
+                            reinterpret_cast<int32_t*>(ws + l.pairs), chunks, own0, own1))
+    return e;
+  return experts_tc(latent, weights, *gate_up, *down, reinterpret_cast<const int32_t*>(ws + l.offsets),
+                    reinterpret_cast<const int32_t*>(ws + l.pairs), reinterpret_cast<uint16_t*>(ws + l.mid), rows, ws, l.total, T, L, I, E,
+                    top_k, status_word(), s, math != LX_MATH_BF16, own1 - own0);
+}
+
+namespace b200 {
+namespace {
+constexpr int kStatusRowsPoll = 8;  // a peer's rows did not arrive in time
+
+struct RowPacketParams {
+  float* rows;              // f32 [P, L] by pair index
+  const int32_t* offsets;   // [E + 1] sorted position of every expert's first pair
+  const int32_t* pairs;     // [P] the pair at every sorted position
+  uint4* box[8];            // every rank's receive buffer: two halves of P * L / 2 packets, indexed like rows
+  int64_t half_packets;     // packets per half
+  int bound[9];             // rank r owns experts bound[r] .. bound[r + 1] - 1
+  uint32_t* seq;
+  int* done;
+  int ranks, self, L;
+  int* status;
+  uint64_t budget_ns;
+};
+
+// As exchange_packets_kernel (exchange.cu), for rows picked by the grouping tables: a rank sends the rows of the sorted
+// positions of its own experts and polls those of every other rank's experts; a packet's place in the buffer is the
+// place of its 8 bytes in `rows`.
+__global__ void __launch_bounds__(256) exchange_rows_kernel(const RowPacketParams P) {
+  pdl_trigger();
+  pdl_wait();
+  uint32_t seq;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(seq) : "l"(P.seq) : "memory");
+  const int64_t half = static_cast<int64_t>(seq & 1u) * P.half_packets;  // the half this call's parity names, on every rank alike
+  seq += 1;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x, nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int units = P.L / 2;
+  {
+    const int u0 = P.offsets[P.bound[P.self]], u1 = P.offsets[P.bound[P.self + 1]];
+    const int64_t total = static_cast<int64_t>(u1 - u0) * units;
+    for (int64_t i = tid; i < total; i += nthreads) {
+      const int u = u0 + static_cast<int>(i / units);
+      const int64_t at = static_cast<int64_t>(P.pairs[u]) * units + (i % units);
+      const uint2 d = reinterpret_cast<const uint2*>(P.rows)[at];
+      for (int r = 0; r < P.ranks; ++r)
+        if (r != P.self)
+          asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(P.box[r] + half + at), "r"(d.x), "r"(seq), "r"(d.y), "r"(seq) : "memory");
+    }
+  }
+  const uint64_t t0 = global_timer_ns();
+  bool gave_up = false;
+  for (int r = 0; r < P.ranks && !gave_up; ++r) {
+    if (r == P.self) continue;
+    const int u0 = P.offsets[P.bound[r]], u1 = P.offsets[P.bound[r + 1]];
+    const int64_t total = static_cast<int64_t>(u1 - u0) * units;
+    for (int64_t i = tid; i < total && !gave_up; i += nthreads) {
+      const int u = u0 + static_cast<int>(i / units);
+      const int64_t at = static_cast<int64_t>(P.pairs[u]) * units + (i % units);
+      uint32_t a, fa, b, fb;
+      for (int spin = 0;; ++spin) {
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(fa), "=r"(b), "=r"(fb) : "l"(P.box[P.self] + half + at) : "memory");
+        if (fa == seq && fb == seq) break;
+        if ((spin & 63) == 63 && global_timer_ns() - t0 > P.budget_ns) {
+          gave_up = true;
+          break;
+        }
+      }
+      if (gave_up) break;
+      reinterpret_cast<uint2*>(P.rows)[at] = make_uint2(a, b);
+    }
+  }
+  if (gave_up && P.status) atomicExch(P.status, kStatusRowsPoll);
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  __threadfence();
+  int before;
+  asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(before) : "l"(P.done) : "memory");
+  if (before != static_cast<int>(gridDim.x) - 1) return;
+  asm volatile("st.relaxed.gpu.global.s32 [%0], %1;" ::"l"(P.done), "r"(0) : "memory");
+  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(P.seq), "r"(seq) : "memory");
+}
+}  // namespace
+}  // namespace b200
+
+// workspace: the one lx_b200_moe_experts_owned just used with the same T, L, I, E, top_k (its grouping tables are read).
+// boxes: every rank's receive buffer of 2 * half_packets packets of 16 bytes (peer-mapped, zeroed once), half_packets >=
+// T * top_k * L / 2: a call uses the half its sequence number's parity names. seq, done: two zeroed words of this rank's
+// memory that belong to the buffers; bounds: ranks + 1 expert indices.
+extern "C" int lx_b200_moe_exchange_rows(float* rows, const void* workspace, void* const* boxes, int64_t half_packets, uint32_t* seq,
+                                         int* done, int ranks, int rank, const int* bounds, int T, int L, int I, int E, int top_k,
+                                         void* stream) {
+  if (!rows || !workspace || !boxes || !seq || !done || !bounds || ranks < 1 || ranks > 8 || rank < 0 || rank >= ranks) return kInvalid;
+  if (T <= 0) return kOk;
+  if (L <= 0 || L % 2 != 0 || I <= 0 || E <= 0 || top_k <= 0 || !aligned(rows, 8)) return kInvalid;
+  RowPacketParams P{};
+  for (int r = 0; r <= ranks; ++r) {
+    if (bounds[r] < 0 || bounds[r] > E || (r > 0 && bounds[r] < bounds[r - 1])) return kInvalid;
+    P.bound[r] = bounds[r];
+  }
+  if (bounds[0] != 0 || bounds[ranks] != E) return kInvalid;
+  for (int r = 0; r < ranks; ++r) {
+    if (!boxes[r] || !aligned(boxes[r], 16)) return kInvalid;
+    P.box[r] = static_cast<uint4*>(boxes[r]);
+  }
+  const int Pn = T * top_k;
+  if (half_packets < static_cast<int64_t>(Pn) * (L / 2)) return kInvalid;
+  P.half_packets = half_packets;
+  const Layout l = layout(Pn, E, L, I);
+  const auto* ws = static_cast<const uint8_t*>(workspace);
+  P.rows = rows;
+  P.offsets = reinterpret_cast<const int32_t*>(ws + l.offsets);
+  P.pairs = reinterpret_cast<const int32_t*>(ws + l.pairs);
+  P.seq = seq, P.done = done;
+  P.ranks = ranks, P.self = rank, P.L = L;
+  P.status = status_word();
+  uint64_t ms = 1000;  // LX_B200_WAIT_MS: how long the polls may last (default 1000; read on every call)
+  if (const char* v = std::getenv("LX_B200_WAIT_MS")) ms = static_cast<uint64_t>(std::max(1, std::min(10000, atoi(v))));
+  P.budget_ns = ms * 1000000ull;
+  const int64_t most = static_cast<int64_t>(Pn) * (L / 2);
+  const unsigned grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(148, (most + 1023) / 1024)));
+  return launch_kernel(exchange_rows_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), P);
+}
+
+// out[t, :] = rows[t * top_k + 0, :] + rows[t * top_k + 1, :] + ... in that order (the last stage of lx_moe_experts_grouped).
+extern "C" int lx_b200_moe_sum_rows(const float* rows, float* out, int T, int L, int top_k, void* stream) {
+  if (T <= 0) return kOk;
+  if (!rows || !out || L <= 0 || top_k <= 0) return kInvalid;
+  const int64_t n = static_cast<int64_t>(T) * L;
+  return launch_kernel(ordered_sum_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, static_cast<cudaStream_t>(stream), rows,
+                       out, T, L, top_k);
 }
 
 // ---- the same routed experts with no allocation anywhere -------------------------------------------------------------
@@ -642,7 +809,7 @@ extern "C" int lx_b200_moe_experts_grouped_static(const void* latent, const int3
   uint8_t* ws = base + kStaticHeaderBytes;
   const ExpertChunkTables chunks = experts_tc_ok(*gate_up, *down, L, I) ? expert_chunk_tables(ws, l.total, P, E, L, I) : ExpertChunkTables{};
   if (int e = launch_kernel(group_kernel, dim3(1), dim3(1024), 0, s, ids, P, E, reinterpret_cast<int32_t*>(ws + l.offsets),
-                            reinterpret_cast<int32_t*>(ws + l.pairs), chunks))
+                            reinterpret_cast<int32_t*>(ws + l.pairs), chunks, 0, E))
     return e;
   return run_experts(latent, ids, weights, *gate_up, *down, out, ws, l, false, E, E, T, L, I, top_k, s,
                      reinterpret_cast<int*>(base));

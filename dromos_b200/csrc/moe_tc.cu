@@ -69,6 +69,7 @@ __global__ void __launch_bounds__(128) expert_prep_kernel(const uint16_t* __rest
   pdl_wait();
   __shared__ float part[4];
   const int u = blockIdx.y, tid = threadIdx.x;
+  if (pos_chunk[u] < 0) return;  // a row of an expert another rank owns (the whole block leaves together)
   const int k0 = (blockIdx.x * 128 + tid) * V;
   const bool in_range = k0 < n_stages * kKS;
   const int64_t row = static_cast<int64_t>(top_k_or_0 ? pairs[u] / top_k_or_0 : u) * ld;
@@ -403,8 +404,9 @@ bool experts_tc_ok(const lx_weight& gate_up, const lx_weight& down, int L, int I
 // caller's workspace like `tc_ws`, the region ExpertTcLayout describes.
 int experts_tc(const void* latent, const float* weights, const lx_weight& gate_up, const lx_weight& down, const int32_t* offsets,
                const int32_t* pairs, uint16_t* mid, float* rows, uint8_t* ws, int64_t base, int T, int L, int I, int E, int top_k,
-               int* status, cudaStream_t stream, bool quantized) {
+               int* status, cudaStream_t stream, bool quantized, int stack_experts) {
   const int P = T * top_k;
+  if (stack_experts <= 0) stack_experts = E;  // experts the two stacks hold (a rank's own when the experts are split over ranks)
   const ExpertTcLayout lay(base, P, E, L, I);
   int32_t* n_chunks = reinterpret_cast<int32_t*>(ws + lay.n_chunks);
   int32_t* chunk_expert = reinterpret_cast<int32_t*>(ws + lay.chunk_expert);
@@ -466,9 +468,9 @@ int experts_tc(const void* latent, const float* weights, const lx_weight& gate_u
     G.chunk_stride = static_cast<int64_t>(n_stages) * Pm.x_bytes;
     int e;
     switch (gate_up.type) {
-      case LX_W_BF16: e = launch_expert<LX_W_BF16, kGateUpStage>(gate_up, G, static_cast<int64_t>(E) * 2 * I, chunks_expected, stream); break;
-      case LX_W_INT8: e = launch_expert<LX_W_INT8, kGateUpStage>(gate_up, G, static_cast<int64_t>(E) * 2 * I, chunks_expected, stream); break;
-      default: e = launch_expert<LX_W_FP8, kGateUpStage>(gate_up, G, static_cast<int64_t>(E) * 2 * I, chunks_expected, stream); break;
+      case LX_W_BF16: e = launch_expert<LX_W_BF16, kGateUpStage>(gate_up, G, static_cast<int64_t>(stack_experts) * 2 * I, chunks_expected, stream); break;
+      case LX_W_INT8: e = launch_expert<LX_W_INT8, kGateUpStage>(gate_up, G, static_cast<int64_t>(stack_experts) * 2 * I, chunks_expected, stream); break;
+      default: e = launch_expert<LX_W_FP8, kGateUpStage>(gate_up, G, static_cast<int64_t>(stack_experts) * 2 * I, chunks_expected, stream); break;
     }
     if (e) return e;
   }
@@ -482,9 +484,9 @@ int experts_tc(const void* latent, const float* weights, const lx_weight& gate_u
     D.chunk_stride = static_cast<int64_t>(n_stages) * Pm.x_bytes;
     int e;
     switch (down.type) {
-      case LX_W_BF16: e = launch_expert<LX_W_BF16, kDownStage>(down, D, static_cast<int64_t>(E) * L, chunks_expected, stream); break;
-      case LX_W_INT8: e = launch_expert<LX_W_INT8, kDownStage>(down, D, static_cast<int64_t>(E) * L, chunks_expected, stream); break;
-      default: e = launch_expert<LX_W_FP8, kDownStage>(down, D, static_cast<int64_t>(E) * L, chunks_expected, stream); break;
+      case LX_W_BF16: e = launch_expert<LX_W_BF16, kDownStage>(down, D, static_cast<int64_t>(stack_experts) * L, chunks_expected, stream); break;
+      case LX_W_INT8: e = launch_expert<LX_W_INT8, kDownStage>(down, D, static_cast<int64_t>(stack_experts) * L, chunks_expected, stream); break;
+      default: e = launch_expert<LX_W_FP8, kDownStage>(down, D, static_cast<int64_t>(stack_experts) * L, chunks_expected, stream); break;
     }
     if (e) return e;
   }

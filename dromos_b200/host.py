@@ -194,6 +194,75 @@ def remap_for_owner(ids: torch.Tensor, weights: torch.Tensor, e0: int, e1: int):
     return local_ids, local_w, mine
 
 
+class ReplicatedExpertParallel:
+    """Experts split over ranks with routing and tokens replicated: rank g holds the stacks of experts [g E / G, (g + 1) E / G)
+    and every rank calls with the same latent, ids and weights of all T tokens. Three library calls, no host read-back
+    (so the call can be captured in a graph): the weighted rows of this rank's experts, their exchange as flag-in-data
+    packets over peer memory, the sum of each token's rows in k order: bit for bit what Experts gives on one GPU.
+
+    The receive buffers (torch symmetric memory, plain peer mappings) are sized for max_tokens."""
+
+    def __init__(self, lib, gate_up_local: StoredWeight, down_local: StoredWeight, E: int, L: int, I: int, top_k: int, max_tokens: int,
+                 device, group=None, math: int = abi.MATH_BF16):
+        import torch.distributed as dist
+
+        self.lib, self.gate_up, self.down, self.E, self.L, self.I, self.top_k, self.math = lib, gate_up_local, down_local, E, L, I, top_k, math
+        self.dist, self.group = dist, group
+        multi = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if multi else 1
+        self.rank = dist.get_rank(group) if multi else 0
+        if self.world > 8:
+            raise RuntimeError("the row exchange addresses at most 8 ranks")
+        self.bounds = [expert_range(E, r, self.world)[0] for r in range(self.world)] + [E]
+        self.bounds_array = (ctypes.c_int * (self.world + 1))(*self.bounds)
+        self.max_tokens = max_tokens
+        self.rows = torch.empty((max_tokens * top_k, L), dtype=torch.float32, device=device)
+        self.ws = torch.empty(max(256, lib.lx_moe_grouped_workspace_bytes(max_tokens, L, I, E, top_k, math)), dtype=torch.uint8, device=device)
+        self.seq = torch.zeros((64,), dtype=torch.int32, device=device)  # word 0: sequence, word 32: CTA counter
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm
+
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            self.packets = max_tokens * top_k * (L // 2)
+            self.boxes = symm.empty((2, self.packets, 4), dtype=torch.int32, device=device)
+            self.boxes.zero_()
+            hb = symm.rendezvous(self.boxes, group if group is not None else dist.group.WORLD)
+            self.box_array = (ctypes.c_void_p * self.world)(*[int(p) for p in hb.buffer_ptrs])
+            torch.cuda.synchronize()
+            dist.barrier(group)
+
+    def owned(self, latent, ids, weights, e0: int | None = None, e1: int | None = None):
+        """The first call alone: this rank's (or the given range's) weighted rows into self.rows."""
+        T = latent.shape[0]
+        assert T <= self.max_tokens
+        e0 = self.bounds[self.rank] if e0 is None else e0
+        e1 = self.bounds[self.rank + 1] if e1 is None else e1
+        st = self.lib.lx_b200_moe_experts_owned(abi.ptr(latent), abi.ptr(ids), abi.ptr(weights), self.gate_up.ref(), self.down.ref(), self.math,
+                                                abi.ptr(self.rows), abi.ptr(self.ws), T, self.L, self.I, self.E, e0, e1, self.top_k, _stream())
+        if st:
+            raise RuntimeError(f"lx_b200_moe_experts_owned failed: {st}")
+
+    def sum(self, T: int, out: torch.Tensor):
+        st = self.lib.lx_b200_moe_sum_rows(abi.ptr(self.rows), abi.ptr(out), T, self.L, self.top_k, _stream())
+        if st:
+            raise RuntimeError(f"lx_b200_moe_sum_rows failed: {st}")
+        return out
+
+    def __call__(self, latent: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """latent bf16 [T, L], ids / weights [T, top_k] of ALL tokens (the same on every rank) -> f32 [T, L] on every rank."""
+        T = latent.shape[0]
+        if out is None:
+            out = torch.empty((T, self.L), dtype=torch.float32, device=latent.device)
+        self.owned(latent, ids, weights)
+        if self.world > 1:
+            st = self.lib.lx_b200_moe_exchange_rows(abi.ptr(self.rows), abi.ptr(self.ws), self.box_array, self.packets, abi.ptr(self.seq),
+                                                    abi.ptr(self.seq[32:]), self.world, self.rank, self.bounds_array, T, self.L, self.I, self.E,
+                                                    self.top_k, _stream())
+            if st:
+                raise RuntimeError(f"lx_b200_moe_exchange_rows failed: {st}")
+        return self.sum(T, out)
+
+
 class ExpertParallel:
     """Experts split over ranks: rank g holds experts [g E / G, (g + 1) E / G). Tokens are split over ranks too (rank g
     is home to tokens [g T / G, (g + 1) T / G)); the routed rows are exchanged with one all-to-all each way:
@@ -273,7 +342,12 @@ class ExpertParallel:
 class PeerBuffers:
     """What the ranks of a row-sharded layer share: two whole-y buffers used in turn (so that a rank one call ahead never
     overwrites the y a slower rank still reads) and the arrival counters, all torch symmetric memory (plain peer mappings,
-    multicast off), exchanged once at construction. One set serves any number of layers of the same output width."""
+    multicast off), exchanged once at construction. One set serves any number of layers of the same output width.
+
+    The y buffer of a call is picked here, on the host, by the count of calls: a captured graph that is replayed back to
+    back must hold an even number of calls, or the last call of one replay and the first of the next share a buffer and
+    a peer one call ahead stores into a y this rank may still read. (The packet exchange has no such rule: peers never
+    write into y, and the half of the receive buffer is picked on the device from the sequence number.)"""
 
     def __init__(self, N: int, max_rows: int, device, dtype=torch.float32, group=None):
         import torch.distributed as dist
@@ -307,7 +381,8 @@ class PeerBuffers:
         self.boxes.zero_()
         hb = symm.rendezvous(self.boxes, self.group)
         self.b_ptrs = [int(p) for p in hb.buffer_ptrs]
-        self.seq = torch.zeros((2, 64), dtype=torch.int32, device=device)  # word 0: sequence, word 32: CTA counter (separate lines)
+        self.seq = torch.zeros((64,), dtype=torch.int32, device=device)  # word 0: sequence, word 32: CTA counter (separate lines)
+        self.box_array = (ctypes.c_void_p * self.world)(*self.b_ptrs)
         self.bounds_array = (ctypes.c_int64 * (self.world + 1))(*self.bounds)
         self.calls = 0
         torch.cuda.synchronize()
@@ -322,10 +397,6 @@ class PeerBuffers:
         stride = self.max_rows * self.N * self.y.element_size()
         return (ctypes.c_void_p * self.world)(*[p + half * stride for p in self.y_ptrs])
 
-    def box_array(self, half: int):
-        stride = self.world * self.region * 16
-        return (ctypes.c_void_p * self.world)(*[p + half * stride for p in self.b_ptrs])
-
     def exchange(self, lib, half: int, M: int, packets: bool | None = None):
         """Makes y[half, :M] whole on every rank (every rank has written its own columns). packets: force one of the two
         exchanges; by default slices of at most packet_bytes travel as packets."""
@@ -338,8 +409,8 @@ class PeerBuffers:
         if packets:
             if not fits:
                 raise RuntimeError("the slices do not fit the packet buffers")
-            st = lib.lx_b200_exchange_packets(abi.ptr(self.y[half]), self.box_array(half), self.region, abi.ptr(self.seq[half]),
-                                              abi.ptr(self.seq[half, 32:]), self.world, self.rank, self.bounds_array, y_dt, self.N, M, _stream())
+            st = lib.lx_b200_exchange_packets(abi.ptr(self.y[half]), self.box_array, self.region, abi.ptr(self.seq), abi.ptr(self.seq[32:]),
+                                              self.world, self.rank, self.bounds_array, y_dt, self.N, M, _stream())
         else:
             st = lib.lx_b200_exchange_slices(self.y_array(half), self.c_array, self.world, self.rank, n0, n1 - n0, y_dt, self.N, M, _stream())
         if st:

@@ -212,15 +212,38 @@ LX_API int lx_b200_exchange_slices(void* const* y_all, int* const* arrivals, int
 /* The same all-gather for small slices, with the flag inside the data (no counterpart in the reference). Rank r owns
  * columns bounds[r] .. bounds[r + 1] - 1 of the [M, ld_y] output y (this rank's own buffer; ranks + 1 host integers).
  * The call sends this rank's slice as 16-byte packets {8 bytes of y, sequence, 8 bytes, sequence} into region `rank` of
- * every peer's receive buffer boxes[r] (host array of peer-mapped device pointers; each buffer is ranks * region packets,
- * zeroed once when allocated), polls the packets the peers send it and unpacks them into y: no fence and no semaphore on
- * the critical path, twice the bytes on the wire. seq and done are two zeroed words of this rank's own device memory that
- * belong to these buffers: the sequence number is kept on the device, so the call can sit in a replayed graph. Callers
- * alternate two sets (boxes, seq, done, y) so that a rank one call ahead never overwrites packets a slower rank still
- * polls. Slice rows must be whole 8-byte pieces (else LX_ERR_NOT_SUPPORTED). The polls are bounded (LX_B200_WAIT_MS);
+ * every peer's receive buffer boxes[r] (host array of peer-mapped device pointers; each buffer is two halves of
+ * ranks * region packets, zeroed once when allocated), polls the packets the peers send it and unpacks them into y: no
+ * fence and no semaphore on the critical path, twice the bytes on the wire. seq and done are two zeroed words of this
+ * rank's own device memory that belong to these buffers: the sequence number is kept on the device, so the call can sit
+ * in a replayed graph, and its parity names the half a call uses (a rank one call ahead never overwrites packets a
+ * slower rank still polls). Slice rows must be whole 8-byte pieces (else LX_ERR_NOT_SUPPORTED). The polls are bounded (LX_B200_WAIT_MS);
  * one that gives up shows as 7 in lx_b200_last_error and the next call still uses the next sequence number. */
 LX_API int lx_b200_exchange_packets(void* y, void* const* boxes, int64_t region, uint32_t* seq, int* done, int ranks, int rank,
                                     const int64_t* bounds, lx_dtype y_dtype, int ld_y, int M, void* stream);
+
+/* Routed experts split over ranks, in three calls that read nothing back on the host (no counterpart in the reference,
+ * which is single-GPU). Routing and tokens are replicated: every rank calls with the same latent [T, L], ids and weights
+ * [T, top_k] of ALL tokens, and holds gate_up / down stacks of its own experts own0 .. own1 - 1 only (expert own0 first).
+ *   lx_b200_moe_experts_owned   rows[p, :] = weights[p] * expert(ids[p], latent[p / top_k]) for the pairs p whose expert
+ *                               this rank owns (f32 [T * top_k, L], other rows untouched). Arguments, maths and errors as
+ *                               lx_moe_experts_grouped, workspace of lx_moe_grouped_workspace_bytes(T, L, I, E, top_k, math);
+ *                               stacks the tcgen05 expert kernels read as stored (BF16 / INT8 / FP8, one format).
+ *   lx_b200_moe_exchange_rows   sends this rank's rows to every rank and receives theirs, as flag-in-data packets (see
+ *                               lx_b200_exchange_packets; boxes[r]: two halves of half_packets >= T * top_k * L / 2 packets
+ *                               of 16 bytes, zeroed once; seq, done: two zeroed words of this rank's memory). workspace is the one the call above
+ *                               just used with the same sizes (its grouping tables say which rows are whose); bounds:
+ *                               ranks + 1 expert indices, rank r owns experts bounds[r] .. bounds[r + 1] - 1. A poll that
+ *                               gives up (LX_B200_WAIT_MS) shows as 8 in lx_b200_last_error.
+ *   lx_b200_moe_sum_rows        out[t, :] = rows[t * top_k, :] + rows[t * top_k + 1, :] + ... in that order: the bits one
+ *                               GPU with every expert gives, however the experts are split. */
+LX_API int lx_b200_moe_experts_owned(const void* latent, const int32_t* ids, const float* weights, const lx_weight* gate_up,
+                                     const lx_weight* down, lx_math math, float* rows, void* workspace, int T, int L, int I,
+                                     int E, int own0, int own1, int top_k, void* stream);
+LX_API int lx_b200_moe_exchange_rows(float* rows, const void* workspace, void* const* boxes, int64_t half_packets, uint32_t* seq,
+                                     int* done, int ranks, int rank, const int* bounds, int T, int L, int I, int E, int top_k,
+                                     void* stream);
+LX_API int lx_b200_moe_sum_rows(const float* rows, float* out, int T, int L, int top_k, void* stream);
 
 /* Routed experts for callers that must not allocate. No counterpart in the reference: its lx_moe_experts_grouped always
  * takes a caller workspace. Same arguments, result and error codes as lx_moe_experts_grouped above minus the workspace:

@@ -80,7 +80,7 @@ def main():
             # caller that abandons a round has to do (here: both buffers' words from rank 0, whose count is right)
             seq = buffers.seq.clone()
             dist.broadcast(seq, src=0)
-            buffers.seq[:, 0].copy_(seq[:, 0])
+            buffers.seq[0:1].copy_(seq[0:1])
         else:
             # rank 0's lone arrival is still in everyone's semaphore: drain it, then a normal round works again
             buffers.counter.zero_()
@@ -90,6 +90,45 @@ def main():
         torch.cuda.synchronize()
         if not torch.equal(got.view(torch.int32), want.view(torch.int32)) or lib.lx_b200_last_error() != 0:
             failures.append(f"rank {rank}: the round after the abandoned one is wrong (packets={packets})")
+    # ---- experts split over the ranks: replicated routing and tokens, rows exchanged as packets ----
+    os.environ["LX_B200_WAIT_MS"] = "1000"
+    E, top_k, L, I = 16, 4, 512, 384
+    gu_bf = (torch.randn((E, 2 * I, L), generator=gen, device=dev) * 0.03).to(torch.bfloat16)
+    dn_bf = (torch.randn((E, L, I), generator=gen, device=dev) * 0.03).to(torch.bfloat16)
+    e0, e1 = host.expert_range(E, rank, world)
+    for wtype in (abi.W_BF16, abi.W_FP8, abi.W_INT8):
+        plain = host.Experts(lib, host.store_weight(lib, gu_bf, wtype), host.store_weight(lib, dn_bf, wtype), E, L, I, top_k)
+        split = host.ReplicatedExpertParallel(lib, host.store_weight(lib, gu_bf[e0:e1].contiguous(), wtype), host.store_weight(lib, dn_bf[e0:e1].contiguous(), wtype),
+                                              E, L, I, top_k, 40, dev)
+        for T in (1, 32, 5, 40, 8, 8):
+            latent = torch.randn((T, L), generator=gen, device=dev).to(torch.bfloat16)
+            ids, weights = plain.route(torch.randn((T, E), generator=gen, device=dev))
+            want = plain(latent, ids, weights)
+            got = split(latent, ids, weights)
+            torch.cuda.synchronize()
+            if not torch.equal(got.view(torch.int32), want.view(torch.int32)):
+                failures.append(f"rank {rank} experts wtype {wtype} T={T}: split experts differ from one GPU's (max abs {float((got - want).abs().max()):.3e})")
+        if lib.lx_b200_last_error() != 0:
+            failures.append(f"rank {rank} experts wtype {wtype}: a bounded wait ran out")
+        dist.barrier()
+    # a round only rank 0 joins: its polls give up (status 8); the others put their sequence word forward; the next round is right
+    os.environ["LX_B200_WAIT_MS"] = "50"
+    if rank == 0:
+        split(latent, ids, weights)
+        torch.cuda.synchronize()
+        code = lib.lx_b200_last_error()
+        if code != 8:
+            failures.append(f"rank 0: expected status 8 after a row exchange nobody joined, got {code}")
+    dist.barrier()
+    seq = split.seq.clone()
+    dist.broadcast(seq, src=0)
+    split.seq[0:1].copy_(seq[0:1])
+    torch.cuda.synchronize()
+    dist.barrier()
+    got = split(latent, ids, weights)
+    torch.cuda.synchronize()
+    if not torch.equal(got.view(torch.int32), want.view(torch.int32)) or lib.lx_b200_last_error() != 0:
+        failures.append(f"rank {rank}: the row exchange after the abandoned one is wrong")
     flag = torch.tensor([len(failures)], device=dev)
     dist.all_reduce(flag)
     for f in failures:

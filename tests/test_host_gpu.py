@@ -53,3 +53,52 @@ def test_expert_parallel_with_one_rank_matches_the_grouped_experts(lx):
     # the owner runs one pair per row (top_k = 1) and the home rank adds the k rows: same products, same order of the sum
     assert torch.allclose(got, want, rtol=0, atol=2e-3 * float(want.abs().max()))
     util.check_status(lx)
+
+
+@pytest.mark.parametrize("wtype", [abi.W_BF16, abi.W_INT8, abi.W_FP8], ids=["bf16", "int8", "fp8"])
+@pytest.mark.parametrize("cuts", [(0, 8), (0, 3, 8), (0, 2, 2, 5, 8)], ids=["whole", "two", "four-one-empty"])
+def test_owned_experts_of_every_split_add_up_to_the_grouped_experts(lx, wtype, cuts):
+    """The expert-parallel path without its exchange, on one GPU: each "rank" computes the rows of its own experts from
+    its own slice of the stacks into one shared rows buffer, then the ordered sum: bit for bit lx_moe_experts_grouped,
+    however the experts are cut (an empty range and a range whose experts nobody chose included)."""
+    T, L, I, E, top_k = 19, 512, 256, 8, 3
+    gu_bf = (torch.randn((E, 2 * I, L), device="cuda") * 0.02).to(torch.bfloat16)
+    dn_bf = (torch.randn((E, L, I), device="cuda") * 0.02).to(torch.bfloat16)
+    latent = torch.randn((T, L), device="cuda").to(torch.bfloat16)
+    logits = torch.randn((T, E), device="cuda")
+    logits[:, 6] = -50.0  # nobody chooses expert 6
+    plain = host.Experts(lx, host.store_weight(lx, gu_bf, wtype), host.store_weight(lx, dn_bf, wtype), E, L, I, top_k)
+    ids, weights = plain.route(logits)
+    want = plain(latent, ids, weights)
+    shared = None
+    for e0, e1 in zip(cuts[:-1], cuts[1:]):
+        if e1 == e0:
+            continue
+        eng = host.ReplicatedExpertParallel(lx, host.store_weight(lx, gu_bf[e0:e1].contiguous(), wtype), host.store_weight(lx, dn_bf[e0:e1].contiguous(), wtype),
+                                            E, L, I, top_k, T, latent.device)
+        if shared is None:
+            shared = eng
+            shared.rows.fill_(float("nan"))
+        else:
+            eng.rows = shared.rows
+        eng.owned(latent, ids, weights, e0, e1)
+    got = shared.sum(T, torch.empty_like(want))
+    torch.cuda.synchronize()
+    assert torch.equal(got.view(torch.int32), want.view(torch.int32))
+    util.check_status(lx)
+
+
+def test_owned_experts_refuse_what_they_cannot_take(lx):
+    T, L, I, E, top_k = 4, 256, 128, 8, 2
+    gu = host.store_weight(lx, (torch.randn((E, 2 * I, L), device="cuda") * 0.02).to(torch.bfloat16), abi.W_NVFP4)
+    dn = host.store_weight(lx, (torch.randn((E, L, I), device="cuda") * 0.02).to(torch.bfloat16), abi.W_NVFP4)
+    eng = host.ReplicatedExpertParallel(lx, gu, dn, E, L, I, top_k, T, torch.device("cuda"))
+    latent = torch.randn((T, L), device="cuda").to(torch.bfloat16)
+    ids = torch.zeros((T, top_k), dtype=torch.int32, device="cuda")
+    w = torch.ones((T, top_k), device="cuda")
+    args = lambda own0, own1: (abi.ptr(latent), abi.ptr(ids), abi.ptr(w), gu.ref(), dn.ref(), abi.MATH_BF16, abi.ptr(eng.rows), abi.ptr(eng.ws), T, L, I,
+                               E, own0, own1, top_k, None)
+    assert lx.lx_b200_moe_experts_owned(*args(0, 8)) == 801   # NVFP4 stacks: not a format the expert tensor-core kernels read as stored
+    assert lx.lx_b200_moe_experts_owned(*args(5, 3)) == 1     # an empty-negative range
+    assert lx.lx_b200_moe_experts_owned(*args(0, 9)) == 1     # beyond the experts
+    assert lx.lx_b200_moe_sum_rows(abi.ptr(eng.rows), None, T, L, top_k, None) == 1
