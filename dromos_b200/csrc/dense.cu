@@ -110,7 +110,7 @@ int launch_gemv_inst(const GemvParams& P, size_t smem, cudaStream_t stream) {
   if (int e = allow_dynamic_smem<4096 + F * 64 + NT * 8 + CPS>(kernel)) return e;
   const int sms = sm_count();
   if (!sms) return kInvalid;
-  const unsigned grid = static_cast<unsigned>(std::max(1, std::min(P.N, sms * CPS)));
+  const unsigned grid = static_cast<unsigned>(std::max(1, std::min((P.N + kGemvGranule - 1) / kGemvGranule, sms * CPS)));
   return launch_kernel(kernel, dim3(grid), dim3(kGemvThreads), smem, stream, P);
 }
 

@@ -667,7 +667,14 @@ constexpr int kChunks = kKS4 / 16;   // tcgen05.mma instructions per stage (K = 
 constexpr int kASlots = 3;           // A-operand slots in TMEM, one stage each (kKS4 / 2 columns)
 constexpr int kAColumns = kKS4 / 2;
 constexpr int kDColumn = kASlots * kAColumns;  // the accumulator's first TMEM column (128 columns remain for it)
-constexpr int kConvWarps = 8, kConvThreads = 320;  // warps 0-7 convert, warp 8 produces, warp 9 issues
+// Eight or sixteen converter warps (kConvWarps = 8 or 16) were both measured on the 28672 x 8192 matrix: 76.9 / 82.2 us
+// at M = 16 / 64 with eight, 80.1 / 86.2 us with sixteen, so the converters' instruction stream is not what bounds a stage
+// (ncu: 30 % of issue slots, tensor pipe 6 %). A stage writes 64 KB of f16 into tensor memory for 16 KB of weights, and
+// 2375 cycles per stage is 27 bytes per cycle and SM of tcgen05.st.
+constexpr int kConvWarps = 8, kConvParts = kConvWarps / 4;  // a part: the share of a stage's K one converter thread expands for its row
+constexpr int kConvPieces = 8 / kConvParts;                  // 16-byte pieces (32 values, two block scales) per thread and stage
+constexpr int kProducerWarp = kConvWarps, kIssuerWarp = kConvWarps + 1;
+constexpr int kConvThreads = (kConvWarps + 2) * 32;  // converter warps, then the producer warp, then the MMA issuer
 
 __global__ void __launch_bounds__(kConvThreads, 1)
     tc_nvfp4_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap, const TcParams P) {
@@ -713,7 +720,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
     mbar_init(d_full, 1);
     mbar_init_fence();
   }
-  if (warp == 9) {
+  if (warp == kIssuerWarp) {
     tmem_alloc(smem_u32(tmem_slot), kTmemColumns);
     tmem_relinquish();
     tc_fence_before();
@@ -722,7 +729,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
+  if (warp == kProducerWarp) {
     // ================================ producers ================================
     pdl_trigger();
     if (lane == 0) {
@@ -760,7 +767,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
         if (++s == n_stages) s = 0;
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kIssuerWarp) {
     // ================================ MMA issuer ================================
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(NC >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);  // f16 x f16 -> f32
@@ -791,7 +798,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
     }
   } else {
     // ================================ converters, then epilogue ================================
-    const int quarter = warp & 3, half = warp >> 2;
+    const int quarter = warp & 3, part = warp >> 2;
     const int r = quarter * 32 + lane;  // weight row of the tile = TMEM lane
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     Ring w, a;
@@ -803,18 +810,22 @@ __global__ void __launch_bounds__(kConvThreads, 1)
       // Rows past R read what shared memory holds behind the box (this CTA's own, see tc_launch); their lanes are
       // never read back.
       const uint8_t* stage = smem + static_cast<size_t>(w.slot) * slot_bytes;
-      const uint32_t a_addr = lane_addr + a.slot * kAColumns + half * (kAColumns / 2);
+      const uint32_t a_addr = lane_addr + a.slot * kAColumns + part * (kAColumns / kConvParts);
       const int sw = r & 7;
-      // this half's 128 values = 64 bytes = pieces 4 half .. 4 half + 3 of the row's 128 bytes; 8 block scales
+      // this part's pieces kConvPieces * part .. of the row's eight 16-byte pieces (32 values each), two block scales per piece
       const uint8_t* box = stage + r * 128;
-      uint4 q[4];
+      uint4 q[kConvPieces];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) q[j] = *reinterpret_cast<const uint4*>(box + (((4 * half + j) ^ sw) << 4));
-      const uint2 sc = *reinterpret_cast<const uint2*>(stage + box_bytes + r * 16 + half * 8);
+      for (int j = 0; j < kConvPieces; ++j) q[j] = *reinterpret_cast<const uint4*>(box + (((kConvPieces * part + j) ^ sw) << 4));
+      uint32_t sc[(kConvPieces + 1) / 2];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < (kConvPieces + 1) / 2; ++j)
+        sc[j] = *reinterpret_cast<const uint32_t*>(stage + box_bytes + r * 16 + part * (2 * kConvPieces) + 4 * j);
+      static_assert(kConvPieces % 2 == 0, "a thread's scale bytes are read as whole words");
+#pragma unroll
+      for (int j = 0; j < kConvPieces; ++j) {
         uint32_t p[8];
-        const uint32_t sword = j < 2 ? sc.x : sc.y;
+        const uint32_t sword = sc[j / 2];
         expand_nvfp4(q[j].x, q[j].y, sword >> (16 * (j & 1)), p);
         tmem_st8(a_addr + (2 * j) * 8, p);
         expand_nvfp4(q[j].z, q[j].w, sword >> (16 * (j & 1) + 8), p);
@@ -838,12 +849,12 @@ __global__ void __launch_bounds__(kConvThreads, 1)
       tc_fence_after();
       pdl_wait();  // y and the activation scales come from earlier kernels
       const float inv_lo = lane < P.M ? P.inv_scales[lane] : 0.0f, inv_hi = 32 + lane < P.M ? P.inv_scales[32 + lane] : 0.0f;
-      finish_tile<F, false>(P, T, lane_addr + kDColumn, lane, half, 2, inv_lo, inv_hi, 0u);
+      finish_tile<F, false>(P, T, lane_addr + kDColumn, lane, part, kConvParts, inv_lo, inv_hi, 0u);
       ++t;
     }
   }
   __syncthreads();
-  if (warp == 9) tmem_dealloc(tmem_base, kTmemColumns);
+  if (warp == kIssuerWarp) tmem_dealloc(tmem_base, kTmemColumns);
 }
 
 // ---- launching -------------------------------------------------------------------------------------------------------

@@ -6,18 +6,21 @@
 // in flight reach 6 TB/s and more, provided L1 is not carved out as shared memory (the in-flight lines live there) and
 // the loop stays within ~100 warp instructions per KB of weights (at 6.5 TB/s an SM has 176 issue slots per KB). So:
 //
-//   * A CTA is 16 warps; warp w owns the w-th sixteenth of K for every row the CTA handles. CTA b owns the rows
-//     [N b / G, N (b + 1) / G), taken in units of 16 rows (the rows of one mma.sync; the last unit may be short). Per
+//   * A CTA is 16 warps; warp w owns the w-th sixteenth of K for every row the CTA handles. CTA b owns a contiguous
+//     range of rows cut at multiples of 16, taken in units of 16 rows (the rows of one mma.sync; the matrix's last unit
+//     may be short). (N = 14336 on 296 CTAs gives 3 units to most CTAs and 4 to eight of them. Cutting the ranges at
+//     multiples of 4 rows instead evens that out and was measured: no faster on any configuration, because a CTA that
+//     is still streaming when its neighbours are done gets their share of the memory system.) Per
 //     64-byte step of a row pair a lane loads 16 bytes of row g and 16 bytes of row g + 8 (lane = 4 g + t, bytes
 //     16 t .. 16 t + 15 of the step) and uses them as the k-slots the instruction gives that lane: a dot product does not
 //     care about the order of k as long as the activations follow it, and with this assignment they follow it in their
 //     natural order (lane (g, t) reads contiguous bytes of column g's activations), so neither side is ever shuffled.
 //   * Math per format:
 //       BF16, BF16X  bf16 x bf16 (m16n8k16); BF16X steps are decoded in registers to the very bf16 bits the record encodes.
-//       INT8         s8 x s8 -> s32 (m16n8k32) on the stored bytes against three int8 digit columns per activation row
-//                    (base 128 below a per-row power of two); the integer sums are exact. (Expanding int8 to f16 pairs in
-//                    registers for one f16 column per row was measured slower at M = 1: 17.9 against 15.2 us on the
-//                    14336 x 4096 matrix.)
+//       INT8         int8 -> f16 pairs in registers (exact: xor the sign bit, splice the byte into 1024 + v, subtract),
+//                    f16 x f16 like FP8. (s8 x s8 -> s32 on the stored bytes against three int8 digit columns per row
+//                    is exact too and needs no expansion, but was measured slower with 32-byte loads: 17.0 against
+//                    16.3 us on the 14336 x 4096 matrix. Wide INT8 weights run on the tcgen05 product instead.)
 //       FP8          e4m3 -> f16 pairs in registers (one conversion per two values, exact), f16 x f16 against the
 //                    activations as f16 after a per-row power-of-two scaling. (mma.sync with e4m3 operands is not native
 //                    on this part: the assembler expands it into ~10 times the instructions.)
@@ -33,16 +36,13 @@
 
 #include "tc.cuh"
 
-#ifndef GEMV_STAGE1
-#define GEMV_STAGE1 0
-#endif
-
 namespace b200 {
 namespace {
 
 constexpr int kGemvWarps = 16;  // = slices of K; fixed, because it fixes the order a row's products are added in
 constexpr int kGemvThreads = 32 * kGemvWarps;
 constexpr int kGemvUnitRows = 16;
+constexpr int kGemvGranule = 16;  // a CTA's range of rows starts and ends at a multiple of this (any multiple of 4 works)
 // words between two warps' sums of a unit in shared memory (NT 8-column tiles)
 constexpr int kGemvRedStride(int nt) { return kGemvUnitRows * 8 * nt + 2; }
 
@@ -79,16 +79,9 @@ template <>
 struct GemvFmt<LX_W_BF16X> {  // the same steps, slices and k-slots as BF16, so that the sums come out bit for bit the same
   static constexpr int kMma = kMmaBf16, kLane = 32, kStepValues = 64, kXStep = 128, kSwz = 0;
 };
-#ifndef GEMV_INT8_F16
-#define GEMV_INT8_F16 1
-#endif
 template <>
-struct GemvFmt<LX_W_INT8> {
-#if GEMV_INT8_F16
+struct GemvFmt<LX_W_INT8> {  // expanded to f16 pairs like FP8 (kMmaS8 with kXStep 128 and no swizzle is the other, slower, choice)
   static constexpr int kMma = kMmaF16, kLane = 32, kStepValues = 128, kXStep = 256, kSwz = 1;
-#else
-  static constexpr int kMma = kMmaS8, kLane = 32, kStepValues = 128, kXStep = 128, kSwz = 0;
-#endif
 };
 template <>
 struct GemvFmt<LX_W_FP8> {
@@ -145,13 +138,12 @@ __device__ __forceinline__ void lds16(uint4& v, uint32_t addr, uint32_t on) {
 }
 
 // ---- staging the activations as mma B operands: column c = m * planes + digit, K contiguous ------------------------------
-// The scaled maths need each row's largest magnitude before the first digit can be made. A second trip to global memory
-// for the values themselves would queue behind the weight loads already in flight (about 2 us on a loaded GPU), so bf16
-// activations that fit are kept in registers between the two steps: up to kHold 16-byte pieces of a plane per thread.
+// The scaled maths need each row's largest magnitude before the first digit can be made: one pass over the rows for the
+// maxima, a second (from L2) for the values. (Keeping the first pass's values in registers for the second was tried:
+// the registers it holds across the barrier cost the main loop more than the second pass costs.)
 template <int ACT, bool XBF, bool SWZ>
 __device__ __forceinline__ void gemv_stage_x(const GemvParams& P, uint8_t* xs, float* inv_scale, float* part, int tid) {
   constexpr int V = 16 / act_elem(ACT);  // activations per 16 bytes of a plane
-  constexpr int kHold = V == 16 ? 2 : 4;
   const int warp = tid >> 5, lane = tid & 31;
   const bool aligned16 = (reinterpret_cast<uintptr_t>(P.x) & 15) == 0 && P.ld_x % (XBF ? 8 : 4) == 0;
   const int pieces = P.K / V;
@@ -176,60 +168,6 @@ __device__ __forceinline__ void gemv_stage_x(const GemvParams& P, uint8_t* xs, f
       inv_scale[tid] = 1.0f / sc;
     }
   };
-  if (GEMV_STAGE1 && XBF && aligned16 && items <= kHold * kGemvThreads) {
-    uint4 raw[kHold][V / 8];
-    int pm[kHold], pp[kHold];
-    if (ACT != kActBf16 && tid < 8) row_max[tid] = 0u;
-#pragma unroll
-    for (int h = 0; h < kHold; ++h) {
-      const int i = tid + h * kGemvThreads;
-      int m = 0, p = i;
-      while (p >= pieces) p -= pieces, ++m;
-      pm[h] = i < items ? m : -1, pp[h] = p;
-      if (i < items) {
-        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(P.x) + static_cast<int64_t>(m) * P.ld_x + p * V);
-#pragma unroll
-        for (int q = 0; q < V / 8; ++q) raw[h][q] = src[q];
-      }
-    }
-    if constexpr (ACT != kActBf16) {
-      __syncthreads();  // row_max is zero
-#pragma unroll
-      for (int h = 0; h < kHold; ++h) {
-        if (pm[h] < 0) continue;
-        uint32_t mx = 0;  // bf16 magnitudes compare as integers
-#pragma unroll
-        for (int q = 0; q < V / 8; ++q) {
-          const uint32_t w4[4] = {raw[h][q].x, raw[h][q].y, raw[h][q].z, raw[h][q].w};
-#pragma unroll
-          for (int z = 0; z < 4; ++z) mx = max(mx, max((w4[z] & 0x7fffu) << 16, w4[z] & 0x7fff0000u));
-        }
-        atomicMax(&row_max[pm[h]], mx);
-      }
-      __syncthreads();
-      set_scales();
-      __syncthreads();
-    } else {
-      if (tid < 8) inv_scale[tid] = 1.0f;
-    }
-#pragma unroll
-    for (int h = 0; h < kHold; ++h) {
-      if (pm[h] < 0) continue;
-      float v[V];
-#pragma unroll
-      for (int q = 0; q < V / 8; ++q) {
-        const uint32_t w4[4] = {raw[h][q].x, raw[h][q].y, raw[h][q].z, raw[h][q].w};
-#pragma unroll
-        for (int z = 0; z < 4; ++z) {
-          v[8 * q + 2 * z] = __uint_as_float(w4[z] << 16);
-          v[8 * q + 2 * z + 1] = __uint_as_float(w4[z] & 0xffff0000u);
-        }
-      }
-      store_planes(pm[h], pp[h], v);
-    }
-    __syncthreads();
-    return;
-  }
   if constexpr (ACT != kActBf16) {
     for (int m = 0; m < P.M; ++m) {
       const float a = warp_max(row_max_share<XBF>(P.x, static_cast<int64_t>(m) * P.ld_x, P.K, aligned16, tid, kGemvThreads));
@@ -360,13 +298,13 @@ __global__ void __launch_bounds__(kGemvThreads, CPS) gemv_kernel(const GemvParam
   pdl_trigger();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  // The CTA's units: whole groups of 16 rows (the matrix's last group may be short), dealt out evenly. A CTA with one
-  // group more than its neighbours ends later, but the successor's CTAs take the neighbours' places meanwhile.
-  const int n_groups = (P.N + kGemvUnitRows - 1) / kGemvUnitRows;
-  const int group0 = static_cast<int>(static_cast<int64_t>(n_groups) * blockIdx.x / gridDim.x);
-  const int n_units = static_cast<int>(static_cast<int64_t>(n_groups) * (blockIdx.x + 1) / gridDim.x) - group0;
-  const int cta_row0 = group0 * kGemvUnitRows;
-  const int my_rows = min(P.N - cta_row0, n_units * kGemvUnitRows);
+  // The CTA's rows: granules of kGemvGranule rows dealt out evenly, taken in units of up to 16 rows (only the last unit
+  // of a CTA can be short). Where a row lands in a unit changes nothing about its sum.
+  const int granules = (P.N + kGemvGranule - 1) / kGemvGranule;
+  const int cta_row0 = static_cast<int>(static_cast<int64_t>(granules) * blockIdx.x / gridDim.x) * kGemvGranule;
+  const int cta_row1 = min(P.N, static_cast<int>(static_cast<int64_t>(granules) * (blockIdx.x + 1) / gridDim.x) * kGemvGranule);
+  const int my_rows = max(0, cta_row1 - cta_row0);
+  const int n_units = (my_rows + kGemvUnitRows - 1) / kGemvUnitRows;
   const int s0 = P.steps * warp / kGemvWarps, s1 = P.steps * (warp + 1) / kGemvWarps;
   const int n_b = ((P.steps + kGemvWarps - 1) / kGemvWarps + D - 1) / D;  // batches per unit: the longest slice's
   const int hb = kX16 ? x16::header_bytes(P.K) : 0;
