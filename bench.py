@@ -69,8 +69,11 @@ ROTATE_BYTES = 1 << 30  # weights touched between two uses of the same copy (L2 
 METRIC = "decode matmul effective HBM TB/s"
 
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of a workload's dominant kernel, from ncu captures of this
-# library on a B200 (None: no capture of the current kernel).
-NCU_TRAFFIC = {"c1_bf16": None, "c2_int8": 58.864e6 + 0.071e6, "c3_fp8": None, "c3_nvfp4": None, "c4_bf16x": None, "c5_moe_fp8": None}
+# library on a B200 (the summaries under profiles/; bytes; mean of the captured launches). c3_fp8: tc_direct_kernel,
+# the M = 16 and M = 64 launches; c3_nvfp4: tc_nvfp4_kernel at M = 16; c5_moe_fp8: the gate/up plus the down launch of
+# one step. The few MB written are mostly lines the setup left dirty in L2: the kernels write 0.1-7 MB of outputs.
+NCU_TRAFFIC = {"c1_bf16": 33.59e6, "c2_int8": 58.854e6 + 0.105e6, "c3_fp8": (235.69e6 + 5.20e6 + 237.49e6 + 6.77e6) / 2, "c3_nvfp4": 132.49e6 + 3.97e6,
+               "c4_bf16x": 88.82e6 + 4.25e6, "c5_moe_fp8": 400.74e6 + 7.10e6 + 840.85e6 + 4.11e6}
 
 
 def measured_peak_gbs():
