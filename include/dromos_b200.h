@@ -8,6 +8,11 @@
  * whole integration: functions this library does not export answer LX_ERR_NOT_SUPPORTED from the
  * dispatcher's own stub (tools/gen_dispatch.py:168-184).
  *
+ * Where the behaviour is narrower than the reference's: lx_gemm_w and lx_moe_experts_grouped compute LX_MATH_BF16 on
+ * every format, LX_MATH_INT8 on INT8 weights and LX_MATH_FP8 on FP8 weights; LX_MATH_FP4 and LX_MATH_FP8 on NVFP4 weights
+ * (products of the 12x parts in the reference) answer LX_ERR_NOT_SUPPORTED, as does any pair under an architecture
+ * override below the pair's first architecture. Tile-variant families exist for lx_gemm_w only, with one variant each.
+ *
  * Conventions (kernels.h:1-4, 29-38): pointers are device pointers to row-major buffers, ld_* is a row
  * stride in elements, `stream` is a cudaStream_t passed as void* (null = default stream), weights are
  * [out, in] and y = x @ W^T. Functions return a cudaError_t value: 0 success, 1 invalid argument, 801 an
