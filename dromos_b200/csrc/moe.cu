@@ -25,8 +25,8 @@ constexpr int kMaxTopK = 32;
 // ---- routing (one warp per token) ------------------------------------------------------------------------------
 // One warp routes one row of logits (global or shared memory): softmax statistics of the whole row, top_k picks by
 // logit + bias (descending, ties to the lower index), weights = softmax over the picks of their unbiased logits.
-// picks: top_k ints of shared memory private to the warp.
-__device__ __forceinline__ void route_row(const float* row, const float* __restrict__ bias, int E, int top_k, int lane, int* picks,
+// Callers hand a row in shared memory where they can: it is read 3 + top_k times.
+__device__ __forceinline__ void route_row(const float* row, const float* __restrict__ bias, int E, int top_k, int lane,
                                           int32_t* __restrict__ ids, float* __restrict__ weights, float* entropy, float* confidence) {
   float m = -INFINITY;
   for (int i = lane; i < E; i += 32) m = fmaxf(m, row[i]);
@@ -44,16 +44,24 @@ __device__ __forceinline__ void route_row(const float* row, const float* __restr
     if (entropy) *entropy = h;
     if (confidence) *confidence = 1.0f / z;
   }
-  // top_k rounds of a warp arg-max over what is left
+  // top_k rounds of a warp arg-max over what is left. Lane l owns elements l, l + 32, ...: bit j of `taken` says that
+  // element l + 32 j has been picked (the first 1024 experts; rarer ones beyond are looked up among the picks).
   int mine = -1;  // lane j keeps pick j
   float mine_logit = -INFINITY;
+  uint32_t taken = 0;
   for (int r = 0; r < top_k; ++r) {
     float best = -INFINITY;
     int best_i = E;
-    for (int i = lane; i < E; i += 32) {
-      bool taken = false;
-      for (int j = 0; j < r; ++j) taken |= picks[j] == i;
-      if (taken) continue;
+    for (int base = 0, j = 0; base < E; base += 32, ++j) {  // the same trip count in every lane: the shuffle below needs them all
+      const int i = base + lane;
+      bool gone;
+      if (j < 32) {
+        gone = (taken >> j) & 1u;
+      } else {  // beyond 1024 experts: compare with the picks so far, which lanes 0 .. r - 1 hold
+        gone = false;
+        for (int q = 0; q < r; ++q) gone |= __shfl_sync(0xffffffffu, mine, q) == i;
+      }
+      if (gone || i >= E) continue;
       const float v = row[i] + (bias ? bias[i] : 0.0f);
       if (v > best || (v == best && i < best_i)) best = v, best_i = i;
     }
@@ -64,8 +72,7 @@ __device__ __forceinline__ void route_row(const float* row, const float* __restr
       if (ov > best || (ov == best && oi < best_i)) best = ov, best_i = oi;
     }
     if (lane == r) mine = best_i, mine_logit = best_i < E ? row[best_i] : -INFINITY;
-    if (lane == 0) picks[r] = best_i;
-    __syncwarp();
+    if (best_i < 1024 && best_i < E && (best_i & 31) == lane) taken |= 1u << (best_i >> 5);
   }
   const bool live = lane < top_k && mine >= 0 && mine < E;
   const float lmax = warp_max(live ? mine_logit : -INFINITY);
@@ -77,17 +84,25 @@ __device__ __forceinline__ void route_row(const float* row, const float* __restr
   }
 }
 
+constexpr int kRouteStaged = 1024;
 __global__ void __launch_bounds__(256) route_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                                                     int32_t* __restrict__ ids, float* __restrict__ weights,
                                                     float* __restrict__ entropy, float* __restrict__ confidence, int T,
                                                     int E, int top_k) {
   pdl_trigger();
   pdl_wait();
-  const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 8 + warp;
   if (t >= T) return;
-  __shared__ int picks[8][32];
-  route_row(logits + static_cast<int64_t>(t) * E, bias, E, top_k, threadIdx.x & 31, picks[threadIdx.x >> 5],
-            ids + static_cast<int64_t>(t) * top_k, weights + static_cast<int64_t>(t) * top_k, entropy ? entropy + t : nullptr,
+  // the warp's row, staged once (rows of more than kRouteStaged values are read where they are)
+  __shared__ float staged[8][kRouteStaged];
+  const float* row = logits + static_cast<int64_t>(t) * E;
+  if (E <= kRouteStaged) {
+    for (int i = lane; i < E; i += 32) staged[warp][i] = row[i];
+    __syncwarp();
+    row = staged[warp];
+  }
+  route_row(row, bias, E, top_k, lane, ids + static_cast<int64_t>(t) * top_k, weights + static_cast<int64_t>(t) * top_k, entropy ? entropy + t : nullptr,
             confidence ? confidence + t : nullptr);
 }
 
@@ -144,7 +159,6 @@ __global__ void __launch_bounds__(256) router_kernel(const float* __restrict__ x
   // publish this block's logits, then count it; the block that counts last routes every row
   __shared__ int last;
   __shared__ float rows[kRouterRows][kRouterMaxE];
-  __shared__ int picks[kRouterRows][32];
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) last = atomicAdd(ticket, 1) == static_cast<int>(gridDim.x) - 1;
@@ -155,7 +169,7 @@ __global__ void __launch_bounds__(256) router_kernel(const float* __restrict__ x
   for (int i = threadIdx.x; i < M * E; i += 256) rows[i / E][i % E] = __ldcg(logits + i);
   __syncthreads();
   if (warp < M)
-    route_row(rows[warp], selection_bias, E, top_k, lane, picks[warp], ids + static_cast<int64_t>(warp) * top_k,
+    route_row(rows[warp], selection_bias, E, top_k, lane, ids + static_cast<int64_t>(warp) * top_k,
               weights + static_cast<int64_t>(warp) * top_k, entropy ? entropy + warp : nullptr, confidence ? confidence + warp : nullptr);
 }
 
@@ -266,6 +280,99 @@ __global__ void __launch_bounds__(1024) group_kernel(const int32_t* __restrict__
       for (int m = 0; m < n; ++m) chunks.pos_chunk[first + m] = c, chunks.pos_col[first + m] = m;
     }
   }
+}
+
+// The same tables for up to 1024 pairs (every decode-sized call), a thread per pair instead of a thread per expert
+// walking all ids: a pair's place among its expert's pairs is how many earlier pairs chose the same expert (a scan of
+// the staged ids, broadcast reads), the experts' counts are scanned by the whole block, and every thread writes its
+// own table entries. (The thread-per-expert kernel above took 22 us of a 233 us step at 256 pairs.)
+__device__ __forceinline__ int block_exclusive_scan_1024(int x, int* warp_totals, int* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int v = x;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int n = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += n;
+  }
+  if (lane == 31) warp_totals[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    int w = warp_totals[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, w, o);
+      if (lane >= o) w += n;
+    }
+    warp_totals[lane] = w;  // inclusive
+  }
+  __syncthreads();
+  const int before = warp ? warp_totals[warp - 1] : 0;
+  if (total) *total = warp_totals[31];
+  __syncthreads();  // warp_totals may be reused by the caller
+  return before + v - x;
+}
+
+__global__ void __launch_bounds__(1024) group_pairs_kernel(const int32_t* __restrict__ ids, int P, int E,
+                                                           int32_t* __restrict__ offsets, int32_t* __restrict__ pairs,
+                                                           const ExpertChunkTables chunks, int own0, int own1) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ __align__(16) int32_t sid[1024];
+  __shared__ int32_t count[kMaxExperts], start[kMaxExperts], chunk0[kMaxExperts];
+  __shared__ int warp_totals[32];
+  const int p = threadIdx.x;
+  const int mine = p < P ? ids[p] : -1;
+  sid[p] = mine;
+  count[p] = 0;  // kMaxExperts == the block size
+  __syncthreads();
+  int rank = 0;
+  const bool valid = p < P && mine >= 0 && mine < E;  // a pair with an id outside the experts is left out of the tables
+  if (valid) {
+    const int4* v = reinterpret_cast<const int4*>(sid);
+    const int whole = p >> 2;
+    for (int q = 0; q < whole; ++q) {
+      const int4 w = v[q];
+      rank += (w.x == mine) + (w.y == mine) + (w.z == mine) + (w.w == mine);
+    }
+    for (int q = whole * 4; q < p; ++q) rank += sid[q] == mine;
+    atomicAdd(&count[mine], 1);
+  }
+  __syncthreads();
+  const int e = threadIdx.x;
+  const int rows = e < E ? count[e] : 0;
+  int total = 0;
+  const int first = block_exclusive_scan_1024(rows, warp_totals, &total);
+  start[e] = first;
+  if (e < E) offsets[e] = first;
+  if (e == 0) offsets[E] = total;
+  const bool own = e >= own0 && e < own1;
+  int n_chunks = 0;
+  if (chunks.n_chunks) {
+    const int c0 = block_exclusive_scan_1024(own && e < E ? (rows + kExpertChunkRows - 1) / kExpertChunkRows : 0, warp_totals, &n_chunks);
+    chunk0[e] = c0;
+    if (e == 0) *chunks.n_chunks = n_chunks;
+  }
+  __syncthreads();
+  if (!valid) return;
+  const int u = start[mine] + rank;  // the pair's sorted position: stable, ascending pair index inside an expert
+  pairs[u] = p;
+  if (chunks.n_chunks) {
+    if (mine >= own0 && mine < own1) {
+      const int c = chunk0[mine] + rank / kExpertChunkRows, col = rank % kExpertChunkRows;
+      chunks.pos_chunk[u] = c, chunks.pos_col[u] = col;
+      if (col == 0)
+        chunks.chunk_expert[c] = mine - own0, chunks.chunk_row0[c] = u, chunks.chunk_rows[c] = min(kExpertChunkRows, count[mine] - rank);
+    } else {
+      chunks.pos_chunk[u] = -1;
+    }
+  }
+}
+
+// Picks the kernel by the number of pairs.
+int launch_group(const int32_t* ids, int P, int E, int32_t* offsets, int32_t* pairs, const ExpertChunkTables& chunks, int own0, int own1,
+                 cudaStream_t s) {
+  if (P <= 1024) return launch_kernel(group_pairs_kernel, dim3(1), dim3(1024), 0, s, ids, P, E, offsets, pairs, chunks, own0, own1);
+  return launch_kernel(group_kernel, dim3(1), dim3(1024), 0, s, ids, P, E, offsets, pairs, chunks, own0, own1);
 }
 
 // Grouping without knowing E (the decode entry points): the distinct experts of the ids in ascending order.
@@ -566,8 +673,7 @@ extern "C" int lx_moe_experts_grouped(const void* latent, const int32_t* ids, co
   const Layout l = layout(P, E, L, I);
   auto* ws = static_cast<uint8_t*>(workspace);
   const ExpertChunkTables chunks = experts_tc_ok(*gate_up, *down, L, I) ? expert_chunk_tables(ws, l.total, P, E, L, I) : ExpertChunkTables{};
-  if (int e = launch_kernel(group_kernel, dim3(1), dim3(1024), 0, s, ids, P, E, reinterpret_cast<int32_t*>(ws + l.offsets),
-                            reinterpret_cast<int32_t*>(ws + l.pairs), chunks, 0, E))
+  if (int e = launch_group(ids, P, E, reinterpret_cast<int32_t*>(ws + l.offsets), reinterpret_cast<int32_t*>(ws + l.pairs), chunks, 0, E, s))
     return e;
   return run_experts(latent, ids, weights, *gate_up, *down, out, ws, l, false, E, E, T, L, I, top_k, s, nullptr, quantized);
 }
@@ -600,8 +706,7 @@ extern "C" int lx_b200_moe_experts_owned(const void* latent, const int32_t* ids,
   const Layout l = layout(P, E, L, I);
   auto* ws = static_cast<uint8_t*>(workspace);
   const ExpertChunkTables chunks = expert_chunk_tables(ws, l.total, P, E, L, I);
-  if (int e = launch_kernel(group_kernel, dim3(1), dim3(1024), 0, s, ids, P, E, reinterpret_cast<int32_t*>(ws + l.offsets),
-                            reinterpret_cast<int32_t*>(ws + l.pairs), chunks, own0, own1))
+  if (int e = launch_group(ids, P, E, reinterpret_cast<int32_t*>(ws + l.offsets), reinterpret_cast<int32_t*>(ws + l.pairs), chunks, own0, own1, s))
     return e;
   return experts_tc(latent, weights, *gate_up, *down, reinterpret_cast<const int32_t*>(ws + l.offsets),
                     reinterpret_cast<const int32_t*>(ws + l.pairs), reinterpret_cast<uint16_t*>(ws + l.mid), rows, ws, l.total, T, L, I, E,
@@ -808,8 +913,7 @@ extern "C" int lx_b200_moe_experts_grouped_static(const void* latent, const int3
   auto s = static_cast<cudaStream_t>(stream);
   uint8_t* ws = base + kStaticHeaderBytes;
   const ExpertChunkTables chunks = experts_tc_ok(*gate_up, *down, L, I) ? expert_chunk_tables(ws, l.total, P, E, L, I) : ExpertChunkTables{};
-  if (int e = launch_kernel(group_kernel, dim3(1), dim3(1024), 0, s, ids, P, E, reinterpret_cast<int32_t*>(ws + l.offsets),
-                            reinterpret_cast<int32_t*>(ws + l.pairs), chunks, 0, E))
+  if (int e = launch_group(ids, P, E, reinterpret_cast<int32_t*>(ws + l.offsets), reinterpret_cast<int32_t*>(ws + l.pairs), chunks, 0, E, s))
     return e;
   return run_experts(latent, ids, weights, *gate_up, *down, out, ws, l, false, E, E, T, L, I, top_k, s,
                      reinterpret_cast<int*>(base));
