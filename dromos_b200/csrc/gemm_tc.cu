@@ -857,6 +857,237 @@ __global__ void __launch_bounds__(kConvThreads, 1)
   if (warp == kIssuerWarp) tmem_dealloc(tmem_base, kTmemColumns);
 }
 
+// ---- NVFP4 with the expanded weights in shared memory ---------------------------------------------------------------
+// The kernel above is bound by tcgen05.st (27 bytes per cycle and SM measured; a stage writes 64 KB). Here the converter
+// warps write the f16 expansion into shared memory instead (st.shared takes 128 bytes per cycle), in the layout a
+// 128-byte-swizzled tile copy would have left it, and the products read both operands from shared memory like the
+// kernels of the formats that need no conversion. A weight stage (256 values of K per row, as above) is converted in two
+// halves of 128 values; an A slot holds one half: two boxes of 128 rows x 128 bytes. Converter thread (row r, part p)
+// expands kSsPieces 16-byte pieces (32 values, two block scales each) of its row per half.
+//
+// Measured on the 28672 x 8192 matrix at M = 16 / 64: 72.3 / 80.9 us, against 79.1 / 87.3 us for the kernel above in the
+// same run. Variants measured and dropped: quarter-stage slots (86 us: the per-slot handshakes cost more than the finer
+// overlap gives), sixteen converter warps (75 us), block scales fetched for four stages per copy (75 / 91 us: the 32 KB
+// they take leave fewer weight stages). Switching the conversion off (raw bytes stored) gives 67 us and issuing one
+// product in eight gives 66 us: two bounds of nearly the same height. The converters execute ~2080 warp instructions
+// per stage on dependent chains; and the sixteen products of a stage take ~2050 cycles whatever their column count: the
+// tensor core takes its 4 KB A tile (128 rows x 32 bytes) at about 32 bytes per cycle, and the f16 expansion is four
+// times the stored bytes. A faster NVFP4 product needs the weights as the B operand (256 rows per product) or a kind
+// that reads e2m1 as stored.
+constexpr int kSsWarps = 8, kSsParts = kSsWarps / 4, kSsPieces = 4 / kSsParts;
+constexpr int kSsProducer = kSsWarps, kSsIssuer = kSsWarps + 1, kSsThreads = (kSsWarps + 2) * 32;
+constexpr int kSsSlotBytes = 2 * kBM * 128;  // one half stage of f16: 128 rows x 128 values
+
+__global__ void __launch_bounds__(kSsThreads, 1)
+    tc_nvfp4_ss_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap, const TcParams P) {
+  constexpr int F = LX_W_NVFP4;
+  using Fm = TcFmt<F>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const int NC = P.NC, SW = P.SW, SX = P.SX, SA = P.tmem_cols;  // (tmem_cols carries the number of A slots: the kernel takes all of TMEM)
+  const int x_bytes = P.x_bytes, box_bytes = P.box_bytes, slot_bytes = P.dstride;  // (dstride carries the bytes of a weight slot)
+  uint8_t* const aring = smem + static_cast<size_t>(SW) * slot_bytes;
+  uint8_t* const xring = aring + static_cast<size_t>(SA) * kSsSlotBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(xring + static_cast<size_t>(SX) * x_bytes);
+  const uint32_t bar0 = smem_u32(bars);
+  auto w_full = [&](int s) { return bar0 + 8u * s; };
+  auto w_empty = [&](int s) { return bar0 + 8u * (SW + s); };
+  auto x_full = [&](int s) { return bar0 + 8u * (2 * SW + s); };
+  auto x_empty = [&](int s) { return bar0 + 8u * (2 * SW + SX + s); };
+  auto a_full = [&](int a) { return bar0 + 8u * (2 * SW + 2 * SX + a); };
+  auto a_empty = [&](int a) { return bar0 + 8u * (2 * SW + 2 * SX + SA + a); };
+  const uint32_t d_full = bar0 + 8u * (2 * SW + 2 * SX + 2 * SA);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * SW + 2 * SX + 2 * SA + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_stages = (P.K + kKS4 - 1) / kKS4;
+  const int n_tiles = (P.N + P.R - 1) / P.R;
+  const int tile_begin = static_cast<int>(static_cast<int64_t>(n_tiles) * blockIdx.x / gridDim.x);
+  const int tile_end = static_cast<int>(static_cast<int64_t>(n_tiles) * (blockIdx.x + 1) / gridDim.x);
+  const int total = (tile_end - tile_begin) * n_stages;
+
+  if (tid == 0) {
+    for (int s = 0; s < SW; ++s) {
+      mbar_init(w_full(s), 1);
+      mbar_init(w_empty(s), kSsWarps);
+    }
+    for (int s = 0; s < SX; ++s) {
+      mbar_init(x_full(s), 1);
+      mbar_init(x_empty(s), 1);
+    }
+    for (int a = 0; a < SA; ++a) {
+      mbar_init(a_full(a), kSsWarps);
+      mbar_init(a_empty(a), 1);
+    }
+    mbar_init(d_full, 1);
+    mbar_init_fence();
+  }
+  if (warp == kSsIssuer) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemColumns);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == kSsProducer) {
+    // ================================ producers ================================
+    pdl_trigger();
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&smap) : "memory");
+    }
+    if (lane == 0) {  // weights and their scales are static: no wait
+      Ring w;
+      bool ok = true, wrapped = false;
+      for (int tile = tile_begin; tile < tile_end && ok; ++tile) {
+        for (int s = 0; s < n_stages; ++s) {
+          if (wrapped && !tc_wait(w_empty(w.slot), w.lap ^ 1u, P.status)) {
+            ok = false;
+            break;
+          }
+          const uint32_t dst = smem_u32(smem) + static_cast<uint32_t>(w.slot) * slot_bytes;
+          mbar_arrive_expect_tx(w_full(w.slot), P.R * (128 + 16));
+          tile_g2s(dst, &wmap, (s * Fm::kRowBytes) / 4, tile * P.R, w_full(w.slot));
+          tile_g2s(dst + box_bytes, &smap, s * 16, tile * P.R, w_full(w.slot));
+          w.advance(SW);
+          wrapped |= w.slot == 0;
+        }
+      }
+    } else if (lane == 1) {
+      pdl_wait();  // the prepared activations come from the kernel before this one
+      Ring x;
+      bool wrapped = false;
+      int s = 0;
+      for (int i = 0; i < total; ++i) {
+        if (wrapped && !tc_wait(x_empty(x.slot), x.lap ^ 1u, P.status)) break;
+        mbar_arrive_expect_tx(x_full(x.slot), x_bytes);
+        bulk_g2s(smem_u32(xring) + static_cast<uint32_t>(x.slot) * x_bytes, P.xprep + static_cast<size_t>(s) * x_bytes, x_bytes, x_full(x.slot));
+        x.advance(SX);
+        wrapped |= x.slot == 0;
+        if (++s == n_stages) s = 0;
+      }
+    }
+  } else if (warp == kSsIssuer) {
+    // ================================ MMA issuer ================================
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(NC >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);  // f16 x f16 -> f32
+      const uint32_t lbo = static_cast<uint32_t>(NC / 8) * 128, sbo = 128;
+      const uint32_t a_hi = (1024u >> 4) | (1u << 14) | (2u << 29), b_hi = (sbo >> 4) | (1u << 14);
+      const uint32_t a_lo0 = ((smem_u32(aring) & 0x3ffffu) >> 4) | (1u << 16);
+      const uint32_t b_lo0 = ((smem_u32(xring) & 0x3ffffu) >> 4) | ((lbo >> 4) << 16);
+      const uint32_t b_step = (2u * lbo) >> 4;
+      Ring x, a;
+      int s = 0;
+      bool ok = true;
+      for (int i = 0; i < total && ok; ++i) {
+        if (!tc_wait(x_full(x.slot), x.lap, P.status)) break;
+        const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(x.slot) * (static_cast<uint32_t>(x_bytes) >> 4);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (!tc_wait(a_full(a.slot), a.lap, P.status)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(a.slot) * (kSsSlotBytes >> 4);
+#pragma unroll
+          for (int b = 0; b < 2; ++b) {
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+              const int c = 8 * h + 4 * b + ks;  // 16 values of K per instruction
+              umma_ss_halves<kActF16>(tmem_base, a_lo + b * ((kSsSlotBytes / 2) >> 4) + ks * 2, a_hi, b_lo + c * b_step, b_hi, idesc, (s | c) ? 1u : 0u);
+            }
+          }
+          umma_commit(a_empty(a.slot));  // the half stage may be overwritten once these products are done
+          a.advance(SA);
+        }
+        if (!ok) break;
+        umma_commit(x_empty(x.slot));
+        if (++s == n_stages) {
+          s = 0;
+          umma_commit(d_full);  // the tile's accumulator is complete when everything issued so far is
+        }
+        x.advance(SX);
+      }
+    }
+  } else {
+    // ================================ converters, then epilogue ================================
+    const int quarter = warp & 3, part = warp >> 2;
+    const int r = quarter * 32 + lane;  // weight row of the tile = TMEM lane
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const int sw = r & 7;
+    Ring w, a;
+    int s = 0, t = 0;
+    bool a_wrapped = false, ok = true;
+    for (int i = 0; i < total && ok; ++i) {
+      if (!tc_wait(w_full(w.slot), w.lap, P.status)) break;
+      // Rows past R read what shared memory holds behind the box (this CTA's own); their lanes are never read back.
+      const uint8_t* stage = smem + static_cast<size_t>(w.slot) * slot_bytes;
+      const uint8_t* box = stage + r * 128;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint4 q[kSsPieces];
+#pragma unroll
+        for (int j = 0; j < kSsPieces; ++j) q[j] = *reinterpret_cast<const uint4*>(box + (((4 * h + kSsPieces * part + j) ^ sw) << 4));
+        uint32_t sc[kSsPieces];  // two scale bytes per piece
+#pragma unroll
+        for (int j = 0; j < kSsPieces; ++j)
+          sc[j] = *reinterpret_cast<const uint16_t*>(stage + box_bytes + r * 16 + 2 * (4 * h + kSsPieces * part + j));
+        if (a_wrapped && !tc_wait(a_empty(a.slot), a.lap ^ 1u, P.status)) {
+          ok = false;
+          break;
+        }
+        uint8_t* arow = aring + static_cast<size_t>(a.slot) * kSsSlotBytes + r * 128;
+#pragma unroll
+        for (int j = 0; j < kSsPieces; ++j) {
+          const int g = kSsPieces * part + j;  // the piece's place in the half: box g / 2, chunks 4 (g % 2) ..
+          uint8_t* dst = arow + (g >> 1) * (kSsSlotBytes / 2);
+          const int c0 = 4 * (g & 1);
+          uint32_t p[8];
+          expand_nvfp4(q[j].x, q[j].y, sc[j], p);
+          *reinterpret_cast<uint4*>(dst + (((c0 + 0) ^ sw) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
+          *reinterpret_cast<uint4*>(dst + (((c0 + 1) ^ sw) << 4)) = make_uint4(p[4], p[5], p[6], p[7]);
+          expand_nvfp4(q[j].z, q[j].w, sc[j] >> 8, p);
+          *reinterpret_cast<uint4*>(dst + (((c0 + 2) ^ sw) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
+          *reinterpret_cast<uint4*>(dst + (((c0 + 3) ^ sw) << 4)) = make_uint4(p[4], p[5], p[6], p[7]);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads what these threads wrote
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(a_full(a.slot));
+          if (h == 1) mbar_arrive(w_empty(w.slot));  // both halves have been read and used: the stage may be refilled
+        }
+        a.advance(SA);
+        a_wrapped |= a.slot == 0;
+      }
+      if (!ok) break;
+      w.advance(SW);
+      if (++s != n_stages) continue;
+      s = 0;
+      // ---- the tile is over ----
+      const RowTerms T = row_terms<F>(P, tile_begin + t, r);
+      if (!tc_wait(d_full, t & 1, P.status)) break;
+      tc_fence_after();
+      pdl_wait();  // y and the activation scales come from earlier kernels
+      const float inv_lo = lane < P.M ? P.inv_scales[lane] : 0.0f, inv_hi = 32 + lane < P.M ? P.inv_scales[32 + lane] : 0.0f;
+      finish_tile<F, false>(P, T, lane_addr, lane, part, kSsParts, inv_lo, inv_hi, 0u);
+      ++t;
+    }
+  }
+  __syncthreads();
+  if (warp == kSsIssuer) tmem_dealloc(tmem_base, kTmemColumns);
+}
+
+// LX_B200_NVFP4_TMEM=1 keeps the kernel that expands into tensor memory.
+bool nvfp4_through_tmem() {
+  static const bool on = [] {
+    const char* v = std::getenv("LX_B200_NVFP4_TMEM");
+    return v && v[0] == '1';
+  }();
+  return on;
+}
+
 // ---- launching -------------------------------------------------------------------------------------------------------
 // LX_B200_TC_SMALL=1 lets products whose rings fit take small CTAs (two per SM); LX_B200_TC_SMALL_STAGES sets the fewest
 // weight stages a small CTA must keep (default 3). Off by default: measured on C2, a product between small neighbours
@@ -941,6 +1172,22 @@ int tc_launch(const lx_weight& w, TcParams P, cudaStream_t stream, int* grid_out
   if constexpr (F == LX_W_NVFP4) {
     static_assert(XMODE == 0, "NVFP4 takes prepared activations");
     if (int e = make_tile_map(&smap, w.scale, P.K / 16, P.N, 16, P.R, 1, false)) return e;
+    if (!nvfp4_through_tmem()) {
+      // weight slots of the box and 128 rows of scales; two or three half-stage A slots; two activation blocks
+      constexpr int kBudget = 224 * 1024;
+      const int slot = (P.box_bytes + kBM * 16 + 1023) / 1024 * 1024;
+      P.SX = 2;
+      int sa = 3;
+      int sw_fit = (kBudget - kBars - P.SX * P.x_bytes - sa * kSsSlotBytes) / slot;
+      if (sw_fit < 5) sa = 2, sw_fit = (kBudget - kBars - P.SX * P.x_bytes - sa * kSsSlotBytes) / slot;
+      if (sw_fit >= 2) {
+        P.SW = std::min(12, sw_fit);
+        P.tmem_cols = sa, P.dstride = slot;  // (the kernel takes all of TMEM; these two fields carry its ring geometry)
+        const size_t bytes = static_cast<size_t>(P.SW) * slot + static_cast<size_t>(sa) * kSsSlotBytes + P.SX * P.x_bytes + kBars;
+        if (int e = allow_big_smem<F * 4 + 1>(tc_nvfp4_ss_kernel)) return e;
+        return launch_kernel(tc_nvfp4_ss_kernel, dim3(grid), dim3(kSsThreads), bytes, stream, wmap, smap, P);
+      }
+    }
     if (int e = allow_big_smem<F * 4>(tc_nvfp4_kernel)) return e;
     return launch_kernel(tc_nvfp4_kernel, dim3(grid), dim3(kConvThreads), smem, stream, wmap, smap, P);
   } else {
