@@ -1020,6 +1020,19 @@ __global__ void __launch_bounds__(kSsThreads, 1)
     Ring w, a;
     int s = 0, t = 0;
     bool a_wrapped = false, ok = true;
+    // The arrival for a slot is sent one half later, after the next half has been expanded into registers: the proxy
+    // fence waits for the slot's stores to complete, and that wait is what the expansion of the next half hides.
+    int owed_a = -1, owed_w = -1;  // the A slot (and, after a stage's second half, the weight slot) whose arrival is still owed
+    auto settle = [&]() {
+      if (owed_a < 0) return;
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads what these threads wrote
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(a_full(owed_a));
+        if (owed_w >= 0) mbar_arrive(w_empty(owed_w));  // both halves have been read and used: the stage may be refilled
+      }
+      owed_a = owed_w = -1;
+    };
     for (int i = 0; i < total && ok; ++i) {
       if (!tc_wait(w_full(w.slot), w.lap, P.status)) break;
       // Rows past R read what shared memory holds behind the box (this CTA's own); their lanes are never read back.
@@ -1034,6 +1047,16 @@ __global__ void __launch_bounds__(kSsThreads, 1)
 #pragma unroll
         for (int j = 0; j < kSsPieces; ++j)
           sc[j] = *reinterpret_cast<const uint16_t*>(stage + box_bytes + r * 16 + 2 * (4 * h + kSsPieces * part + j));
+        uint32_t p[kSsPieces][16];
+#pragma unroll
+        for (int j = 0; j < kSsPieces; ++j) {
+          uint32_t lo[8], hi[8];
+          expand_nvfp4(q[j].x, q[j].y, sc[j], lo);
+          expand_nvfp4(q[j].z, q[j].w, sc[j] >> 8, hi);
+#pragma unroll
+          for (int z = 0; z < 8; ++z) p[j][z] = lo[z], p[j][8 + z] = hi[z];
+        }
+        settle();
         if (a_wrapped && !tc_wait(a_empty(a.slot), a.lap ^ 1u, P.status)) {
           ok = false;
           break;
@@ -1044,20 +1067,11 @@ __global__ void __launch_bounds__(kSsThreads, 1)
           const int g = kSsPieces * part + j;  // the piece's place in the half: box g / 2, chunks 4 (g % 2) ..
           uint8_t* dst = arow + (g >> 1) * (kSsSlotBytes / 2);
           const int c0 = 4 * (g & 1);
-          uint32_t p[8];
-          expand_nvfp4(q[j].x, q[j].y, sc[j], p);
-          *reinterpret_cast<uint4*>(dst + (((c0 + 0) ^ sw) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
-          *reinterpret_cast<uint4*>(dst + (((c0 + 1) ^ sw) << 4)) = make_uint4(p[4], p[5], p[6], p[7]);
-          expand_nvfp4(q[j].z, q[j].w, sc[j] >> 8, p);
-          *reinterpret_cast<uint4*>(dst + (((c0 + 2) ^ sw) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
-          *reinterpret_cast<uint4*>(dst + (((c0 + 3) ^ sw) << 4)) = make_uint4(p[4], p[5], p[6], p[7]);
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            *reinterpret_cast<uint4*>(dst + (((c0 + c) ^ sw) << 4)) = make_uint4(p[j][4 * c], p[j][4 * c + 1], p[j][4 * c + 2], p[j][4 * c + 3]);
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads what these threads wrote
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(a_full(a.slot));
-          if (h == 1) mbar_arrive(w_empty(w.slot));  // both halves have been read and used: the stage may be refilled
-        }
+        owed_a = a.slot, owed_w = h == 1 ? w.slot : -1;
         a.advance(SA);
         a_wrapped |= a.slot == 0;
       }
@@ -1066,6 +1080,7 @@ __global__ void __launch_bounds__(kSsThreads, 1)
       if (++s != n_stages) continue;
       s = 0;
       // ---- the tile is over ----
+      settle();
       const RowTerms T = row_terms<F>(P, tile_begin + t, r);
       if (!tc_wait(d_full, t & 1, P.status)) break;
       tc_fence_after();
