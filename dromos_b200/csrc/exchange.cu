@@ -31,23 +31,21 @@ template <int V>  // bytes per thread and store: 16, 4 or 2
 __global__ void __launch_bounds__(256) exchange_kernel(const ExchangeParams P) {
   pdl_trigger();
   pdl_wait();  // the slice comes from the product before this kernel
-  const int64_t per_row = P.row_bytes / V, total = per_row * P.M;
+  // One (peer, piece of the slice) pair per thread and turn, pieces fastest: a warp stores 512 contiguous bytes to one peer,
+  // the warps of the grid cover all peers at once, and the grid grows with the number of peers (with a thread storing its piece to every peer in turn, 56 CTAs carried the
+  // 6.4 MB a rank sends at M = 64 on 8 GPUs, and the exchange took 35 us).
+  const int64_t per_row = P.row_bytes / V, pieces = per_row * P.M;
+  const int peers = P.ranks - 1;
+  const int64_t total = pieces * peers;
   const uint8_t* src = P.y[P.self];
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+  for (int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; j < total; j += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    int r = static_cast<int>(j / pieces);
+    const int64_t i = j - r * pieces;
+    r += r >= P.self;  // skip this rank
     const int64_t m = i / per_row, at = m * P.pitch + (i - m * per_row) * V;
-    if constexpr (V == 16) {
-      const uint4 v = *reinterpret_cast<const uint4*>(src + at);
-      for (int r = 0; r < P.ranks; ++r)
-        if (r != P.self) *reinterpret_cast<uint4*>(P.y[r] + at) = v;
-    } else if constexpr (V == 4) {
-      const uint32_t v = *reinterpret_cast<const uint32_t*>(src + at);
-      for (int r = 0; r < P.ranks; ++r)
-        if (r != P.self) *reinterpret_cast<uint32_t*>(P.y[r] + at) = v;
-    } else {
-      const uint16_t v = *reinterpret_cast<const uint16_t*>(src + at);
-      for (int r = 0; r < P.ranks; ++r)
-        if (r != P.self) *reinterpret_cast<uint16_t*>(P.y[r] + at) = v;
-    }
+    if constexpr (V == 16) *reinterpret_cast<uint4*>(P.y[r] + at) = *reinterpret_cast<const uint4*>(src + at);
+    else if constexpr (V == 4) *reinterpret_cast<uint32_t*>(P.y[r] + at) = *reinterpret_cast<const uint32_t*>(src + at);
+    else *reinterpret_cast<uint16_t*>(P.y[r] + at) = *reinterpret_cast<const uint16_t*>(src + at);
   }
   // The CTA's stores are visible system-wide before it counts itself; the grid's last CTA tells every rank (one remote
   // atomic per rank and launch: atomics on one word serialise) and then waits for the peers.
@@ -59,7 +57,9 @@ __global__ void __launch_bounds__(256) exchange_kernel(const ExchangeParams P) {
   if (before != static_cast<int>(gridDim.x) - 1) return;
   asm volatile("st.relaxed.gpu.global.s32 [%0], %1;" ::"l"(P.done_local), "r"(0) : "memory");
   __threadfence_system();
-  for (int r = 0; r < P.ranks; ++r) asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(P.arrive[r]) : "memory");
+  // (relaxed: the fence above already orders this rank's stores before them; a release on each would wait for the one
+  // before it, one NVLink round trip per rank: 23 us for a 14 KB slice on 8 GPUs)
+  for (int r = 0; r < P.ranks; ++r) asm volatile("red.relaxed.sys.global.add.s32 [%0], 1;" ::"l"(P.arrive[r]) : "memory");
   const uint64_t t0 = global_timer_ns();
   for (;;) {
     int v;
@@ -183,8 +183,8 @@ extern "C" int lx_b200_exchange_slices(void* const* y_all, int* const* arrivals,
   bool v16 = P.row_bytes % 16 == 0 && P.pitch % 16 == 0;
   for (int r = 0; r < ranks; ++r) v16 = v16 && aligned(P.y[r], 16);
   const int V = v16 ? 16 : static_cast<int>(elem);
-  const int64_t units = P.row_bytes / V * M;
-  const unsigned grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(148, (units + 1023) / 1024)));
+  const int64_t units = P.row_bytes / V * M * std::max(1, ranks - 1);
+  const unsigned grid = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(4 * 148, (units + 511) / 512)));
   auto s = static_cast<cudaStream_t>(stream);
   if (V == 16) return launch_kernel(exchange_kernel<16>, dim3(grid), dim3(256), 0, s, P);
   if (V == 4) return launch_kernel(exchange_kernel<4>, dim3(grid), dim3(256), 0, s, P);

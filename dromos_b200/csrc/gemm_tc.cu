@@ -253,7 +253,7 @@ __device__ __forceinline__ void signal_peers(const TcParams& P, int lane, int* c
     if (before == static_cast<int>(gridDim.x) - 1) {
       asm volatile("st.relaxed.gpu.global.s32 [%0], %1;" ::"l"(P.done_local), "r"(0) : "memory");
       __threadfence_system();
-      for (int g = 0; g < P.peers; ++g) asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(P.flag_peer[g]) : "memory");
+      for (int g = 0; g < P.peers; ++g) asm volatile("red.relaxed.sys.global.add.s32 [%0], 1;" ::"l"(P.flag_peer[g]) : "memory");  // ordered by the fence above
     }
   }
 }
