@@ -339,6 +339,27 @@ class ExpertParallel:
         return out
 
 
+def packet_plan(N: int, world: int, elem_bytes: int, max_rows: int, packet_bytes: int):
+    """The geometry of the packet exchange for an [max_rows, N] output split over `world` ranks: the column bounds of the
+    ranks' slices, the packets a rank's region of a receive buffer holds (rows that may travel as packets x 8-byte pieces of
+    the widest slice), and whether slices are whole 8-byte pieces at all. Pure arithmetic (tested on CPU)."""
+    bounds = [shard_rows(N, r, world)[0] for r in range(world)] + [N]
+    widest = max(bounds[r + 1] - bounds[r] for r in range(world))
+    rows = min(max_rows, max(1, packet_bytes // max(1, widest * elem_bytes * max(1, world - 1))))
+    region = rows * ((widest * elem_bytes + 7) // 8)
+    ok = all((b * elem_bytes) % 8 == 0 for b in bounds) and (N * elem_bytes) % 8 == 0
+    return bounds, region, ok
+
+
+def travels_as_packets(M: int, bounds, region: int, ok: bool, elem_bytes: int, packet_bytes: int) -> bool:
+    """The default choice between the two exchanges for M rows: packets when the slices fit the regions and what a rank sends
+    (its slice to every peer) is at most packet_bytes."""
+    world = len(bounds) - 1
+    widest = max(bounds[r + 1] - bounds[r] for r in range(world))
+    fits = ok and M * ((widest * elem_bytes + 7) // 8) <= region
+    return fits and M * widest * elem_bytes * max(1, world - 1) <= packet_bytes
+
+
 class PeerBuffers:
     """What the ranks of a row-sharded layer share: two whole-y buffers used in turn (so that a rank one call ahead never
     overwrites the y a slower rank still reads) and the arrival counters, all torch symmetric memory (plain peer mappings,
@@ -371,12 +392,7 @@ class PeerBuffers:
         # against 16.6; 1.8 MB 10.3 against 17.8; 3.7 MB 18.7 against 19.8. Packets put twice the bytes on the wire, once
         # per peer, so the limit is on what a rank sends.
         self.packet_bytes = int(os.environ.get("LX_B200_PACKET_BYTES", str(3 << 20)))
-        esz = self.y.element_size()
-        self.bounds = [shard_rows(N, r, self.world)[0] for r in range(self.world)] + [N]
-        widest = max(self.bounds[r + 1] - self.bounds[r] for r in range(self.world))
-        rows = min(max_rows, max(1, self.packet_bytes // max(1, widest * esz * max(1, self.world - 1))))
-        self.region = rows * ((widest * esz + 7) // 8)
-        self.packets_ok = all((b * esz) % 8 == 0 for b in self.bounds) and (N * esz) % 8 == 0
+        self.bounds, self.region, self.packets_ok = packet_plan(N, self.world, self.y.element_size(), max_rows, self.packet_bytes)
         self.boxes = symm.empty((2, self.world, self.region, 4), dtype=torch.int32, device=device)
         self.boxes.zero_()
         hb = symm.rendezvous(self.boxes, self.group)
@@ -402,12 +418,12 @@ class PeerBuffers:
         exchanges; by default slices of at most packet_bytes travel as packets."""
         y_dt = abi.BF16 if self.dtype == torch.bfloat16 else abi.F32
         n0, n1 = self.bounds[self.rank], self.bounds[self.rank + 1]
+        esz = self.y.element_size()
         widest = max(self.bounds[r + 1] - self.bounds[r] for r in range(self.world))
-        fits = self.packets_ok and M * ((widest * self.y.element_size() + 7) // 8) <= self.region
         if packets is None:
-            packets = fits and M * widest * self.y.element_size() * max(1, self.world - 1) <= self.packet_bytes
+            packets = travels_as_packets(M, self.bounds, self.region, self.packets_ok, esz, self.packet_bytes)
         if packets:
-            if not fits:
+            if not (self.packets_ok and M * ((widest * esz + 7) // 8) <= self.region):
                 raise RuntimeError("the slices do not fit the packet buffers")
             st = lib.lx_b200_exchange_packets(abi.ptr(self.y[half]), self.box_array, self.region, abi.ptr(self.seq), abi.ptr(self.seq[32:]),
                                               self.world, self.rank, self.bounds_array, y_dt, self.N, M, _stream())

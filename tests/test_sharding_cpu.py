@@ -32,6 +32,23 @@ def test_remap_for_owner():
     assert lid.tolist() == [[0, 1], [0, 2]] and lw.tolist() == [[0.0, 0.75], [0.0, 0.5]] and mine.tolist() == [[False, True], [False, True]]
 
 
+def test_packet_plan_geometry():
+    """Which exchanges travel as packets: by what a rank sends, not by the slice alone; odd splits fall back."""
+    # C3 on 2 GPUs, f32 y, up to 64 rows, 3 MB limit: M = 1 and 16 as packets, M = 64 (3.7 MB sent) not
+    bounds, region, ok = host.packet_plan(28672, 2, 4, 64, 3 << 20)
+    assert bounds == [0, 14336, 28672] and ok and region == (3 << 20) // (14336 * 4) * (14336 * 4 // 8)
+    assert [host.travels_as_packets(M, bounds, region, ok, 4, 3 << 20) for M in (1, 16, 64)] == [True, True, False]
+    # 8 GPUs: a rank sends its slice seven times
+    bounds, region, ok = host.packet_plan(28672, 8, 4, 64, 3 << 20)
+    assert bounds[1] == 3584 and [host.travels_as_packets(M, bounds, region, ok, 4, 3 << 20) for M in (1, 16, 64)] == [True, True, False]
+    # slices that are not whole 8-byte pieces (bf16, a bound at an odd column) never travel as packets
+    bounds, region, ok = host.packet_plan(30, 4, 2, 8, 3 << 20)
+    assert not ok and not host.travels_as_packets(1, bounds, region, ok, 2, 3 << 20)
+    # one rank: nothing to send, packets trivially fit
+    bounds, region, ok = host.packet_plan(64, 1, 4, 8, 1 << 20)
+    assert bounds == [0, 64] and ok
+
+
 class OracleExperts:
     """Stands in for host.Experts on CPU: same call signature, computed by the oracle."""
 
@@ -74,6 +91,31 @@ def _worker(rank, world, port, ret):
         lat_t = torch.from_numpy(latent[t0:t1].view(np.int16)).view(torch.bfloat16)
         got = ep(lat_t, torch.from_numpy(ids[t0:t1]), torch.from_numpy(weights[t0:t1]))
         err = np.abs(got.numpy() - want[t0:t1]).max() / np.abs(want).max()
+        # experts over ranks with routing and tokens replicated (what host.ReplicatedExpertParallel does on GPUs): every rank
+        # computes the weighted rows of the pairs whose expert it owns, the rows meet (here: a sum of zero-filled buffers,
+        # exact because the owners are disjoint), and every rank adds a token's rows in k order. Bit for bit the single-rank sum.
+        def pair_rows(e_lo, e_hi):
+            rows = np.zeros((T * k, L), dtype=np.float32)
+            for p in range(T * k):
+                e = int(ids.reshape(-1)[p])
+                if e_lo <= e < e_hi:
+                    one = O.moe_experts_reference(latent[p // k : p // k + 1], np.array([[e]], dtype=np.int32), weights.reshape(-1)[p : p + 1].reshape(1, 1),
+                                                  O.Weight(O.W_BF16, gu_bits), O.Weight(O.W_BF16, dn_bits), I)
+                    rows[p] = one[0].astype(np.float32)
+            return rows
+
+        def k_ordered_sum(rows):
+            acc = np.zeros((T, L), dtype=np.float32)
+            for j in range(k):
+                acc = (acc + rows.reshape(T, k, L)[:, j]).astype(np.float32)
+            return acc
+
+        mine_rows = torch.from_numpy(pair_rows(e0, e1))
+        dist.all_reduce(mine_rows)
+        split = k_ordered_sum(mine_rows.numpy())
+        whole = k_ordered_sum(pair_rows(0, E))
+        rep_equal = bool(np.array_equal(split.view(np.uint32), whole.view(np.uint32)))
+        rep_err = float(np.abs(split - want).max() / np.abs(want).max())
         # dense: row shards gathered equal the whole product
         N, K = 24, 64
         w = bits((N, K), 0.05)
@@ -84,7 +126,7 @@ def _worker(rank, world, port, ret):
         gathered = torch.empty((world, 3, n1 - n0))
         dist.all_gather_into_tensor(gathered.view(world * 3, n1 - n0), mine.contiguous())
         dense_err = np.abs(gathered.permute(1, 0, 2).reshape(3, N).numpy() - full).max()
-        ret[rank] = (float(err), float(dense_err))
+        ret[rank] = (float(err), float(dense_err), rep_equal, rep_err)
     finally:
         dist.destroy_process_group()
 
@@ -97,6 +139,7 @@ def test_expert_parallel_and_row_sharding_two_ranks():
     mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     assert len(ret) == world
     for r in range(world):
-        err, dense_err = ret[r]
+        err, dense_err, rep_equal, rep_err = ret[r]
         assert err <= 1e-6, f"rank {r}: expert-parallel output differs from the unsharded one ({err})"
         assert dense_err <= 1e-5
+        assert rep_equal and rep_err <= 1e-6, f"rank {r}: replicated-routing expert split differs from one rank's sum ({rep_err})"
