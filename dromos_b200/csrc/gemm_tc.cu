@@ -1168,8 +1168,14 @@ int tc_launch(const lx_weight& w, TcParams P, cudaStream_t stream, int* grid_out
     } else if (F != LX_W_NVFP4 && kLarge / (w_stage + P.x_bytes) >= 4) {
       P.SW = P.SX = std::min(12, kLarge / (w_stage + P.x_bytes));  // one ring again: one commit per stage
     } else {
-      P.SX = P.x_bytes > 24 * 1024 ? 2 : 3;
-      P.SW = std::min(12, (kLarge - P.SX * P.x_bytes - kStaging) / w_stage);
+      // Large activation blocks (64 rows of two digits are 32 KB per stage): measured at M = 64 on the 28672 x 8192 FP8
+      // matrix, three, four or five weight stages make no difference (57.9-58.2 us) while a third activation slot gives
+      // 54.8 us and a single one 95.7 us: a block is asked for only when the products that used its slot are done, then
+      // travels from L2 for a microsecond, so the activation ring is what is latency-bound (a fourth slot at the price of
+      // a weight stage: 56.3 us). Up to three activation slots as long as three weight stages stay, the rest to the weights.
+      constexpr int kRoom = 222 * 1024 - kBars;
+      P.SX = std::max(2, std::min(3, (kRoom - 3 * w_stage - kStaging) / P.x_bytes));
+      P.SW = std::min(12, (kRoom - P.SX * P.x_bytes - kStaging) / w_stage);
     }
     if (P.SW < 2) return kNotSupported;
     P.tmem_cols = kTmemColumns, P.dstride = 256;
