@@ -665,7 +665,7 @@ def main():
         exch = "none" if world == 1 else os.environ.get("LX_BENCH_EXCHANGE_NAME", "one kernel over peer memory: lx_b200_exchange_packets (flag-in-data packets) for small slices, lx_b200_exchange_slices (stores + semaphore) for large")
         print(json.dumps({"impl": "reference", "metric": METRIC, "value": head["value"], "unit": "TB/s", "n_gpus": args.gpus, "steps": args.steps,
                           "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True,
-                          "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": DTYPE[DENSE[HEADLINE][0]], "data": "synthetic",
+                          "scaling": "strong", "vs_baseline": None, "dtype": DTYPE[DENSE[HEADLINE][0]], "data": "synthetic",
                           "config": config_of(HEADLINE, world, "strong", exch), "cpu_baseline": head["cpu_baseline"],
                           "e2e": {"value": head["value"], "unit": "TB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                           "per_config": per_config}))
@@ -702,7 +702,7 @@ def main():
         for n in names:
             per_config[n]["cpu_baseline"], _ = cpu_leg(n, 5 if n != HEADLINE else 8, 2)
     line = {"metric": METRIC, "value": head["value"], "unit": "TB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None,
+            "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": head["dtype"], "data": "synthetic", "config": config_of(HEADLINE, world, "strong", head["exchange"]), "roofline": head["roofline"],
             "e2e": head["e2e"], "gpu_launches": head["gpu_launches"], "launch": "CUDA graphs" if G.use_graphs else "eager", "clocks": sampler.summary(),
             "pct_of_8TBs": head["pct_of_8TBs"], "kernel_status": status, "per_config": per_config}
