@@ -66,6 +66,7 @@ struct TcParams {
   float alpha, beta;
   int* status;
   int SW, SX;             // depth of the weight ring and of the activation ring
+  int SA, slot_bytes;     // (NVFP4 through shared memory) A slots, and the bytes of a weight slot (box + block scales)
   int tmem_cols, dstride; // TMEM columns the CTA takes (a power of two >= 32) and the distance between its two accumulators
 };
 
@@ -883,8 +884,8 @@ __global__ void __launch_bounds__(kSsThreads, 1)
   constexpr int F = LX_W_NVFP4;
   using Fm = TcFmt<F>;
   extern __shared__ __align__(1024) uint8_t smem[];
-  const int NC = P.NC, SW = P.SW, SX = P.SX, SA = P.tmem_cols;  // (tmem_cols carries the number of A slots: the kernel takes all of TMEM)
-  const int x_bytes = P.x_bytes, box_bytes = P.box_bytes, slot_bytes = P.dstride;  // (dstride carries the bytes of a weight slot)
+  const int NC = P.NC, SW = P.SW, SX = P.SX, SA = P.SA;
+  const int x_bytes = P.x_bytes, box_bytes = P.box_bytes, slot_bytes = P.slot_bytes;
   uint8_t* const aring = smem + static_cast<size_t>(SW) * slot_bytes;
   uint8_t* const xring = aring + static_cast<size_t>(SA) * kSsSlotBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(xring + static_cast<size_t>(SX) * x_bytes);
@@ -1203,7 +1204,7 @@ int tc_launch(const lx_weight& w, TcParams P, cudaStream_t stream, int* grid_out
       if (sw_fit < 5) sa = 2, sw_fit = (kBudget - kBars - P.SX * P.x_bytes - sa * kSsSlotBytes) / slot;
       if (sw_fit >= 2) {
         P.SW = std::min(12, sw_fit);
-        P.tmem_cols = sa, P.dstride = slot;  // (the kernel takes all of TMEM; these two fields carry its ring geometry)
+        P.SA = sa, P.slot_bytes = slot;
         const size_t bytes = static_cast<size_t>(P.SW) * slot + static_cast<size_t>(sa) * kSsSlotBytes + P.SX * P.x_bytes + kBars;
         if (int e = allow_big_smem<F * 4 + 1>(tc_nvfp4_ss_kernel)) return e;
         return launch_kernel(tc_nvfp4_ss_kernel, dim3(grid), dim3(kSsThreads), bytes, stream, wmap, smap, P);

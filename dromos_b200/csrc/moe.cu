@@ -312,6 +312,7 @@ __device__ __forceinline__ int block_exclusive_scan_1024(int x, int* warp_totals
   return before + v - x;
 }
 
+static_assert(kMaxExperts == 1024, "group_pairs_kernel zeroes one count per thread of its 1024");
 __global__ void __launch_bounds__(1024) group_pairs_kernel(const int32_t* __restrict__ ids, int P, int E,
                                                            int32_t* __restrict__ offsets, int32_t* __restrict__ pairs,
                                                            const ExpertChunkTables chunks, int own0, int own1) {
@@ -689,25 +690,30 @@ extern "C" int lx_moe_experts_grouped(const void* latent, const int32_t* ids, co
 extern "C" int lx_b200_moe_experts_owned(const void* latent, const int32_t* ids, const float* weights, const lx_weight* gate_up,
                                          const lx_weight* down, lx_math math, float* rows, void* workspace, int T, int L, int I,
                                          int E, int own0, int own1, int top_k, void* stream) {
-  if (T < 0 || L <= 0 || I <= 0 || E <= 0 || top_k <= 0 || top_k > E || !gate_up || !down) return kInvalid;
+  if (T < 0 || L <= 0 || I <= 0 || E <= 0 || top_k <= 0 || top_k > E) return kInvalid;
   if (own0 < 0 || own1 < own0 || own1 > E) return kInvalid;
   if (math < LX_MATH_BF16 || math > LX_MATH_FP4) return kInvalid;
-  if (T == 0 || own1 == own0) return kOk;
-  if (!latent || !ids || !weights || !rows || !workspace || !gate_up->data || !down->data) return kInvalid;
-  if (gate_up->type < LX_W_BF16 || gate_up->type > LX_W_NVFP4 || down->type < LX_W_BF16 || down->type > LX_W_NVFP4)
-    return kNotSupported;
-  if ((gate_up->type != LX_W_BF16 && !gate_up->scale) || (down->type != LX_W_BF16 && !down->scale)) return kInvalid;
+  if (T == 0) return kOk;
+  if (!ids || !workspace) return kInvalid;
   if (E > kMaxExperts || static_cast<int64_t>(T) * top_k > (1ll << 30)) return kNotSupported;
-  if (int e = math_admitted(math, gate_up->type)) return e;
-  if (int e = math_admitted(math, down->type)) return e;
-  if (I % 8 != 0 || L % 8 != 0 || !experts_tc_ok(*gate_up, *down, L, I)) return kNotSupported;  // the tensor-core kernels only
+  if (I % 8 != 0 || L % 8 != 0) return kNotSupported;
   auto s = static_cast<cudaStream_t>(stream);
   const int P = T * top_k;
   const Layout l = layout(P, E, L, I);
   auto* ws = static_cast<uint8_t*>(workspace);
+  // The grouping tables are written whatever the owned range is: the row exchange reads them on every rank, also on a
+  // rank that owns no expert (more ranks than experts) and therefore holds no stacks.
   const ExpertChunkTables chunks = expert_chunk_tables(ws, l.total, P, E, L, I);
   if (int e = launch_group(ids, P, E, reinterpret_cast<int32_t*>(ws + l.offsets), reinterpret_cast<int32_t*>(ws + l.pairs), chunks, own0, own1, s))
     return e;
+  if (own1 == own0) return kOk;
+  if (!gate_up || !down || !latent || !weights || !rows || !gate_up->data || !down->data) return kInvalid;
+  if (gate_up->type < LX_W_BF16 || gate_up->type > LX_W_NVFP4 || down->type < LX_W_BF16 || down->type > LX_W_NVFP4)
+    return kNotSupported;
+  if ((gate_up->type != LX_W_BF16 && !gate_up->scale) || (down->type != LX_W_BF16 && !down->scale)) return kInvalid;
+  if (int e = math_admitted(math, gate_up->type)) return e;
+  if (int e = math_admitted(math, down->type)) return e;
+  if (!experts_tc_ok(*gate_up, *down, L, I)) return kNotSupported;  // the tensor-core kernels only
   return experts_tc(latent, weights, *gate_up, *down, reinterpret_cast<const int32_t*>(ws + l.offsets),
                     reinterpret_cast<const int32_t*>(ws + l.pairs), reinterpret_cast<uint16_t*>(ws + l.mid), rows, ws, l.total, T, L, I, E,
                     top_k, status_word(), s, math != LX_MATH_BF16, own1 - own0);

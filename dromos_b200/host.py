@@ -237,7 +237,9 @@ class ReplicatedExpertParallel:
         assert T <= self.max_tokens
         e0 = self.bounds[self.rank] if e0 is None else e0
         e1 = self.bounds[self.rank + 1] if e1 is None else e1
-        st = self.lib.lx_b200_moe_experts_owned(abi.ptr(latent), abi.ptr(ids), abi.ptr(weights), self.gate_up.ref(), self.down.ref(), self.math,
+        gu = self.gate_up.ref() if self.gate_up is not None else None  # a rank that owns no expert holds no stacks
+        dn = self.down.ref() if self.down is not None else None
+        st = self.lib.lx_b200_moe_experts_owned(abi.ptr(latent), abi.ptr(ids), abi.ptr(weights), gu, dn, self.math,
                                                 abi.ptr(self.rows), abi.ptr(self.ws), T, self.L, self.I, self.E, e0, e1, self.top_k, _stream())
         if st:
             raise RuntimeError(f"lx_b200_moe_experts_owned failed: {st}")

@@ -88,6 +88,22 @@ def test_owned_experts_of_every_split_add_up_to_the_grouped_experts(lx, wtype, c
     util.check_status(lx)
 
 
+def test_a_rank_without_experts_still_writes_the_grouping_tables(lx):
+    """More ranks than experts: the rank's owned range is empty and it holds no stacks; the call groups (the row exchange reads
+    the tables on every rank) and multiplies nothing."""
+    T, L, I, E, top_k = 6, 256, 128, 4, 2
+    eng = host.ReplicatedExpertParallel(lx, None, None, E, L, I, top_k, T, torch.device("cuda"))
+    eng.ws.fill_(0xFF)
+    latent = torch.randn((T, L), device="cuda").to(torch.bfloat16)
+    ids = torch.tensor([[0, 1], [2, 3], [1, 0], [3, 3], [2, 0], [1, 2]], dtype=torch.int32, device="cuda")
+    w = torch.ones((T, top_k), device="cuda")
+    eng.owned(latent, ids, w, 2, 2)
+    torch.cuda.synchronize()
+    offsets = eng.ws[: 4 * (E + 1)].view(torch.int32).tolist()
+    assert offsets == [0, 3, 6, 9, 12]  # pairs per expert: 3, 3, 3, 3
+    util.check_status(lx)
+
+
 def test_owned_experts_refuse_what_they_cannot_take(lx):
     T, L, I, E, top_k = 4, 256, 128, 8, 2
     gu = host.store_weight(lx, (torch.randn((E, 2 * I, L), device="cuda") * 0.02).to(torch.bfloat16), abi.W_NVFP4)
