@@ -200,46 +200,58 @@ __device__ __forceinline__ void gemv_stage_x(const GemvParams& P, uint8_t* xs, f
 // ---- BF16X: a row's patches, walked forward in k ---------------------------------------------------------------------------
 // Two registers per row: the next patch not yet passed ((k << 8) | exponent, 0xffffffff when there is none) and how many
 // the lane has taken. Where the list lives (header slots or an overflow record) is looked up again on every take: rows
-// with patches are few and their patches fewer.
+// with patches are few and their patches fewer. The walking functions are out of line (they are rarely called) and take
+// and return everything BY VALUE: a cursor handed over by reference (or as `this`) has to live in local memory, and then
+// every check of `next` in the main loop is a local load (that version ran the C4 product in 45 us).
 struct X16Cursor {
   uint32_t next, taken;
-  __device__ __noinline__ void take(const uint8_t* rec, int slots) {
-    const uint32_t* list = reinterpret_cast<const uint32_t*>(rec);
-    uint32_t n = static_cast<uint32_t>(slots);
-    const uint32_t first = __ldg(list);
-    if (first != x16::kNoPatch && (first & 0x80000000u)) {  // more patches than slots: they live in an overflow record
-      const uint32_t* r = reinterpret_cast<const uint32_t*>(rec + static_cast<int64_t>(first & 0x7fffffffu) * 8);
-      n = __ldg(r);
-      list = r + 1;
-    }
-    next = taken < n ? __ldg(list + taken) : x16::kNoPatch;
-    ++taken;
-  }
-  __device__ __forceinline__ void start(const uint8_t* rec, int slots, uint32_t k_from) {
-    taken = 0;
-    next = __ldg(reinterpret_cast<const uint32_t*>(rec));
-    if (next == x16::kNoPatch) return;  // most rows
-    take(rec, slots);
-    while ((next >> 8) < k_from) take(rec, slots);
-  }
-  // the patches that fall in [k0, k0 + 8) go into the exponent bytes of values k0..k0+3 (e_lo) and k0+4..k0+7 (e_hi)
-  __device__ __noinline__ void apply(const uint8_t* rec, int slots, uint32_t k0, uint32_t& e_lo, uint32_t& e_hi) {
-    while ((next >> 8) < k0) take(rec, slots);
-    while ((next >> 8) < k0 + 8) {
-      const uint32_t d = (next >> 8) - k0, sh = 8 * (d & 3), v = (next & 0xffu) << sh, m = ~(0xffu << sh);
-      if (d < 4) e_lo = (e_lo & m) | v;
-      else e_hi = (e_hi & m) | v;
-      take(rec, slots);
-    }
-  }
 };
+__device__ __noinline__ uint2 x16_take(const uint8_t* rec, int slots, uint32_t taken) {
+  const uint32_t* list = reinterpret_cast<const uint32_t*>(rec);
+  uint32_t n = static_cast<uint32_t>(slots);
+  const uint32_t first = __ldg(list);
+  if (first != x16::kNoPatch && (first & 0x80000000u)) {  // more patches than slots: they live in an overflow record
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(rec + static_cast<int64_t>(first & 0x7fffffffu) * 8);
+    n = __ldg(r);
+    list = r + 1;
+  }
+  return make_uint2(taken < n ? __ldg(list + taken) : x16::kNoPatch, taken + 1);
+}
+__device__ __forceinline__ X16Cursor x16_start(const uint8_t* rec, int slots, uint32_t k_from) {
+  X16Cursor c{__ldg(reinterpret_cast<const uint32_t*>(rec)), 0u};
+  if (c.next == x16::kNoPatch) return c;  // most rows
+  do {
+    const uint2 r = x16_take(rec, slots, c.taken);
+    c.next = r.x, c.taken = r.y;
+  } while ((c.next >> 8) < k_from);
+  return c;
+}
+// the patches that fall in [k0, k0 + 8) go into the exponent bytes of values k0..k0+3 (e_lo) and k0+4..k0+7 (e_hi);
+// returns {next, taken, e_lo, e_hi}
+__device__ __noinline__ uint4 x16_apply(const uint8_t* rec, int slots, uint32_t k0, uint32_t next, uint32_t taken, uint32_t e_lo, uint32_t e_hi) {
+  while ((next >> 8) < k0) {
+    const uint2 r = x16_take(rec, slots, taken);
+    next = r.x, taken = r.y;
+  }
+  while ((next >> 8) < k0 + 8) {
+    const uint32_t d = (next >> 8) - k0, sh = 8 * (d & 3), v = (next & 0xffu) << sh, m = ~(0xffu << sh);
+    if (d < 4) e_lo = (e_lo & m) | v;
+    else e_hi = (e_hi & m) | v;
+    const uint2 r = x16_take(rec, slots, taken);
+    next = r.x, taken = r.y;
+  }
+  return make_uint4(next, taken, e_lo, e_hi);
+}
 
 // 8 bf16 (4 registers, values in k order) from 8 sign|mantissa bytes (sm0, sm1), their word of codes and the block's base
 __device__ __forceinline__ void x16_decode8(uint32_t sm0, uint32_t sm1, uint32_t codes, uint32_t base, X16Cursor& cur, const uint8_t* rec, int slots, uint32_t k0, uint32_t (&a)[4]) {
   const uint32_t base4 = base * 0x01010101u;
   uint32_t e_lo = base4 - (codes & 0x0f0f0f0fu);
   uint32_t e_hi = base4 - ((codes >> 4) & 0x0f0f0f0fu);
-  if ((cur.next >> 8) < k0 + 8) cur.apply(rec, slots, k0, e_lo, e_hi);
+  if ((cur.next >> 8) < k0 + 8) {
+    const uint4 r = x16_apply(rec, slots, k0, cur.next, cur.taken, e_lo, e_hi);
+    cur.next = r.x, cur.taken = r.y, e_lo = r.z, e_hi = r.w;
+  }
   const uint2 v0 = x16_assemble(sm0, e_lo), v1 = x16_assemble(sm1, e_hi);
   a[0] = v0.x, a[1] = v0.y, a[2] = v1.x, a[3] = v1.y;
 }
@@ -418,10 +430,10 @@ __global__ void __launch_bounds__(kGemvThreads, CPS) gemv_kernel(const GemvParam
       for (int c = 0; c < 4; ++c) acc[b][c] = 0u;
     X16Cursor ca, cb;
     if constexpr (kX16) {
-      ca.next = cb.next = x16::kNoPatch;
+      ca = cb = X16Cursor{x16::kNoPatch, 0u};
       if (rem > 0) {
-        ca.start(pa, slots, static_cast<uint32_t>(s0) * 64u);
-        cb.start(pb, slots, static_cast<uint32_t>(s0) * 64u);
+        ca = x16_start(pa, slots, static_cast<uint32_t>(s0) * 64u);
+        cb = x16_start(pb, slots, static_cast<uint32_t>(s0) * 64u);
       }
     }
     for (int j = 0; j < n_b; ++j) {
