@@ -153,6 +153,13 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------------------------------
 
 
+def reference_cuda_library():
+    """The reference's own CUDA backend (oracle/_ref/libdromos_kernels_ref.so, `make -C oracle cuda_ref`), timed beside this
+    library's kernels only when --reference-cuda asks for it: a reported baseline like the CPU one, never part of `value`."""
+    path = os.path.join(ROOT, "oracle", "_ref", "libdromos_kernels_ref.so")
+    return abi.Library(path) if os.path.exists(path) else None
+
+
 def cpu_library():
     path = os.path.join(ROOT, "oracle", "_ref", "libdromos_cpu.so")
     return abi.Library(path) if os.path.exists(path) else None
@@ -461,6 +468,23 @@ def dense_leg(G, name, steps, warmup, scaling, peaks, sampler=None, parity=False
         k_bytes += shard_bytes
         k_ms += t
     achieved = k_bytes / (k_ms * 1e-3) / 1e9
+    reference_cuda = None
+    if getattr(G, "refcuda", None) is not None and world == 1:  # the same sweep on the reference's own CUDA kernels
+        theirs = [host.Linear(G.refcuda, s_, rows, K) for s_ in stored]
+        ref_m, ref_ms = {}, 0.0
+        for M in Ms:
+            def ref_sweep(_, M=M):
+                for c in range(copies):
+                    theirs[c](xs[M], ys[M])
+            run_ref, _ = G.replayer(ref_sweep, 1)
+            for i in range(2):
+                run_ref(i)
+            t = G.timed(run_ref, reps) / (reps * copies)
+            ref_m[str(M)] = {"us": t * 1e3, "GB/s": shard_bytes / (t * 1e-3) / 1e9, "speedup_of_this_library": t * 1e3 / per_m[str(M)]["us"]}
+            ref_ms += t
+        reference_cuda = {"kind": "the reference's engine/cuda compiled unmodified for architecture 100 (its kernels of the 80 / 89 / 90 families)",
+                          "per_m": ref_m, "GB/s": k_bytes / (ref_ms * 1e-3) / 1e9, "speedup_of_this_library": ref_ms / k_ms}
+        del theirs
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": NCU_TRAFFIC.get(name) if world == 1 else None, "peak_source": f"{peak_kind} copy bandwidth (burst)",
                 "read_only_peak": read_only, "frac_of_read_only": achieved / read_only if read_only else None,
@@ -502,6 +526,8 @@ def dense_leg(G, name, steps, warmup, scaling, peaks, sampler=None, parity=False
     out = {"workload": DENSE[name][-1], "scaling": scaling, "value": value, "unit": "TB/s", "ms_per_step": ms / steps, "steps": steps,
            "pct_of_8TBs": value / 8.0 / max(world, 1) * 100.0, "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches),
            "exchange": exchange, "dtype": DTYPE[wtype]}
+    if reference_cuda is not None:
+        out["reference_cuda"] = reference_cuda
 
     # ---- correctness of what the exchange delivered: a peer's slice, recomputed here from the peer's seed ----
     if parity and world > 1:
@@ -618,6 +644,18 @@ def moe_leg(G, name, steps, warmup, peaks):
            "dtype": DTYPE[wtype]}
     if parity is not None:
         rec["parity_check"] = parity
+    if getattr(G, "refcuda", None) is not None and world == 1:
+        theirs = [host.Experts(G.refcuda, gu, dn, E, L, I, top_k) for gu, dn in stacks]
+        their_router = host.Experts(G.refcuda, stacks[0][0], stacks[0][1], E, L, I, top_k)
+
+        def ref_step(i):
+            ids, w = their_router.route(logits[i % periods])
+            theirs[i % copies](latent, ids, w, out)
+
+        ref_ms, _, _ = G.timed_steps(ref_step, steps, warmup, periods * copies)
+        rec["reference_cuda"] = {"kind": "the reference's engine/cuda compiled unmodified for architecture 100", "ms_per_step": ref_ms / steps,
+                                 "value": sum(step_bytes) / (ref_ms * 1e-3) / 1e12, "speedup_of_this_library": ref_ms / ms}
+        del theirs, their_router
     del stacks, engines
     torch.cuda.empty_cache()
     return rec
@@ -641,6 +679,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--only", default="", help="comma-separated workloads to time besides the headline (default: all six)")
+    ap.add_argument("--reference-cuda", action="store_true", help="also time the reference's own CUDA kernels (oracle/_ref/libdromos_kernels_ref.so) on every workload")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -672,6 +711,7 @@ def main():
         return
 
     G = Gpu()
+    G.refcuda = reference_cuda_library() if args.reference_cuda else None
     peak, peak_kind = measured_peak_gbs()
     read_only = read_only_ceiling(G)
     peaks = (peak, peak_kind, read_only)

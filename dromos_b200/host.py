@@ -160,7 +160,10 @@ class Experts:
         T = logits.shape[0]
         ids = torch.empty((T, self.top_k), dtype=torch.int32, device=logits.device)
         weights = torch.empty((T, self.top_k), dtype=torch.float32, device=logits.device)
-        st = self.lib.lx_moe_route(abi.ptr(logits), abi.ptr(bias), abi.ptr(ids), abi.ptr(weights), None, None, T,
+        # entropy and confidence are required outputs of the reference's entry point (its kernel writes them without a null
+        # check, engine/cuda/moe.cu:67), so they are always passed; the last call's values stay readable as self.stats
+        self.stats = torch.empty((2, T), dtype=torch.float32, device=logits.device)
+        st = self.lib.lx_moe_route(abi.ptr(logits), abi.ptr(bias), abi.ptr(ids), abi.ptr(weights), abi.ptr(self.stats[0]), abi.ptr(self.stats[1]), T,
                                    logits.shape[1], self.top_k, _stream())
         if st:
             raise RuntimeError(f"lx_moe_route failed: {st}")
