@@ -6,6 +6,7 @@
 #include <cstring>
 
 #include "gemv.cuh"
+#include "gemv_x16.cuh"
 #include "launch.cuh"
 #include "scalar.cuh"
 #include "variants.h"
@@ -114,6 +115,31 @@ int launch_gemv_inst(const GemvParams& P, size_t smem, cudaStream_t stream) {
   return launch_kernel(kernel, dim3(grid), dim3(kGemvThreads), smem, stream, P);
 }
 
+// The lossless format's own kernel (gemv_x16.cuh): one CTA per SM, records brought in by bulk copies. `taken` = false when
+// the shape is not for it (no ring fits beside the activations, or the copy of the last record would read past the
+// matrix: records that are not 16-byte aligned are copied from 8 bytes before to 8 bytes after).
+template <int NT>
+int launch_x16(const GemvParams& P, cudaStream_t stream, bool& taken) {
+  taken = false;
+  X16Ring R{};
+  size_t smem = 0;
+  const bool a16 = P.row_bytes % 16 == 0;
+  if (!aligned(P.w, 16) || (!a16 && P.N % 2 != 0) || !x16_ring_for(P.K, P.ncols, R, smem)) return kOk;
+  const int sms = sm_count();
+  if (!sms) return kInvalid;
+  R.status = status_word();
+  taken = true;
+  const unsigned grid = static_cast<unsigned>(std::max(1, std::min((P.N + kGemvGranule - 1) / kGemvGranule, sms)));
+  if (a16) {
+    auto kernel = gemv_x16_kernel<NT, true>;
+    if (int e = allow_dynamic_smem<4800 + NT * 2 + 1>(kernel)) return e;
+    return launch_kernel(kernel, dim3(grid), dim3(kX16Threads), smem, stream, P, R);
+  }
+  auto kernel = gemv_x16_kernel<NT, false>;
+  if (int e = allow_dynamic_smem<4800 + NT * 2>(kernel)) return e;
+  return launch_kernel(kernel, dim3(grid), dim3(kX16Threads), smem, stream, P, R);
+}
+
 // variant: an index into kGemvVariantNames (see variants.h), -1 = two CTAs per SM when their shared memory allows
 template <int F>
 int launch_gemv(GemvParams P, int variant, cudaStream_t stream) {
@@ -123,8 +149,15 @@ int launch_gemv(GemvParams P, int variant, cudaStream_t stream) {
   P.steps = P.K / GemvFmt<F>::kStepValues;
   const size_t smem = gemv_smem(P.K, F, P.ncols);
   const int NT = (P.ncols + 7) / 8;
-  // BF16X decodes in registers and wants more of them than two CTAs per SM leave (measured: 36 us against 55 on the
-  // 14336 x 4096 matrix), so one CTA per SM is its default; the table can still name d4c2.
+  // BF16X: its own kernel by default (gemv_x16.cuh); the table can still name this one's two forms, of which d8c1 is the
+  // fallback (two CTAs per SM leave the in-register decode too few registers: 55 us against 39 on a 14336 x 4096 matrix).
+  if constexpr (F == LX_W_BF16X) {
+    if ((variant == kGemvX16Pipe || variant < 0) && NT <= 2) {
+      bool taken = false;
+      const int e = NT == 1 ? launch_x16<1>(P, stream, taken) : launch_x16<2>(P, stream, taken);
+      if (taken) return e;
+    }
+  }
   const bool two = variant == kGemvD4C2 || (variant < 0 && F != LX_W_BF16X);
   const int cps = (smem <= 110 * 1024 && two) ? 2 : 1;
   switch (NT * 10 + cps) {
@@ -183,7 +216,9 @@ int dense_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, cons
   // the tcgen05 product ("s1tc", INT8 / FP8 weights with enough rows per SM). LX_B200_GEMV=0 restores the ring / tc pair.
   if (M <= 8 && !force_scalar()) {
     int tuned = lx_tune_get(gemv_kernel_name(w.type), M, N, K);
+    if (w.type == LX_W_BF16X) tuned = x16_variant(tuned);  // its list has its own third entry
     if (tuned < 0) tuned = gemv_env_variant();  // LX_B200_GEMV_VARIANT=<name>: the variant of shapes the table does not hold
+    if (tuned == kGemvX16Pipe && w.type != LX_W_BF16X) tuned = -1;
     const bool gemv_named = tuned == kGemvD4C2 || tuned == kGemvD8C1;
     const bool want_tc = tuned == kGemvTc || (tuned < 0 && (!gemv_enabled() || w.type == LX_W_INT8));
     const bool want_ring = tuned == kGemvRing || (tuned < 0 && !gemv_enabled());

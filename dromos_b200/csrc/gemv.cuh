@@ -141,8 +141,14 @@ __device__ __forceinline__ void lds16(uint4& v, uint32_t addr, uint32_t on) {
 // The scaled maths need each row's largest magnitude before the first digit can be made: one pass over the rows for the
 // maxima, a second (from L2) for the values. (Keeping the first pass's values in registers for the second was tried:
 // the registers it holds across the barrier cost the main loop more than the second pass costs.)
-template <int ACT, bool XBF, bool SWZ>
+// NAMED: the kGemvThreads callers are not the whole CTA (another warp does something else meanwhile): they meet at named
+// barrier 1 instead of the CTA's barrier.
+template <int ACT, bool XBF, bool SWZ, bool NAMED = false>
 __device__ __forceinline__ void gemv_stage_x(const GemvParams& P, uint8_t* xs, float* inv_scale, float* part, int tid) {
+  auto meet = [] {
+    if constexpr (NAMED) named_bar_sync(1, kGemvThreads);
+    else __syncthreads();
+  };
   constexpr int V = 16 / act_elem(ACT);  // activations per 16 bytes of a plane
   const int warp = tid >> 5, lane = tid & 31;
   const bool aligned16 = (reinterpret_cast<uintptr_t>(P.x) & 15) == 0 && P.ld_x % (XBF ? 8 : 4) == 0;
@@ -173,7 +179,7 @@ __device__ __forceinline__ void gemv_stage_x(const GemvParams& P, uint8_t* xs, f
       const float a = warp_max(row_max_share<XBF>(P.x, static_cast<int64_t>(m) * P.ld_x, P.K, aligned16, tid, kGemvThreads));
       if (lane == 0) part[8 + m * kGemvWarps + warp] = a;
     }
-    __syncthreads();
+    meet();
     if (tid < 8) {
       float a = 0.0f;
       if (tid < P.M) {
@@ -182,9 +188,9 @@ __device__ __forceinline__ void gemv_stage_x(const GemvParams& P, uint8_t* xs, f
       }
       row_max[tid] = __float_as_uint(a);
     }
-    __syncthreads();
+    meet();
     set_scales();
-    __syncthreads();
+    meet();
   } else {
     if (tid < 8) inv_scale[tid] = 1.0f;
   }
@@ -194,7 +200,7 @@ __device__ __forceinline__ void gemv_stage_x(const GemvParams& P, uint8_t* xs, f
     load_values<XBF, V>(P.x, static_cast<int64_t>(m) * P.ld_x, p * V, P.K, aligned16, v);
     store_planes(m, p, v);
   }
-  __syncthreads();
+  meet();
 }
 
 // ---- BF16X: a row's patches, walked forward in k ---------------------------------------------------------------------------

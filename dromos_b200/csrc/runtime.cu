@@ -161,7 +161,7 @@ int lx_tune_set(const char* kernel, int M, int N, int K, int variant) {
   if (wtype >= 0) {
     const bool eligible = gemv_shape_ok(wtype, K, true);
     const bool wide_int8 = wtype == LX_W_INT8 && tc_rows_shape_ok(wtype, N, K);
-    const int cls = gemv_order_class(variant), default_cls = wide_int8 ? 2 : eligible ? 0 : 1;
+    const int cls = gemv_order_class(wtype == LX_W_BF16X ? x16_variant(variant) : variant), default_cls = wide_int8 ? 2 : eligible ? 0 : 1;
     if (cls != default_cls && !(cls == 0 && !eligible && !wide_int8)) return LX_ERR_TUNE_REJECTED;
   }
   std::lock_guard<std::mutex> lock(g_mu);

@@ -8,10 +8,11 @@
 //   s16d8c1  the same kernel, one CTA per SM, 128 bytes in flight
 //   s8ring   the TMA-ring mma.sync kernel of stream.cuh     another order: lx_tune_set refuses it, lx_tune_force takes it
 //   s1tc     the tcgen05 product (INT8 / FP8, wide weights) another order again
-// "gemv_bf16x" lists only the two forms of the decode GEMV, without a split: its variants are the format's own, change
-// no sum and are admitted at every key (the kernel must keep the bits of the bf16 kernel's default).
+// "gemv_bf16x" lists only forms of the decode GEMV, without a split: its variants are the format's own, change no sum and
+// are admitted at every key (the kernel must keep the bits of the bf16 kernel's default): d4c2 and d8c1 as above, and
+//   d1c1     the format's own kernel (gemv_x16.cuh): one CTA per SM, records brought into shared memory by bulk copies
 // What runs when the table holds nothing for a shape: d4c2 when two CTAs' activation columns fit an SM, else d8c1
-// (BF16X: always d8c1, it needs the registers).
+// (BF16X: d1c1).
 //
 // "gemm_w.<kind>.sm100" are the families of lx_gemm_w by operand kind (the reference's names, engine/cuda/gemm_w.cu):
 // each has the one tile shape of the tcgen05 product, rows of W split evenly over the SMs, so there is nothing to pick.
@@ -27,9 +28,12 @@ struct VariantList {
   const char* const* names;
 };
 
-enum GemvVariant { kGemvD4C2 = 0, kGemvD8C1 = 1, kGemvRing = 2, kGemvTc = 3, kGemvVariants = 4 };
+enum GemvVariant { kGemvD4C2 = 0, kGemvD8C1 = 1, kGemvRing = 2, kGemvTc = 3, kGemvVariants = 4, kGemvX16Pipe = 4 };
 inline const char* const kGemvVariantNames[kGemvVariants] = {"s16d4c2", "s16d8c1", "s8ring", "s1tc"};
-inline const char* const kX16VariantNames[2] = {"d4c2", "d8c1"};
+constexpr int kX16Variants = 3;
+inline const char* const kX16VariantNames[kX16Variants] = {"d4c2", "d8c1", "d1c1"};
+// The lossless kernel's third entry is its own kernel, not the ring: an index of its list as a GemvVariant.
+inline int x16_variant(int index) { return index == 2 ? kGemvX16Pipe : index; }
 inline const char* const kGemmWVariantNames[1] = {"rows128"};
 // Variants of one class add a row's products in the same order (same bits).
 inline int gemv_order_class(int variant) { return variant == kGemvRing ? 1 : variant == kGemvTc ? 2 : 0; }
@@ -39,7 +43,7 @@ constexpr int kVariantKernels = 11;
 inline const VariantList kVariantTable[kVariantKernels] = {
     {"gemv_w_bf16", kGemvVariants, kGemvVariantNames},  {"gemv_w_int8", kGemvVariants, kGemvVariantNames},
     {"gemv_w_fp8", kGemvVariants, kGemvVariantNames},   {"gemv_w_nvfp4", kGemvVariants, kGemvVariantNames},
-    {"gemv_bf16x", 2, kX16VariantNames},
+    {"gemv_bf16x", kX16Variants, kX16VariantNames},
     {"gemm_w.bf16.sm100", 1, kGemmWVariantNames},  {"gemm_w.w8i8.sm100", 1, kGemmWVariantNames},
     {"gemm_w.w8f8.sm100", 1, kGemmWVariantNames},  {"gemm_w.w4a16.sm100", 1, kGemmWVariantNames},
     {"gemm_w.i8.sm100", 1, kGemmWVariantNames},    {"gemm_w.f8.sm100", 1, kGemmWVariantNames},
@@ -60,6 +64,7 @@ inline int gemv_variant_by_name(const char* name) {
     const char* bare = full + std::strspn(full, "s0123456789");
     if (name && (std::strcmp(full, name) == 0 || std::strcmp(bare, name) == 0)) return i;
   }
+  if (name && std::strcmp(name, kX16VariantNames[2]) == 0) return kGemvX16Pipe;  // means something to the lossless kernel only
   return -1;
 }
 

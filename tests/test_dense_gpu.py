@@ -220,13 +220,19 @@ def test_rows_do_not_depend_on_batch_and_runs_repeat(lx, fmt, K, x_f32, N):
         assert np.array_equal(outs[M], outs[8][:M]), f"rows at M={M} differ from the same rows at M=8"
 
 
-def test_bf16x_product_equals_bf16_product_bitwise(lx):
-    N, K = 512, 4096
+@pytest.mark.parametrize("N,K", [(512, 4096), (520, 1536), (264, 8192), (77, 1536), (40, 14336), (2400, 512)],
+                         ids=["aligned", "short_last_unit", "records_8_aligned", "odd_rows", "long_rows", "many_units"])
+def test_bf16x_product_equals_bf16_product_bitwise(lx, N, K):
+    """Records that start on 16-byte boundaries (header a multiple of 16 bytes: K = 4096, 512) and records that do not
+    (K = 1536, 8192, 14336: every other record starts 8 bytes off), a last unit of fewer than 16 rows, an odd number of
+    8-aligned records (the copy of the last one would end past the matrix: the in-register kernel takes those)."""
     w_bits = util.bf16_normal((N, K), 0.02, 5)
     # patches: a few values far below their block's largest, one row with more patches than its slots
     w_bits[3, 100] = O.f32_to_bf16_bits(np.float32([2.0**-60]))[0]
-    w_bits[3, 1000] = O.f32_to_bf16_bits(np.float32([-(2.0**-70)]))[0]
+    w_bits[3, 1000 % K] = O.f32_to_bf16_bits(np.float32([-(2.0**-70)]))[0]
     w_bits[17, ::9] = O.f32_to_bf16_bits(np.float32([2.0**-90]))[0]
+    w_bits[N - 1, K - 1] = O.f32_to_bf16_bits(np.float32([2.0**-80]))[0]
+    w_bits[N - 2, 0] = O.f32_to_bf16_bits(np.float32([-(2.0**-80)]))[0]
     dw16 = util.DeviceWeight(util.make_weight(w_bits, O.W_BF16))
     dwx = util.DeviceWeight(util.make_weight(w_bits, O.W_BF16X))
     for x_dt, x_dev in ((abi.BF16, util.dev(util.bf16_normal((8, K), 1.0, 6))), (abi.F32, util.dev(util.f32_normal((8, K), 1.0, 6)))):
