@@ -31,6 +31,8 @@
 //     returns at once; the copying warp still waits (bounded) for the copies it has in flight before it leaves.
 #pragma once
 
+#include <type_traits>
+
 #include "gemv.cuh"
 
 namespace b200 {
@@ -63,7 +65,9 @@ inline bool x16_ring_for(int K, int ncols, X16Ring& r, size_t& smem_total) {
     smem_total = r.bar_off + 8u * (2u * r.S + 8u) + 16u;
     return true;
   };
-  if (fixed + 2u * ((unit_bytes + 127u) & ~127u) <= room) {
+  const char* env_w = std::getenv("LX_B200_X16_WHOLE");  // TEMP
+  const char* env_cb = std::getenv("LX_B200_X16_CB");  // TEMP
+  if (!(env_w && env_w[0] == '0') && fixed + 2u * ((unit_bytes + 127u) & ~127u) <= room) {
     r.whole = 1;
     r.cb = nblk, r.spu = 1;
     r.stride = static_cast<uint32_t>(x16::row_bytes(K));
@@ -85,7 +89,7 @@ inline bool x16_ring_for(int K, int ncols, X16Ring& r, size_t& smem_total) {
     r.spu = (nblk + cb - 1) / cb;
     return r.ring_off + 3u * r.slot_bytes <= room;
   };
-  for (int cb = std::min(32, nblk); cb >= 1; --cb) {
+  for (int cb = std::min(env_cb ? std::atoi(env_cb) : 32, nblk); cb >= 1; --cb) {
     if (!shape(cb)) continue;
     shape((nblk + r.spu - 1) / r.spu);  // the same number of stages, of even sizes
     r.S = static_cast<int>(std::min<uint32_t>(8u, (room - r.ring_off) / r.slot_bytes));
@@ -369,33 +373,38 @@ __global__ void __launch_bounds__(kX16Threads, 1) gemv_x16_kernel(const GemvPara
       if (R.whole) ca = cursor_at(hdr_a, ra), cb = cursor_at(hdr_b, rb);  // the headers came with the stage
       if (a < b) {
         const uint8_t* slot = smem + R.ring_off + ring.slot * R.slot_bytes;
-        const uint8_t* row_a = slot + blocks_a;
-        const uint8_t* row_b = slot + blocks_b;
-#pragma unroll 2
-        for (int s = a; s < b; ++s) {
-          // step s is half s & 1 of block s >> 1
-          const uint32_t blk = static_cast<uint32_t>(s) >> 1, half = static_cast<uint32_t>(s) & 1u;
-          const uint32_t at = (blk - static_cast<uint32_t>(blk_lo)) * 192u;
-          const uint32_t at_sm = at + 64u * half + 16u * t, at_cd = at + 128u + 32u * half + 8u * t;
+        // The lane's place in the block step `a` lies in, and on from there block by block: nothing in the loop multiplies.
+        const uint32_t first = static_cast<uint32_t>(a >> 1) - static_cast<uint32_t>(blk_lo);
+        const uint8_t* row_a = slot + blocks_a + first * 192u + 16u * t;
+        const uint8_t* row_b = slot + blocks_b + first * 192u + 16u * t;
+        const uint8_t* base_at_a = hdr_a + 4 * slots + (a >> 1);
+        const uint8_t* base_at_b = hdr_b + 4 * slots + (a >> 1);
+        uint32_t xo = static_cast<uint32_t>(a) * kXStep;
+        uint32_t lim = (static_cast<uint32_t>(a) * 64u + 16u * t + 16u) << 8;  // the end of this lane's values of the step, as a patch word
+        uint32_t base_a = 0, base_b = 0;
+        // one step: half H of the block at row_a / row_b
+        auto step = [&](auto half_c) {
+          constexpr uint32_t H = decltype(half_c)::value;
           uint4 sm_a, sm_b;
           if constexpr (A16) {
-            sm_a = *reinterpret_cast<const uint4*>(row_a + at_sm);
-            sm_b = *reinterpret_cast<const uint4*>(row_b + at_sm);
+            sm_a = *reinterpret_cast<const uint4*>(row_a + 64u * H);
+            sm_b = *reinterpret_cast<const uint4*>(row_b + 64u * H);
           } else {
-            const uint2 a0 = *reinterpret_cast<const uint2*>(row_a + at_sm), a1 = *reinterpret_cast<const uint2*>(row_a + at_sm + 8);
-            const uint2 b0 = *reinterpret_cast<const uint2*>(row_b + at_sm), b1 = *reinterpret_cast<const uint2*>(row_b + at_sm + 8);
+            const uint2 a0 = *reinterpret_cast<const uint2*>(row_a + 64u * H), a1 = *reinterpret_cast<const uint2*>(row_a + 64u * H + 8);
+            const uint2 b0 = *reinterpret_cast<const uint2*>(row_b + 64u * H), b1 = *reinterpret_cast<const uint2*>(row_b + 64u * H + 8);
             sm_a = make_uint4(a0.x, a0.y, a1.x, a1.y);
             sm_b = make_uint4(b0.x, b0.y, b1.x, b1.y);
           }
-          const uint2 cd_a = *reinterpret_cast<const uint2*>(row_a + at_cd), cd_b = *reinterpret_cast<const uint2*>(row_b + at_cd);
-          const uint32_t base_a = hdr_a[4 * slots + blk] * 0x01010101u, base_b = hdr_b[4 * slots + blk] * 0x01010101u;
+          // the codes of the lane's 16 values: 8 bytes at 128 + 32 H + 8 t of the block (row_a already stands 16 t in)
+          const uint2 cd_a = *reinterpret_cast<const uint2*>(row_a + 128u + 32u * H - 8u * t);
+          const uint2 cd_b = *reinterpret_cast<const uint2*>(row_b + 128u + 32u * H - 8u * t);
           uint32_t wa[8], wb[8];
           x16_words8(sm_a.x, sm_a.y, cd_a.x, base_a, wa);
           x16_words8(sm_a.z, sm_a.w, cd_a.y, base_a, wa + 4);
           x16_words8(sm_b.x, sm_b.y, cd_b.x, base_b, wb);
           x16_words8(sm_b.z, sm_b.w, cd_b.y, base_b, wb + 4);
-          const uint32_t k0 = static_cast<uint32_t>(s) * 64u + 16u * t, lim = (k0 + 16u) << 8;
           if (min(ca.next, cb.next) < lim) {  // rare: a patch of one of the two rows lies below the end of this lane's values
+            const uint32_t k0 = (lim >> 8) - 16u;
             if (ca.next < lim) {
               X16Fix f{ca.next, ca.taken, {wa[0], wa[1], wa[2], wa[3], wa[4], wa[5], wa[6], wa[7]}};
               f = x16_fix16(rec_of(ra), slots, k0, f);
@@ -411,7 +420,6 @@ __global__ void __launch_bounds__(kX16Threads, 1) gemv_x16_kernel(const GemvPara
               for (int i = 0; i < 8; ++i) wb[i] = f.w[i];
             }
           }
-          const uint32_t xo = static_cast<uint32_t>(s) * kXStep;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
 #pragma unroll
@@ -421,6 +429,31 @@ __global__ void __launch_bounds__(kX16Threads, 1) gemv_x16_kernel(const GemvPara
               mma_step<kMmaBf16>(acc[c], wa[4 * h + 2], wb[4 * h + 2], wa[4 * h + 3], wb[4 * h + 3], xv[c].z, xv[c].w);
             }
           }
+          xo += kXStep, lim += 64u << 8;
+        };
+        auto open_block = [&] {
+          base_a = *base_at_a * 0x01010101u, base_b = *base_at_b * 0x01010101u;
+        };
+        auto next_block = [&] {
+          row_a += 192, row_b += 192, ++base_at_a, ++base_at_b;
+        };
+        int s = a;
+        if (s & 1) {  // the slice begins in the second half of a block
+          open_block();
+          step(std::integral_constant<uint32_t, 1>{});
+          next_block();
+          ++s;
+        }
+#pragma unroll 1
+        for (; s + 1 < b; s += 2) {
+          open_block();
+          step(std::integral_constant<uint32_t, 0>{});
+          step(std::integral_constant<uint32_t, 1>{});
+          next_block();
+        }
+        if (s < b) {  // and ends in the first half of one
+          open_block();
+          step(std::integral_constant<uint32_t, 0>{});
         }
       }
       __syncwarp();
