@@ -52,9 +52,12 @@ struct X16Ring {
 };
 
 // The geometry for (K, columns of activations): false when no useful ring fits beside the activations. Measured on a
-// 14336 x 4096 matrix: the larger the copies the better (stages of 4 / 8 / 16 / 32 blocks: 55 / 34 / 30 / 29 us), so a
-// whole unit per stage where two of them fit (its 16 records are one contiguous run: one copy, headers included), else the
-// most blocks per stage that leave three slots.
+// 14336 x 4096 matrix: the fewer and larger the copies the better (per-row copies of 4 / 8 / 11 / 16 blocks per stage: 55 /
+// 34 / 30 / 26 us; one copy per unit: 23.5 us), so a whole unit per stage where two of them fit (its 16 records are one
+// contiguous run: one copy, headers included), else the most blocks per stage that leave three slots. (Stages of 8 or 4
+// whole records would be single copies too, but a unit can only be multiplied when all its rows are there, so they buy
+// nothing unless two whole units fit anyway. Cutting the CTAs' row ranges at multiples of 8 rows, with the second row of
+// each lane left out of a last unit of 8, evens the CTAs out to within half a unit and was measured slower: 24.3 us.)
 inline bool x16_ring_for(int K, int ncols, X16Ring& r, size_t& smem_total) {
   const int nblk = x16::blocks(K), hb = x16::header_bytes(K);
   const uint32_t fixed = static_cast<uint32_t>((gemv_smem(K, LX_W_BF16X, ncols) + 127) / 128 * 128);
@@ -65,9 +68,7 @@ inline bool x16_ring_for(int K, int ncols, X16Ring& r, size_t& smem_total) {
     smem_total = r.bar_off + 8u * (2u * r.S + 8u) + 16u;
     return true;
   };
-  const char* env_w = std::getenv("LX_B200_X16_WHOLE");  // TEMP
-  const char* env_cb = std::getenv("LX_B200_X16_CB");  // TEMP
-  if (!(env_w && env_w[0] == '0') && fixed + 2u * ((unit_bytes + 127u) & ~127u) <= room) {
+  if (fixed + 2u * ((unit_bytes + 127u) & ~127u) <= room) {
     r.whole = 1;
     r.cb = nblk, r.spu = 1;
     r.stride = static_cast<uint32_t>(x16::row_bytes(K));
@@ -89,7 +90,7 @@ inline bool x16_ring_for(int K, int ncols, X16Ring& r, size_t& smem_total) {
     r.spu = (nblk + cb - 1) / cb;
     return r.ring_off + 3u * r.slot_bytes <= room;
   };
-  for (int cb = std::min(env_cb ? std::atoi(env_cb) : 32, nblk); cb >= 1; --cb) {
+  for (int cb = std::min(32, nblk); cb >= 1; --cb) {
     if (!shape(cb)) continue;
     shape((nblk + r.spu - 1) / r.spu);  // the same number of stages, of even sizes
     r.S = static_cast<int>(std::min<uint32_t>(8u, (room - r.ring_off) / r.slot_bytes));
