@@ -63,7 +63,7 @@ HEADLINE = "c3_fp8"
 ORDER = ["c1_bf16", "c2_int8", "c3_fp8", "c3_nvfp4", "c4_bf16x", "c5_moe_fp8"]
 DTYPE = {abi.W_BF16: "bf16", abi.W_INT8: "int8xbf16->f32", abi.W_FP8: "e4m3xbf16->f32", abi.W_NVFP4: "e2m1xbf16->f32", abi.W_BF16X: "bf16"}
 KERNELS = {"c1_bf16": "gemv_kernel<bf16>", "c2_int8": "tc_direct_kernel<int8>", "c3_fp8": "tc_direct_kernel<fp8> (M=16,64), gemv_kernel<fp8> (M=1)",
-           "c3_nvfp4": "tc_nvfp4_ss_kernel (M=16,64), gemv_kernel<nvfp4> (M=1)", "c4_bf16x": "gemv_kernel<bf16x>",
+           "c3_nvfp4": "tc_nvfp4_ss_kernel (M=16,64), gemv_kernel<nvfp4> (M=1)", "c4_bf16x": "gemv_x16_kernel",
            "c5_moe_fp8": "tc_expert_kernel (whole step: route, group, 2 x (prepare, experts), ordered sum)"}
 ROTATE_BYTES = 1 << 30  # weights touched between two uses of the same copy (L2 is 126 MB)
 METRIC = "decode matmul effective HBM TB/s"
@@ -73,7 +73,7 @@ METRIC = "decode matmul effective HBM TB/s"
 # the M = 16 and M = 64 launches; c3_nvfp4: tc_nvfp4_ss_kernel at M = 16; c5_moe_fp8: the gate/up plus the down launch of
 # one step. The few MB written are mostly lines the setup left dirty in L2: the kernels write 0.1-7 MB of outputs.
 NCU_TRAFFIC = {"c1_bf16": 33.59e6, "c2_int8": 58.854e6 + 0.105e6, "c3_fp8": (235.69e6 + 5.20e6 + 237.49e6 + 6.77e6) / 2, "c3_nvfp4": 132.46e6 + 3.55e6,
-               "c4_bf16x": 88.82e6 + 4.25e6, "c5_moe_fp8": 400.74e6 + 7.10e6 + 840.85e6 + 4.11e6}
+               "c4_bf16x": 88.87e6 + 3.47e6, "c5_moe_fp8": 400.74e6 + 7.10e6 + 840.85e6 + 4.11e6}
 
 
 def measured_peak_gbs():
