@@ -57,7 +57,10 @@ struct X16Ring {
 // contiguous run: one copy, headers included), else the most blocks per stage that leave three slots. (Stages of 8 or 4
 // whole records would be single copies too, but a unit can only be multiplied when all its rows are there, so they buy
 // nothing unless two whole units fit anyway. Cutting the CTAs' row ranges at multiples of 8 rows, with the second row of
-// each lane left out of a last unit of 8, evens the CTAs out to within half a unit and was measured slower: 24.3 us.)
+// each lane left out of a last unit of 8, evens the CTAs out to within half a unit and was measured slower: 24.3 us. One
+// 2-D tile copy per stage through a tensor map (8-byte elements, boxes of 16 rows x 8 blocks, ring of 7; possible where
+// records are 16-byte aligned) in place of the 16 per-row copies: 26.8 us at M = 1, 28.1 / 32.3 at M = 4 / 8 against 27.5 /
+// 32.8: nothing gained, so the stages that are not whole units stay per-row bulk copies, which take every alignment.)
 inline bool x16_ring_for(int K, int ncols, X16Ring& r, size_t& smem_total) {
   const int nblk = x16::blocks(K), hb = x16::header_bytes(K);
   const uint32_t fixed = static_cast<uint32_t>((gemv_smem(K, LX_W_BF16X, ncols) + 127) / 128 * 128);
