@@ -7,6 +7,7 @@
 
 #include "gemv.cuh"
 #include "gemv_x16.cuh"
+#include "gemv_ring8.cuh"
 #include "launch.cuh"
 #include "scalar.cuh"
 #include "variants.h"
@@ -140,6 +141,23 @@ int launch_x16(const GemvParams& P, cudaStream_t stream, bool& taken) {
   return launch_kernel(kernel, dim3(grid), dim3(kX16Threads), smem, stream, P, R);
 }
 
+// The 8-bit formats' kernel on bulk copies (gemv_ring8.cuh): one CTA per SM. `taken` = false when two units do not fit.
+template <int F, int NT>
+int launch_ring8(const GemvParams& P, int min_slots, cudaStream_t stream, bool& taken) {
+  taken = false;
+  Ring8 R{};
+  size_t smem = 0;
+  if (!aligned(P.w, 16) || P.K % 128 != 0 || !ring8_for(P.K, F, P.ncols, R, smem) || R.S < min_slots) return kOk;
+  const int sms = sm_count();
+  if (!sms) return kInvalid;
+  R.status = status_word();
+  taken = true;
+  const unsigned grid = static_cast<unsigned>(std::max(1, std::min((P.N + kGemvGranule - 1) / kGemvGranule, sms)));
+  auto kernel = gemv_ring8_kernel<F, NT>;
+  if (int e = allow_dynamic_smem<4900 + F * 4 + NT>(kernel)) return e;
+  return launch_kernel(kernel, dim3(grid), dim3(kX16Threads), smem, stream, P, R);
+}
+
 // variant: an index into kGemvVariantNames (see variants.h), -1 = two CTAs per SM when their shared memory allows
 template <int F>
 int launch_gemv(GemvParams P, int variant, cudaStream_t stream) {
@@ -155,6 +173,17 @@ int launch_gemv(GemvParams P, int variant, cudaStream_t stream) {
     if ((variant == kGemvX16Pipe || variant < 0) && NT <= 2) {
       bool taken = false;
       const int e = NT == 1 ? launch_x16<1>(P, stream, taken) : launch_x16<2>(P, stream, taken);
+      if (taken) return e;
+    }
+  }
+  // The 8-bit formats on short rows: the kernel on bulk copies where it was measured ahead, a single activation row with
+  // three units in shared memory (14336 x 4096: FP8 14.1 against 14.4 us, INT8 14.4 against 17.9; 16384 x 2048 FP8 9.9
+  // against 10.6; at M = 8 it is behind, 24.5 against 22.8). The same sums either way, so the choice may look at M.
+  if constexpr (F == LX_W_INT8 || F == LX_W_FP8) {
+    if ((variant == kGemvX16Pipe || (variant < 0 && P.M == 1)) && NT <= 2) {
+      bool taken = false;
+      const int min_slots = variant == kGemvX16Pipe ? 2 : 3;
+      const int e = NT == 1 ? launch_ring8<F, 1>(P, min_slots, stream, taken) : launch_ring8<F, 2>(P, min_slots, stream, taken);
       if (taken) return e;
     }
   }
@@ -218,8 +247,7 @@ int dense_product(const void* x, int x_dtype, int ld_x, const lx_weight& w, cons
     int tuned = lx_tune_get(gemv_kernel_name(w.type), M, N, K);
     if (w.type == LX_W_BF16X) tuned = x16_variant(tuned);  // its list has its own third entry
     if (tuned < 0) tuned = gemv_env_variant();  // LX_B200_GEMV_VARIANT=<name>: the variant of shapes the table does not hold
-    if (tuned == kGemvX16Pipe && w.type != LX_W_BF16X) tuned = -1;
-    const bool gemv_named = tuned == kGemvD4C2 || tuned == kGemvD8C1;
+    const bool gemv_named = tuned == kGemvD4C2 || tuned == kGemvD8C1 || tuned == kGemvX16Pipe;
     const bool want_tc = tuned == kGemvTc || (tuned < 0 && (!gemv_enabled() || w.type == LX_W_INT8));
     const bool want_ring = tuned == kGemvRing || (tuned < 0 && !gemv_enabled());
     if (want_tc && tc_rows_ok(w, N, K))

@@ -8,6 +8,9 @@
 //   s16d8c1  the same kernel, one CTA per SM, 128 bytes in flight
 //   s8ring   the TMA-ring mma.sync kernel of stream.cuh     another order: lx_tune_set refuses it, lx_tune_force takes it
 //   s1tc     the tcgen05 product (INT8 / FP8, wide weights) another order again
+//   s16d1c1  one CTA per SM, units brought into shared memory by bulk copies (gemv_ring8.cuh: INT8 / FP8 rows short enough
+//            for two units to fit; gemv_x16.cuh: the lossless format); the decode GEMV's sums. Named for a weight it does
+//            not take, it is the default.
 // "gemv_bf16x" lists only forms of the decode GEMV, without a split: its variants are the format's own, change no sum and
 // are admitted at every key (the kernel must keep the bits of the bf16 kernel's default): d4c2 and d8c1 as above, and
 //   d1c1     the format's own kernel (gemv_x16.cuh): one CTA per SM, records brought into shared memory by bulk copies
@@ -28,8 +31,8 @@ struct VariantList {
   const char* const* names;
 };
 
-enum GemvVariant { kGemvD4C2 = 0, kGemvD8C1 = 1, kGemvRing = 2, kGemvTc = 3, kGemvVariants = 4, kGemvX16Pipe = 4 };
-inline const char* const kGemvVariantNames[kGemvVariants] = {"s16d4c2", "s16d8c1", "s8ring", "s1tc"};
+enum GemvVariant { kGemvD4C2 = 0, kGemvD8C1 = 1, kGemvRing = 2, kGemvTc = 3, kGemvX16Pipe = 4, kGemvVariants = 5 };
+inline const char* const kGemvVariantNames[kGemvVariants] = {"s16d4c2", "s16d8c1", "s8ring", "s1tc", "s16d1c1"};
 constexpr int kX16Variants = 3;
 inline const char* const kX16VariantNames[kX16Variants] = {"d4c2", "d8c1", "d1c1"};
 // The lossless kernel's third entry is its own kernel, not the ring: an index of its list as a GemvVariant.
@@ -64,7 +67,6 @@ inline int gemv_variant_by_name(const char* name) {
     const char* bare = full + std::strspn(full, "s0123456789");
     if (name && (std::strcmp(full, name) == 0 || std::strcmp(bare, name) == 0)) return i;
   }
-  if (name && std::strcmp(name, kX16VariantNames[2]) == 0) return kGemvX16Pipe;  // means something to the lossless kernel only
   return -1;
 }
 
