@@ -63,7 +63,7 @@ HEADLINE = "c3_fp8"
 ORDER = ["c1_bf16", "c2_int8", "c3_fp8", "c3_nvfp4", "c4_bf16x", "c5_moe_fp8"]
 DTYPE = {abi.W_BF16: "bf16", abi.W_INT8: "int8xbf16->f32", abi.W_FP8: "e4m3xbf16->f32", abi.W_NVFP4: "e2m1xbf16->f32", abi.W_BF16X: "bf16"}
 KERNELS = {"c1_bf16": "gemv_kernel<bf16>", "c2_int8": "tc_direct_kernel<int8>", "c3_fp8": "tc_direct_kernel<fp8> (M=16,64), gemv_kernel<fp8> (M=1)",
-           "c3_nvfp4": "tc_nvfp4_ss_kernel (M=16,64), gemv_kernel<nvfp4> (M=1)", "c4_bf16x": "gemv_x16_kernel",
+           "c3_nvfp4": "tc_nvfp4_ss_kernel (M=16,64), gemv_ring8_kernel<nvfp4> (M=1)", "c4_bf16x": "gemv_x16_kernel",
            "c5_moe_fp8": "tc_expert_kernel (whole step: route, group, 2 x (prepare, experts), ordered sum)"}
 ROTATE_BYTES = 1 << 30  # weights touched between two uses of the same copy (L2 is 126 MB)
 METRIC = "decode matmul effective HBM TB/s"

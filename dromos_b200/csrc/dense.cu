@@ -147,7 +147,9 @@ int launch_ring8(const GemvParams& P, int min_slots, cudaStream_t stream, bool& 
   taken = false;
   Ring8 R{};
   size_t smem = 0;
-  if (!aligned(P.w, 16) || P.K % 128 != 0 || !ring8_for(P.K, F, P.ncols, R, smem) || R.S < min_slots) return kOk;
+  if (!aligned(P.w, 16) || P.K % 128 != 0 || (F == LX_W_NVFP4 && (P.K % 256 != 0 || !aligned(P.scale, 16))) || !ring8_for(P.K, F, P.ncols, R, smem) ||
+      R.S < min_slots)
+    return kOk;
   const int sms = sm_count();
   if (!sms) return kInvalid;
   R.status = status_word();
@@ -179,6 +181,15 @@ int launch_gemv(GemvParams P, int variant, cudaStream_t stream) {
   // The 8-bit formats on short rows: the kernel on bulk copies where it was measured ahead, a single activation row with
   // three units in shared memory (14336 x 4096: FP8 14.1 against 14.4 us, INT8 14.4 against 17.9; 16384 x 2048 FP8 9.9
   // against 10.6; at M = 8 it is behind, 24.5 against 22.8). The same sums either way, so the choice may look at M.
+  // NVFP4: its 16-byte loads of 8 rows ask for half a line each, so the kernel on bulk copies is ahead wherever two units
+  // fit (28672 x 8192 at M = 1: 31.5 against 37.7 us; 14336 x 4096: 13.3 against 14.4); measured at one activation row.
+  if constexpr (F == LX_W_NVFP4) {
+    if ((variant == kGemvX16Pipe || (variant < 0 && P.M == 1)) && NT <= 2) {
+      bool taken = false;
+      const int e = NT == 1 ? launch_ring8<F, 1>(P, 2, stream, taken) : launch_ring8<F, 2>(P, 2, stream, taken);
+      if (taken) return e;
+    }
+  }
   if constexpr (F == LX_W_INT8 || F == LX_W_FP8) {
     if ((variant == kGemvX16Pipe || (variant < 0 && P.M == 1)) && NT <= 2) {
       bool taken = false;
