@@ -178,23 +178,16 @@ int launch_gemv(GemvParams P, int variant, cudaStream_t stream) {
       if (taken) return e;
     }
   }
-  // The 8-bit formats on short rows: the kernel on bulk copies where it was measured ahead, a single activation row with
-  // three units in shared memory (14336 x 4096: FP8 14.1 against 14.4 us, INT8 14.4 against 17.9; 16384 x 2048 FP8 9.9
-  // against 10.6; at M = 8 it is behind, 24.5 against 22.8). The same sums either way, so the choice may look at M.
-  // NVFP4: its 16-byte loads of 8 rows ask for half a line each, so the kernel on bulk copies is ahead wherever two units
-  // fit (28672 x 8192 at M = 1: 31.5 against 37.7 us; 14336 x 4096: 13.3 against 14.4); measured at one activation row.
-  if constexpr (F == LX_W_NVFP4) {
-    if ((variant == kGemvX16Pipe || (variant < 0 && P.M == 1)) && NT <= 2) {
+  // INT8 / FP8 / NVFP4 on rows short enough for two units in shared memory: the kernel on bulk copies (gemv_ring8.cuh)
+  // where it was measured ahead, up to four activation rows. The same sums either way, so the choice may look at M.
+  //   8-bit, 14336 x 4096 at M = 1 / 2 / 4: FP8 14.1 / 14.6 / 17.3 against 14.4 / 15.2 / 17.8 us, INT8 at M = 1 14.4 against
+  //   17.9; 16384 x 2048 FP8 9.9 against 10.6; at M = 8 it is behind, 24.5 against 22.8.
+  //   NVFP4 (whose 16-byte loads of 8 rows ask for half a line each), 28672 x 8192 at M = 1 / 2 / 4: 31.5 / 33.8 / 40.1
+  //   against 37.7 / 39.3 / 43.4 us; 14336 x 4096 at M = 1: 13.3 against 14.4.
+  if constexpr (F == LX_W_INT8 || F == LX_W_FP8 || F == LX_W_NVFP4) {
+    if ((variant == kGemvX16Pipe || (variant < 0 && P.M <= 4)) && NT <= 2) {
       bool taken = false;
       const int e = NT == 1 ? launch_ring8<F, 1>(P, 2, stream, taken) : launch_ring8<F, 2>(P, 2, stream, taken);
-      if (taken) return e;
-    }
-  }
-  if constexpr (F == LX_W_INT8 || F == LX_W_FP8) {
-    if ((variant == kGemvX16Pipe || (variant < 0 && P.M == 1)) && NT <= 2) {
-      bool taken = false;
-      const int min_slots = variant == kGemvX16Pipe ? 2 : 3;
-      const int e = NT == 1 ? launch_ring8<F, 1>(P, min_slots, stream, taken) : launch_ring8<F, 2>(P, min_slots, stream, taken);
       if (taken) return e;
     }
   }
