@@ -41,7 +41,9 @@ def test_host_only_entry_points_answer_without_a_gpu():
     assert lib.lx_tune_variants(b"gemm_w.f8.sm100") == 1 and lib.lx_tune_set(b"gemm_w.f8.sm100", 200, 384, 1024, 0) == 0
     assert lib.lx_tune_variants(b"gemv_w_fp8") >= 1 and lib.lx_tune_variants(b"nope") == 0
     names = [lib.lx_tune_variant_name(b"gemv_w_fp8", i) for i in range(lib.lx_tune_variants(b"gemv_w_fp8"))]
-    assert re.match(rb"s16d\d+c\d+", names[0]) and b"s8ring" in names and b"s1tc" in names
+    assert re.match(rb"s16d\d+c\d+", names[0]) and b"s8ring" in names and b"s1tc" in names and b"s16d1c1" in names
+    lossless = [lib.lx_tune_variant_name(b"gemv_bf16x", i) for i in range(lib.lx_tune_variants(b"gemv_bf16x"))]
+    assert lossless == [b"d4c2", b"d8c1", b"d1c1"]  # its own forms, no split in the name: every one keeps the bf16 kernel's order
     assert lib.lx_tune_variant_name(b"gemv_w_fp8", len(names)) is None
     assert lib.lx_tune_set(b"gemv_w_fp8", 1, 64, 64, 10**6) == abi.ERR_TUNE_VARIANT
     assert lib.lx_tune_set(b"gemv_w_fp8", 3, 64, 64, 1) == 0 and lib.lx_tune_get(b"gemv_w_fp8", 4, 64, 64) == 1  # M bucket 4
