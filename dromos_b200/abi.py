@@ -81,6 +81,7 @@ SIGNATURES = {
 EXTENSIONS = {
     "lx_b200_kernel_launches": (c_i64, []),
     "lx_b200_last_error": (c_int, []),
+    "lx_b200_gemv_ring_plan": (c_int, [c_int, c_int, c_int, c_int, c_ptr]),
     "lx_b200_moe_experts_grouped_static": (c_int, [c_ptr, c_ptr, c_ptr, _W, _W, c_int, c_ptr, c_int, c_int, c_int, c_int, c_int, c_ptr]),
     "lx_b200_moe_static_scratch_bytes": (c_i64, []),
     "lx_b200_moe_static_scratch_ptr": (c_ptr, []),

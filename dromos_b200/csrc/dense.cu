@@ -451,6 +451,35 @@ extern "C" int lx_b200_linear_allgather(const void* x, lx_dtype x_dtype, int ld_
                               static_cast<cudaStream_t>(stream));
 }
 
+// The shared-memory plan of the decode GEMV kernels that bring their weights in with bulk copies (gemv_x16.cuh,
+// gemv_ring8.cuh) for a weight format, K and M, without launching anything: the same geometry functions the launches use.
+// Fills out[0..11] (see the header); out[0], the ring's slots, stays 0 when the format has no such kernel or no ring fits.
+extern "C" int lx_b200_gemv_ring_plan(int wtype, int K, int M, int x_is_bf16, int32_t* out) {
+  if (!out || K <= 0 || M < 1 || M > 8) return kInvalid;
+  for (int i = 0; i < 12; ++i) out[i] = 0;
+  if (wtype != LX_W_BF16X && wtype != LX_W_INT8 && wtype != LX_W_FP8 && wtype != LX_W_NVFP4) return kOk;
+  if (!gemv_shape_ok(wtype, K, x_is_bf16 != 0)) return kOk;
+  const int planes = terms_for(gemv_mma_of(wtype), x_is_bf16 != 0), ncols = M * planes;
+  if ((ncols + 7) / 8 > 2) return kOk;
+  size_t smem = 0;
+  if (wtype == LX_W_BF16X) {
+    X16Ring r{};
+    if (!x16_ring_for(K, ncols, r, smem)) return kOk;
+    const int32_t v[12] = {r.S, r.whole, r.cb, r.spu, static_cast<int32_t>(r.stride), static_cast<int32_t>(r.slot_bytes),
+                           static_cast<int32_t>(r.hstride), static_cast<int32_t>(r.hslot_bytes), static_cast<int32_t>(r.hdr_off),
+                           static_cast<int32_t>(r.ring_off), static_cast<int32_t>(r.bar_off), static_cast<int32_t>(smem)};
+    for (int i = 0; i < 12; ++i) out[i] = v[i];
+    return kOk;
+  }
+  if (K % 128 != 0 || (wtype == LX_W_NVFP4 && K % 256 != 0)) return kOk;
+  Ring8 r{};
+  if (!ring8_for(K, wtype, ncols, r, smem)) return kOk;
+  const int32_t v[12] = {r.S, 1, 0, 1, row_bytes_of(wtype, K), static_cast<int32_t>(r.slot_bytes), static_cast<int32_t>(r.scale_off), 0,
+                         static_cast<int32_t>(r.ring_off), static_cast<int32_t>(r.ring_off), static_cast<int32_t>(r.bar_off), static_cast<int32_t>(smem)};
+  for (int i = 0; i < 12; ++i) out[i] = v[i];
+  return kOk;
+}
+
 extern "C" int lx_b200_wait_arrivals(int* counter, int total, void* stream) {
   if (!counter || total <= 0) return kInvalid;
   return tc_wait_arrivals(counter, total, static_cast<cudaStream_t>(stream));

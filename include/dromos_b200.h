@@ -183,6 +183,13 @@ LX_API int64_t lx_b200_kernel_launches(void);
  * inside a kernel ran out (the kernel then finished without hanging; its output is not valid).
  * Synchronizes the device. */
 LX_API int lx_b200_last_error(void);
+/* The shared-memory plan of the decode GEMV kernels that bring weights in with bulk copies (BF16X; INT8 / FP8 / NVFP4 on
+ * rows short enough), for a weight format, K, M <= 8 and activation dtype; nothing is launched. out[0..11] = ring slots
+ * (0: no such kernel for this case), whole units per stage (0 / 1), blocks per stage, stages per unit, bytes between two
+ * rows of a slot, bytes of a slot, bytes between two header rows (NVFP4: where the block scales start in a slot), bytes
+ * of a header slot, and the offsets of the header ring, the ring and the barriers in dynamic shared memory, and its total.
+ * Returns 0, or 1 for a null pointer, K <= 0 or M outside 1..8. For tests of the layout on machines without a GPU. */
+LX_API int lx_b200_gemv_ring_plan(int wtype, int K, int M, int x_is_bf16, int32_t* out);
 
 /* A row-sharded product whose epilogue is the all-gather (no counterpart in the reference, which is single-GPU). Every
  * rank calls it with its rows of W (N rows, the columns col0 .. col0 + N - 1 of the whole y): the outputs are stored
